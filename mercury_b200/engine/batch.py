@@ -1,0 +1,168 @@
+"""One step's ragged batch as the kernels see it.
+
+A step runs a list of entries, each a live sequence with its next tokens: a portion of a
+prompt (any length from one token up) or one decoded token. All tokens of all entries are
+laid out as one flat batch; per sequence the kernels get where its tokens start in the
+batch, how many keys it has once this step's tokens are stored, its state slot and its
+block table per layer group. Everything is int32 and lives in ONE pinned host buffer that
+goes to the device in one copy.
+
+Layout of the buffer for capacities (tokens Tc, sequences Sc, pages per sequence Pc,
+logit rows Rc, groups G):
+
+    token_ids[Tc] positions[Tc] seq_of_token[Tc] q_start[Sc+1] kv_len[Sc] slots[Sc]
+    logit_rows[Rc] tables[G][Sc][Pc]
+
+Unused token rows carry sequence -1 (kernels skip them), unused sequences have q_len 0.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache.manager import Sequence
+
+
+@dataclass
+class StepEntry:
+    """`tokens` are the next tokens of `seq` (positions seq.num_computed ...); `want` lists
+    the indices among them whose logits are asked for; `hashes` are the chain hashes of the
+    sequence's full pages, if its pages are to become shareable."""
+
+    seq: Sequence
+    tokens: list[int]
+    want: list[int]
+    hashes: list[int] | None = None
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_seqs: int
+    max_q_len: int
+    max_kv_len: int
+    num_logit_rows: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    seq_of_token: torch.Tensor
+    q_start: torch.Tensor
+    kv_len: torch.Tensor
+    slots: torch.Tensor
+    logit_rows: torch.Tensor
+    tables: list[torch.Tensor]
+    decode_only: bool = False
+
+
+class BatchBuffers:
+    """The pinned host buffer, its device twin, and the code that fills them."""
+
+    def __init__(self, device, max_tokens: int, max_seqs: int, max_pages: int, num_groups: int,
+                 pin: bool):
+        self.device = torch.device(device)
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        self.max_pages = max_pages
+        self.num_groups = num_groups
+        size = self._layout(max_tokens, max_seqs, max_pages, max_tokens)["size"]
+        self.host = torch.zeros(size, dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(size, dtype=torch.int32, device=self.device)
+        self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
+        self._in_flight = False
+
+    def _layout(self, tc: int, sc: int, pc: int, rc: int) -> dict:
+        names = [("token_ids", tc), ("positions", tc), ("seq_of_token", tc), ("q_start", sc + 1),
+                 ("kv_len", sc), ("slots", sc), ("logit_rows", rc),
+                 ("tables", self.num_groups * sc * pc)]
+        out, offset = {}, 0
+        for name, count in names:
+            out[name] = (offset, count)
+            offset += count
+        out["size"] = offset
+        return out
+
+    def build(self, entries: list[StepEntry], page_size: int, token_capacity: int | None = None,
+              seq_capacity: int | None = None, page_capacity: int | None = None) -> StepBatch:
+        """Fill the host buffer for `entries`, copy it, and return device views. The
+        capacities (default: exactly what the entries need) fix the layout, so that a
+        captured graph can be replayed on batches of different content."""
+        num_seqs = len(entries)
+        num_tokens = sum(len(e.tokens) for e in entries)
+        rows = sum(len(e.want) for e in entries)
+        pages = max((len(t) for e in entries for t in e.seq.tables), default=1)
+        tc = num_tokens if token_capacity is None else token_capacity
+        sc = num_seqs if seq_capacity is None else seq_capacity
+        pc = max(1, pages) if page_capacity is None else page_capacity
+        rc = max(1, rows)
+        if tc > self.max_tokens or sc > self.max_seqs or pc > self.max_pages:
+            raise ValueError(
+                f"step of {tc} tokens, {sc} sequences, {pc} pages per sequence exceeds the "
+                f"runner's limits ({self.max_tokens}, {self.max_seqs}, {self.max_pages})"
+            )
+        if num_tokens > tc or num_seqs > sc or pages > pc:
+            raise ValueError("the entries do not fit the capacities given")
+        lay = self._layout(tc, sc, pc, rc)
+        buf = self.host_np
+        if self._in_flight:
+            # the last step's copy reads this buffer; do not overwrite it before it ran
+            self._copied.synchronize()
+            self._in_flight = False
+
+        def view(name):
+            start, count = lay[name]
+            return buf[start:start + count]
+
+        token_ids, positions, seq_of = view("token_ids"), view("positions"), view("seq_of_token")
+        q_start, kv_len, slots = view("q_start"), view("kv_len"), view("slots")
+        logit_rows = view("logit_rows")
+        tables = view("tables").reshape(self.num_groups, sc, pc)
+        seq_of[:] = -1
+        token_ids[num_tokens:] = 0
+        positions[num_tokens:] = 0
+        tables[:] = -1
+        logit_rows[:] = 0
+        cursor = row = 0
+        max_q = max_kv = 0
+        for index, e in enumerate(entries):
+            n = len(e.tokens)
+            start = e.seq.num_computed
+            token_ids[cursor:cursor + n] = e.tokens
+            positions[cursor:cursor + n] = np.arange(start, start + n, dtype=np.int32)
+            seq_of[cursor:cursor + n] = index
+            q_start[index] = cursor
+            kv_len[index] = start + n
+            slots[index] = e.seq.slot
+            for group, table in enumerate(e.seq.tables):
+                tables[group, index, :len(table)] = table
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"{e.seq.seq_id}: wanted place {w} is outside its {n} tokens")
+                logit_rows[row] = cursor + w
+                row += 1
+            cursor += n
+            max_q = max(max_q, n)
+            max_kv = max(max_kv, start + n)
+        q_start[num_seqs:sc + 1] = cursor
+        kv_len[num_seqs:] = 0
+        slots[num_seqs:] = 0
+        size = lay["size"]
+        self.dev[:size].copy_(self.host[:size], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._in_flight = True
+
+        def dview(name):
+            start, count = lay[name]
+            return self.dev[start:start + count]
+
+        return StepBatch(
+            num_tokens=tc, num_seqs=sc, max_q_len=max_q, max_kv_len=max_kv, num_logit_rows=rows,
+            token_ids=dview("token_ids"), positions=dview("positions"),
+            seq_of_token=dview("seq_of_token"), q_start=dview("q_start"), kv_len=dview("kv_len"),
+            slots=dview("slots"), logit_rows=dview("logit_rows")[:rows],
+            tables=[t for t in dview("tables").view(self.num_groups, sc, pc)],
+            decode_only=all(len(e.tokens) == 1 for e in entries),
+        )

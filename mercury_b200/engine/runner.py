@@ -1,0 +1,192 @@
+"""The step function: run a batch of (sequence, its next tokens) from the cache and return
+the logits at the wanted places.
+
+`ModelRunner` owns the model's weights, the page tensors, the per-request state tensors,
+the cache manager and the activation buffers. `step(entries)` is the only way tokens go
+through the model: trace replay, the scheduler's engine and the benchmarks all call it.
+The reference's counterpart is `ModelRunner.execute` (mercury/runner.py:106-178), which
+runs one forward per prompt and another for the decode batch and samples inside; here one
+pass takes prompt portions and decode tokens together and sampling is a separate call.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages, Sequence
+from ..config.model_config import ModelConfig, architecture_named, read_model_config
+from ..models.model import Model
+from ..parts.base import PartSetup
+from ..weights.loader import check_tensors, read_checkpoint
+from .batch import BatchBuffers, StepBatch, StepEntry
+
+
+class Workspace:
+    """Activation buffers by name, allocated once for the largest step and handed out as
+    row slices, so that addresses stay the same from step to step."""
+
+    def __init__(self, device, dtype, max_rows: int):
+        self.device = device
+        self.dtype = dtype
+        self.max_rows = max_rows
+        self._buffers: dict[tuple, torch.Tensor] = {}
+
+    def get(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
+        dt = self.dtype if dtype is None else (torch.float32 if dtype == "float32" else dtype)
+        key = (name, cols, dt)
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
+            capacity = max(rows, self.max_rows if buf is None else 2 * buf.shape[0])
+            buf = torch.empty((capacity, cols), dtype=dt, device=self.device)
+            self._buffers[key] = buf
+        return buf[:rows]
+
+
+class StepContext:
+    """What parts see during one step: the kernels, the batch, buffers, the page size."""
+
+    def __init__(self, ops, workspace: Workspace, page_size: int, dtype):
+        self.ops = ops
+        self.workspace = workspace
+        self.page_size = page_size
+        self.dtype = dtype
+        self.batch: StepBatch | None = None
+
+    def buffer(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
+        return self.workspace.get(name, rows, cols, dtype)
+
+
+class ModelRunner:
+    def __init__(
+        self,
+        model: str | Path | None = None,
+        *,
+        dtype: torch.dtype = torch.bfloat16,
+        device: str = "cuda",
+        page_size: int = 16,
+        num_pages: int = 256,
+        max_seqs: int = 8,
+        max_step_tokens: int = 2048,
+        max_model_len: int | None = None,
+        ops=None,
+        config: ModelConfig | None = None,
+        tensors: dict[str, torch.Tensor] | None = None,
+    ):
+        """`model` is a folder with config.json and safetensors; or pass `config` and
+        `tensors` (a `{name: tensor}` dictionary) directly. `ops` is the kernel set; by
+        default the CUDA kernels, which refuse to load without a GPU."""
+        self.device = torch.device(device)
+        self.dtype = dtype
+        if config is None:
+            _entry, config = read_model_config(model)
+        self.config = config
+        entry = architecture_named(config.architecture)
+        self.spec = entry.describe(config)
+        self.model = Model(self.spec)
+        specs = self.model.tensor_specs()
+        if tensors is None:
+            tensors = read_checkpoint(model, specs, self.model.optional_tensors())
+        else:
+            check_tensors({n: (tuple(t.shape), t.is_floating_point()) for n, t in tensors.items()},
+                          specs, self.model.optional_tensors())
+        if ops is None:
+            from ..kernels.ops import CudaOps
+
+            ops = CudaOps(self.device)
+        self.ops = ops
+        self.max_model_len = min(max_model_len or self.spec.max_positions, self.spec.max_positions)
+        setup = PartSetup(self.device, dtype, ops, self.max_model_len)
+        self.model.load(tensors, setup)
+
+        self.page_size = page_size
+        self.max_seqs = max_seqs
+        self.max_step_tokens = max_step_tokens
+        self.cache = CacheManager(self.model.group_windows, num_pages, page_size, max_seqs)
+        self.kv_layers: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        for cache_id, layer in self.model.cache_layers.items():
+            pages = self.cache.pools[layer.group].num_pages
+            store = torch.zeros(
+                (2, pages, layer.need.num_kv_heads, page_size, layer.need.head_dim),
+                dtype=dtype, device=self.device)
+            self.kv_layers[cache_id] = (store[0], store[1])
+        self.states: dict[int, torch.Tensor] = {
+            index: torch.zeros((max_seqs, *need.shape), dtype=need.dtype, device=self.device)
+            for index, need in self.model.state_needs.items()
+        }
+        self.has_state = bool(self.states)
+        max_pages = -(-self.max_model_len // page_size)
+        self.buffers = BatchBuffers(self.device, max_step_tokens, max_seqs, max_pages,
+                                    max(1, len(self.model.group_windows)),
+                                    pin=self.device.type == "cuda")
+        self.workspace = Workspace(self.device, dtype, max_step_tokens)
+        self.ctx = StepContext(ops, self.workspace, page_size, dtype)
+        self.steps = 0
+
+    # ------------------------------------------------------------------ sizes
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of keys and values one token occupies over all cache layers
+        (mercury/config.py:73-81)."""
+        elem = torch.finfo(self.dtype).bits // 8
+        return sum(2 * l.need.num_kv_heads * l.need.head_dim * elem
+                   for l in self.model.cache_layers.values())
+
+    # ------------------------------------------------------------------ sequences
+
+    def open(self, seq_id: str) -> Sequence:
+        return self.cache.open(seq_id)
+
+    def close(self, seq: Sequence) -> None:
+        self.cache.close(seq)
+
+    def _reset_fresh_state(self) -> None:
+        fresh, self.cache.fresh_slots = self.cache.fresh_slots, []
+        if self.states and fresh:
+            index = torch.tensor(fresh, dtype=torch.long, device=self.device)
+            for state in self.states.values():
+                state.index_fill_(0, index, 0)
+
+    # ------------------------------------------------------------------ the step
+
+    def prepare(self, entries: list[StepEntry], **capacities) -> StepBatch:
+        """Provide pages for the entries' tokens and put the batch on the device."""
+        for e in entries:
+            if not e.tokens:
+                raise ValueError(f"{e.seq.seq_id}: an entry needs at least one token")
+            end = e.seq.num_computed + len(e.tokens)
+            if end > self.max_model_len:
+                raise ValueError(f"{e.seq.seq_id}: {end} tokens exceed max_model_len "
+                                 f"{self.max_model_len}")
+            if not self.cache.ensure(e.seq, end):
+                raise OutOfPages(
+                    f"{e.seq.seq_id}: no pages left for tokens up to {end} "
+                    f"(available per group: {self.cache.num_available()})")
+        self._reset_fresh_state()
+        return self.buffers.build(entries, self.page_size, **capacities)
+
+    def run(self, batch: StepBatch) -> torch.Tensor | None:
+        """The model pass over a prepared batch; float32 logits `[wanted, vocab]` or None."""
+        self.ctx.batch = batch
+        return self.model.forward(self.ctx, self.kv_layers, self.states)
+
+    def finish(self, entries: list[StepEntry]) -> None:
+        """Book the tokens as computed: full pages become shareable, passed pages go back."""
+        for e in entries:
+            self.cache.advance(e.seq, e.seq.num_computed + len(e.tokens), e.hashes)
+        self.steps += 1
+
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run exactly the tokens given, as one batch, from the cache that earlier steps
+        left; returns the logits at the wanted places in the order of the entries and of
+        each entry's `want` (None if nothing is wanted)."""
+        batch = self.prepare(entries)
+        logits = self.run(batch)
+        self.finish(entries)
+        return logits

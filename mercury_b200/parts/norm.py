@@ -1,0 +1,36 @@
+"""RMSNorm fused with the residual sum.
+
+The formula is mercury/model/qwen2.py:27-31: the pending delta is added to the residual
+stream, the sum is the new residual, and the sum is normalised by rsqrt(mean(x^2) + eps)
+and scaled by the weight. The reference adds in the activation dtype on its plain path and
+in float32 on its fused path (mercury/kernels/rmsnorm_quant.py:40-46); here the stream
+itself is float32, so nothing is rounded between layers.
+"""
+
+from __future__ import annotations
+
+from .base import Norm, TensorSpec, register_norm
+
+
+class RMSNorm(Norm):
+    def __init__(self, size: int, eps: float, weight_name: str, init_std: float = 0.05):
+        self.size = size
+        self.eps = eps
+        self.weight_name = weight_name
+        self.init_std = init_std
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weight_name, (self.size,), init="ones_normal", std=self.init_std)]
+
+    def load(self, tensors, setup):
+        self.weight = setup.place(tensors[self.weight_name])
+
+    def add_norm(self, h, delta, ctx, rows=None):
+        count = h.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer("normed" if rows is None else "normed_rows", count, self.size)
+        ctx.ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        return out
+
+
+register_norm("rmsnorm", RMSNorm)

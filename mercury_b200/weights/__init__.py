@@ -1,0 +1,2 @@
+from .loader import WeightError, check_tensors, read_checkpoint, weight_files  # noqa: F401
+from .random_init import random_tensors, write_random_model  # noqa: F401
