@@ -1,0 +1,92 @@
+// Shared helpers of the sm_100a kernels: storage types, error codes, reductions.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and the stream to
+// launch on, and returns 0 or one of the MB_ERR_* codes below when it refuses a size
+// (the Python wrapper turns the code into an exception that names the limit).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MB_OK 0
+#define MB_ERR_UNSUPPORTED_SIZE 1   // a size outside what the kernel was written for
+#define MB_ERR_BAD_DTYPE 2          // a dtype flag the entry point does not know
+#define MB_ERR_LAUNCH 3             // the launch itself failed (cudaGetLastError)
+#define MB_ERR_ALIGNMENT 4          // a pointer or stride breaks an alignment rule
+#define MB_ERR_SCRATCH 5            // the scratch buffer given is too small
+
+// dtype flags of the C interface
+#define MB_F32 0
+#define MB_BF16 1
+
+#define MB_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace mb {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// Load element i of an array whose dtype is only known at run time.
+__device__ __forceinline__ float load_as_float(const void* p, int64_t i, int dtype) {
+    return dtype == MB_F32 ? reinterpret_cast<const float*>(p)[i]
+                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds
+// 33 floats of shared memory. The order of the additions is fixed by the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+inline int launch_status() {
+    return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
+}
+
+}  // namespace mb

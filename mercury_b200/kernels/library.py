@@ -1,0 +1,71 @@
+"""The compiled kernels as a ctypes library, loaded once per process.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA device is
+present, `load()` raises and nothing of the engine runs.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from .build import BuildError, build
+
+_LIB = None
+
+ERRORS = {
+    1: "a size is outside what the kernel supports",
+    2: "unknown dtype flag",
+    3: "the CUDA launch failed",
+    4: "a pointer or stride is misaligned",
+    5: "the scratch buffer is too small",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "mb_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                       c_float, c_int, c_void_p],
+    "mb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "mb_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
+    "mb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                     c_int, c_int, c_void_p],
+    "mb_paged_attention_simt": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                c_void_p],
+    "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+}
+
+
+def load():
+    """Build if needed, load, and declare the entry points."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    try:
+        path = build()
+    except BuildError as err:
+        raise KernelError(f"the CUDA kernels could not be built: {err}") from err
+    lib = ctypes.CDLL(str(path))
+    for name, argtypes in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mb_attention_scratch_floats.restype = c_longlong
+    _LIB = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {ERRORS.get(code, f'error {code}')}")

@@ -1,0 +1,151 @@
+"""The kernel set of the engine: thin Python wrappers that hand tensors' addresses, sizes
+and the current stream to the compiled sm_100a kernels.
+
+This is the only kernel set the product has. It needs a CUDA device of compute capability
+10.x and the compiled library, and raises when either is missing.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .library import KernelError, check
+
+_F32, _BF16 = 0, 1
+
+
+def _flag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"the kernels take float32 and bfloat16, not {dtype}")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class CudaOps:
+    def __init__(self, device="cuda", decode_splits: int | None = None):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
+                              "no CPU path")
+        self.device = torch.device(device)
+        major, _minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}x")
+        self.lib = library.load()
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.decode_splits = decode_splits
+        self._scratch: torch.Tensor | None = None
+        self.launches = 0
+
+    # ------------------------------------------------------------------ helpers
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _scratch_for(self, floats: int) -> torch.Tensor:
+        if self._scratch is None or self._scratch.numel() < floats:
+            self._scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32,
+                                        device=self.device)
+        return self._scratch
+
+    @staticmethod
+    def _rows(t: torch.Tensor) -> torch.Tensor:
+        if not t.is_contiguous():
+            raise KernelError("kernels take contiguous tensors")
+        return t
+
+    # ------------------------------------------------------------------ kernels
+
+    def embed(self, token_ids, table, out):
+        self._rows(out)
+        check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
+                                out.shape[0], out.shape[1], table.shape[0], self._stream()),
+              "embed")
+        self.launches += 1
+
+    def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
+        count = h.shape[0] if rows is None else rows.shape[0]
+        if delta is not None and delta.dtype != out.dtype:
+            raise KernelError("add_rmsnorm: delta and out must share the activation dtype")
+        check(self.lib.mb_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(weight), _flag(weight.dtype),
+                                      _ptr(out), _ptr(rows), count, h.shape[1], float(eps),
+                                      _flag(out.dtype), self._stream()), "add_rmsnorm")
+        self.launches += 1
+
+    def linear(self, x, weight, bias, out):
+        m, k = x.shape
+        n = weight.shape[0]
+        if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+            raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> "
+                              f"{tuple(out.shape)} do not fit")
+        self._rows(x), self._rows(weight), self._rows(out)
+        check(self.lib.mb_gemm_simt(_ptr(x), _flag(x.dtype), _ptr(weight), _flag(weight.dtype),
+                                    _ptr(bias), _flag(bias.dtype) if bias is not None else 0,
+                                    _ptr(out), _flag(out.dtype), m, n, k, self._stream()),
+              "linear")
+        self.launches += 1
+
+    def swiglu(self, gate_up, out):
+        check(self.lib.mb_swiglu(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],
+                                 _flag(out.dtype), self._stream()), "swiglu")
+        self.launches += 1
+
+    def rope_cache_write(self, qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache):
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        store = int(cache is not None and cache.write)
+        if cache is not None and cache.k.dtype != qkv.dtype:
+            raise KernelError("rope_cache_write: pages and activations differ in dtype")
+        check(self.lib.mb_rope_store(
+            _ptr(qkv), _ptr(cos), _ptr(sin), rot, _ptr(batch.positions),
+            _ptr(batch.seq_of_token), _ptr(cache.table) if cache is not None else None,
+            cache.table.shape[1] if cache is not None else 0,
+            _ptr(cache.k) if cache is not None else None,
+            _ptr(cache.v) if cache is not None else None,
+            qkv.shape[0], num_heads, num_kv_heads, head_dim,
+            cache.page_size if cache is not None else 1, store, _flag(qkv.dtype),
+            self._stream()), "rope_cache_write")
+        self.launches += 1
+
+    def _splits(self, batch, num_kv_heads, group) -> int:
+        """Divide the keys of a decode-like batch over more blocks when the batch alone
+        cannot fill the device."""
+        if self.decode_splits is not None:
+            return max(1, self.decode_splits)
+        tiles = -(-batch.max_q_len * group // 16)
+        blocks = batch.num_seqs * tiles * num_kv_heads
+        key_tiles = -(-batch.max_kv_len // 32)
+        if blocks >= self.sm_count or key_tiles < 8:
+            return 1
+        return max(1, min(key_tiles // 4, -(-2 * self.sm_count // blocks), 64))
+
+    def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
+                        window, out):
+        group = num_heads // num_kv_heads
+        splits = self._splits(batch, num_kv_heads, group)
+        tokens = qkv.shape[0]
+        floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
+        scratch = self._scratch_for(floats) if floats else None
+        check(self.lib.mb_paged_attention_simt(
+            _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+            cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
+            _ptr(batch.seq_of_token), _ptr(out), _ptr(scratch),
+            scratch.numel() if scratch is not None else 0, tokens, batch.num_seqs,
+            batch.max_q_len, num_heads, num_kv_heads, head_dim, cache.page_size, float(scale),
+            int(window), splits, _flag(qkv.dtype), self._stream()), "paged_attention")
+        self.launches += 1 if splits == 1 else 2
+
+    def argmax(self, logits, out):
+        check(self.lib.mb_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
+                                 self._stream()), "argmax")
+        self.launches += 1
+
+    def sample(self, logits, temperature, top_p, u, out):
+        check(self.lib.mb_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(out),
+                                 logits.shape[0], logits.shape[1], self._stream()), "sample")
+        self.launches += 1

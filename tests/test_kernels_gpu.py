@@ -1,0 +1,305 @@
+"""Each CUDA kernel alone against its plain PyTorch twin, at sizes other than the engine's:
+widths and vocabularies that are no power of two, head sizes in steps of 16, odd numbers
+of heads and groups, every page size, padding rows, pages given back."""
+
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from kernel_twins import TorchOps
+from mercury_b200.parts.base import LayerCache
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mercury_b200.kernels.ops import CudaOps
+
+    return CudaOps("cuda")
+
+
+@pytest.fixture(scope="module")
+def twin():
+    return TorchOps(exact=True)
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=gen) * scale).to(dtype).cuda()
+
+
+def close(got, want, dtype, what=""):
+    """float32: sums in another order; bfloat16: one rounding of the result."""
+    tol = 2e-6 if dtype == torch.float32 else 5e-3
+    scale = max(float(want.abs().max()), 1e-6)
+    err = float((got.double() - want.double()).abs().max()) / scale
+    assert err <= tol, f"{what}: relative error {err:.3e} > {tol:.0e}"
+
+
+# ------------------------------------------------------------------------------ embedding
+
+@pytest.mark.parametrize("table_dtype", DTYPES, ids=IDS)
+def test_embed(ops, twin, table_dtype):
+    table = rand((1000, 200), table_dtype, 0)
+    ids = torch.randint(0, 1000, (37,), dtype=torch.int32).cuda()
+    got = torch.empty((37, 200), dtype=torch.float32, device="cuda")
+    want = torch.empty_like(got)
+    ops.embed(ids, table, got)
+    twin.embed(ids, table, want)
+    assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------------------ norm
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("rows,cols", [(1, 896), (7, 1536), (64, 100), (1000, 896), (3, 4100)])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_add_rmsnorm(ops, twin, dtype, rows, cols, with_delta):
+    h = rand((rows, cols), torch.float32, 1)
+    delta = rand((rows, cols), dtype, 2) if with_delta else None
+    weight = rand((cols,), dtype, 3) + 1
+    h_want = h.clone()
+    got = torch.empty((rows, cols), dtype=dtype, device="cuda")
+    want = torch.empty_like(got)
+    ops.add_rmsnorm(h, delta, weight, 1e-5, got)
+    twin.add_rmsnorm(h_want, delta, weight, 1e-5, want)
+    close(got, want, dtype, "normed")
+    close(h, h_want, torch.float32, "residual")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_add_rmsnorm_selected_rows_and_wide_weight(ops, twin, dtype):
+    h = rand((50, 330), torch.float32, 4)
+    delta = rand((50, 330), dtype, 5)
+    weight = rand((330,), torch.float32, 6) + 1     # a weight stored in 32-bit stays 32-bit
+    rows = torch.tensor([49, 0, 17, 17, 3], dtype=torch.int32).cuda()
+    before = h.clone()
+    got = torch.empty((5, 330), dtype=dtype, device="cuda")
+    want = torch.empty_like(got)
+    ops.add_rmsnorm(h, delta, weight, 1e-6, got, rows)
+    twin.add_rmsnorm(before.clone(), delta, weight, 1e-6, want, rows)
+    close(got, want, dtype)
+    assert torch.equal(h, before), "selected-row mode must leave the residual alone"
+
+
+def test_add_rmsnorm_zero_row(ops):
+    h = torch.zeros((2, 96), dtype=torch.float32, device="cuda")
+    out = torch.empty((2, 96), dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(h, None, torch.ones(96, dtype=torch.bfloat16, device="cuda"), 1e-6, out)
+    assert torch.count_nonzero(out) == 0
+
+
+# ------------------------------------------------------------------------------ products
+
+@pytest.mark.parametrize("m,n,k", [(1, 151, 70), (5, 130, 896), (77, 1152, 96), (130, 64, 4864),
+                                   (64, 64, 16), (3, 1000, 1)])
+@pytest.mark.parametrize("x_dtype,w_dtype,o_dtype", [
+    (torch.float32, torch.float32, torch.float32),
+    (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+    (torch.bfloat16, torch.bfloat16, torch.float32),
+    (torch.bfloat16, torch.float32, torch.bfloat16),
+], ids=["f32", "bf16", "bf16-f32out", "bf16-f32weight"])
+def test_linear(ops, twin, m, n, k, x_dtype, w_dtype, o_dtype):
+    x = rand((m, k), x_dtype, 7)
+    w = rand((n, k), w_dtype, 8, 0.1)
+    bias = rand((n,), w_dtype, 9) if n % 2 else None
+    got = torch.empty((m, n), dtype=o_dtype, device="cuda")
+    want = torch.empty_like(got)
+    ops.linear(x, w, bias, got)
+    twin.linear(x, w, bias, want)
+    close(got, want, o_dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_swiglu(ops, twin, dtype):
+    gate_up = rand((33, 2 * 517), dtype, 10, 3.0)
+    got = torch.empty((33, 517), dtype=dtype, device="cuda")
+    want = torch.empty_like(got)
+    ops.swiglu(gate_up, got)
+    twin.swiglu(gate_up, want)
+    close(got, want, dtype)
+
+
+# ------------------------------------------------------------------------------ attention
+
+def make_batch(q_lens, kv_lens, page_size, num_pages, pad_tokens=0, seed=0, drop_before=None):
+    """A ragged batch with scattered pages. `drop_before[s]` marks the pages of sequence s
+    that lie wholly below that position as given back (-1)."""
+    gen = torch.Generator().manual_seed(seed)
+    num_seqs = len(q_lens)
+    max_pages = max(-(-kv // page_size) for kv in kv_lens) + 1
+    perm = torch.randperm(num_pages, generator=gen).tolist()
+    table = torch.full((num_seqs, max_pages), -1, dtype=torch.int32)
+    positions, seq_of, q_start = [], [], [0]
+    for s, (q, kv) in enumerate(zip(q_lens, kv_lens)):
+        for i in range(-(-kv // page_size)):
+            table[s, i] = perm.pop()
+        if drop_before is not None:
+            for i in range(drop_before[s] // page_size):
+                table[s, i] = -1
+        positions += list(range(kv - q, kv))
+        seq_of += [s] * q
+        q_start.append(q_start[-1] + q)
+    positions += [0] * pad_tokens
+    seq_of += [-1] * pad_tokens
+    as_dev = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    return SimpleNamespace(
+        num_tokens=len(positions), num_seqs=num_seqs, max_q_len=max(q_lens),
+        max_kv_len=max(kv_lens), positions=as_dev(positions), seq_of_token=as_dev(seq_of),
+        q_start=as_dev(q_start), kv_len=as_dev(list(kv_lens))), table.cuda()
+
+
+def fill_cache(batch, table, kv_lens, q_lens, n_kv, d, page_size, num_pages, dtype, seed, poison):
+    """Pages holding random keys for the positions computed before this step, and poison
+    (NaN) everywhere else, so that any read outside a sequence's keys shows."""
+    fill = float("nan") if poison else 0.0
+    k = torch.full((num_pages, n_kv, page_size, d), fill, dtype=dtype, device="cuda")
+    v = torch.full((num_pages, n_kv, page_size, d), fill, dtype=dtype, device="cuda")
+    gen = torch.Generator().manual_seed(seed)
+    for s, (q, kv) in enumerate(zip(q_lens, kv_lens)):
+        for pos in range(kv - q):
+            page = int(table[s, pos // page_size])
+            if page < 0:
+                continue
+            k[page, :, pos % page_size] = torch.randn((n_kv, d), generator=gen).to(dtype).cuda()
+            v[page, :, pos % page_size] = torch.randn((n_kv, d), generator=gen).to(dtype).cuda()
+    return k, v
+
+
+ATTENTION_CASES = [
+    # n_q, n_kv, d, page, q_lens, kv_lens, window
+    (4, 2, 16, 16, (5, 1, 33), (5, 40, 33), 0),
+    (3, 1, 32, 8, (1, 1, 1, 1), (1, 9, 24, 40), 0),
+    (14, 2, 64, 16, (1, 17, 1), (300, 17, 64), 0),
+    (6, 2, 48, 16, (40, 1, 2), (100, 77, 50), 24),
+    (7, 1, 64, 32, (64, 1), (64, 129), 0),
+    (12, 2, 128, 16, (3, 1), (130, 257), 0),
+    (20, 1, 80, 64, (2, 1), (70, 200), 0),
+    (8, 8, 256, 16, (1, 9), (45, 60), 16),
+    (5, 5, 112, 8, (31, 1), (31, 32), 0),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=[f"case{i}" for i in range(len(ATTENTION_CASES))])
+def test_rope_store_and_attention(twin, dtype, splits, case):
+    from mercury_b200.kernels.ops import CudaOps
+
+    ops = CudaOps("cuda", decode_splits=splits)
+    n_q, n_kv, d, page, q_lens, kv_lens, window = case
+    num_pages = sum(-(-kv // page) for kv in kv_lens) + 5
+    drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
+    batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=3, seed=1,
+                              drop_before=drop)
+    k, v = fill_cache(batch, table, kv_lens, q_lens, n_kv, d, page, num_pages, dtype, 2, True)
+    tokens = batch.num_tokens
+    qkv = rand((tokens, (n_q + 2 * n_kv) * d), dtype, 3)
+    angles = torch.rand((max(kv_lens) + 1, d // 2), generator=torch.Generator().manual_seed(4)) * 6
+    tables = (angles.cos().cuda(), angles.sin().cuda())
+
+    qkv_twin, k_twin, v_twin = qkv.clone(), k.clone(), v.clone()
+    cache = LayerCache(k, v, page, table, True)
+    cache_twin = LayerCache(k_twin, v_twin, page, table, True)
+    ops.rope_cache_write(qkv, n_q, n_kv, d, tables, batch, cache)
+    twin.rope_cache_write(qkv_twin, n_q, n_kv, d, tables, batch, cache_twin)
+    live = batch.seq_of_token >= 0
+    close(qkv[live], qkv_twin[live], dtype, "rotated q/k")
+    assert torch.equal(torch.isnan(k), torch.isnan(k_twin)), "keys stored in the wrong slots"
+    close(torch.nan_to_num(k), torch.nan_to_num(k_twin), dtype, "stored keys")
+    close(torch.nan_to_num(v), torch.nan_to_num(v_twin), dtype, "stored values")
+
+    got = torch.zeros((tokens, n_q * d), dtype=dtype, device="cuda")
+    want = torch.zeros_like(got)
+    ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got)
+    twin.paged_attention(qkv_twin, n_q, n_kv, d, batch, cache_twin, d ** -0.5, window, want)
+    assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
+    close(got[live], want[live], dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("splits", [1, 5])
+def test_attention_finds_one_far_key(twin, dtype, splits):
+    """Among 700 keys one far key matches the query strongly; the output must be that
+    key's value. Its place is moved over page edges and tile edges."""
+    from mercury_b200.kernels.ops import CudaOps
+
+    ops = CudaOps("cuda", decode_splits=splits)
+    n_q, n_kv, d, page, kv = 4, 2, 64, 16, 700
+    for far in (0, 15, 16, 31, 32, 333, 698):
+        batch, table = make_batch((1,), (kv,), page, 60, seed=far)
+        k, v = fill_cache(batch, table, (kv,), (1,), n_kv, d, page, 60, dtype, 5, False)
+        k *= 0.05
+        qkv = torch.zeros((1, (n_q + 2 * n_kv) * d), dtype=dtype, device="cuda")
+        direction = torch.nn.functional.normalize(rand((d,), torch.float32, 6), dim=0)
+        qkv[0, :n_q * d] = (direction * 12).repeat(n_q).to(dtype)
+        slot = int(table[0, far // page])
+        k[slot, :, far % page] = (direction * 12).to(dtype)
+        cache = LayerCache(k, v, page, table, False)
+        ops.rope_cache_write(qkv, n_q, n_kv, d, None, batch, cache)
+        got = torch.zeros((1, n_q * d), dtype=dtype, device="cuda")
+        ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, 0, got)
+        want = v[slot, :, far % page].float().repeat_interleave(n_q // n_kv, dim=0).reshape(-1)
+        err = float((got[0].float() - want).abs().max())
+        assert err < 0.05, f"far key at {far}: output is off by {err}"
+
+
+def test_attention_refuses_what_it_cannot_do(ops):
+    batch, table = make_batch((1,), (4,), 16, 4)
+    k = torch.zeros((4, 1, 16, 272), dtype=torch.bfloat16, device="cuda")
+    cache = LayerCache(k, k.clone(), 16, table, True)
+    qkv = torch.zeros((1, 3 * 272), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((1, 272), dtype=torch.bfloat16, device="cuda")
+    from mercury_b200.kernels.library import KernelError
+
+    with pytest.raises(KernelError):
+        ops.paged_attention(qkv, 1, 1, 272, batch, cache, 1.0, 0, out)
+
+
+# ------------------------------------------------------------------------------ sampling
+
+def test_argmax_lowest_index_wins(ops):
+    logits = rand((9, 1517), torch.float32, 11)
+    logits[3, 700] = logits[3, 20] = 50.0
+    out = torch.empty(9, dtype=torch.int32, device="cuda")
+    ops.argmax(logits, out)
+    assert out.tolist() == torch.argmax(logits, dim=-1).tolist()
+    assert out[3] == 20
+
+
+@pytest.mark.parametrize("vocab", [331, 4097, 151936])
+def test_sample_lands_in_the_right_interval(ops, vocab):
+    """The drawn token's cumulative-probability interval contains u (within float32
+    rounding of the sums); greedy rows are the argmax; top-p keeps the right set."""
+    rows = 12
+    logits = rand((rows, vocab), torch.float32, 12, 2.0)
+    temperature = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.7, 0.2, 1.0, 0.0, 5.0, 0.7, 1.0, 0.05]).cuda()
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.9, 0.5, 0.1, 0.3, 0.95, 0.0, 0.999, 1.0]).cuda()
+    u = torch.tensor([0.5, 0.0, 0.999999, 0.25, 0.5, 0.75, 0.3, 0.1, 0.6, 0.9, 0.42, 0.8]).cuda()
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample(logits, temperature, top_p, u, out)
+    for r in range(rows):
+        t, p = float(temperature[r]), float(top_p[r])
+        tok = int(out[r])
+        if t <= 0:
+            assert tok == int(torch.argmax(logits[r]))
+            continue
+        probs = torch.softmax(logits[r].double().cpu() / max(t, 1e-5), dim=-1)
+        if p < 1.0:
+            ordered, index = probs.sort(descending=True)
+            before = ordered.cumsum(-1) - ordered
+            kept = torch.zeros_like(probs).scatter_(0, index, ordered.masked_fill(before > p, 0.0))
+            # the crossing token may fall either way when float32 sums touch the threshold
+            edge = (before - p).abs() < 1e-5
+            assert kept[tok] > 0 or bool(edge[index == tok]), f"row {r}: dropped token drawn"
+            probs = kept
+        cdf = probs.cumsum(-1) / probs.sum()
+        low = float(cdf[tok - 1]) if tok > 0 else 0.0
+        assert low - 1e-4 <= float(u[r]) <= float(cdf[tok]) + 1e-4, (r, tok, low, float(cdf[tok]))

@@ -1,0 +1,36 @@
+"""The replay program's logic without a GPU: the same traces as the GPU tests, run through
+the step function on top of the PyTorch kernel twins. This checks the batch layout, the
+block tables, page reuse and the window bookkeeping; the kernels are checked on the GPU."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import replay_cases
+from kernel_twins import TorchOps
+from replay_check import requests_for, run_and_check, sharpened_model
+from tiny import PAGE_SIZE, RAW
+
+LENGTHS = {"A": (37, 70, 129, 45), "B": (33, 64, 150, 41), "C": (50, 131, 65, 90),
+           "D": (35, 120, 64, 47)}
+
+
+def make_runner(name, num_tokens=320):
+    from mercury_b200.engine.runner import ModelRunner
+
+    _raw, config, tensors = sharpened_model(name)
+    page = PAGE_SIZE[name]
+    return ModelRunner(config=config, tensors=tensors, dtype=torch.float32, device="cpu",
+                       page_size=page, num_pages=num_tokens // page, max_seqs=4,
+                       max_step_tokens=num_tokens, max_model_len=num_tokens, ops=TorchOps())
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
+def test_replay_logic(name, mode):
+    lengths = LENGTHS[name]
+    requests = requests_for(name, lengths)
+    builder = getattr(replay_cases, mode)
+    steps, rows = builder(requests, 320, seed=2) if mode == "mixed" else builder(requests)
+    run_and_check(make_runner(name), name, lengths, steps, rows, torch.float32)

@@ -1,0 +1,109 @@
+"""Replay on the GPU, in 32-bit and in bfloat16: each request whole; most of it in one step
+and the last 32 tokens one by one; portions of changing size down to two tokens; and mixed,
+up to four live requests with so few pages that they are used again. Every written row is
+compared with the plain implementation."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import replay_cases
+from replay_check import TOLERANCE, oracle, requests_for, run_and_check, sharpened_model
+from tiny import PAGE_SIZE, RAW
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": (37, 70, 129, 200, 45, 96, 161), "B": (33, 64, 150, 41, 97, 208, 80),
+           "C": (50, 131, 65, 190, 77, 40, 100), "D": (35, 120, 64, 201, 90, 47, 133)}
+MAX_TOKENS = 512   # 8 pages of 64: the seven requests need far more, so pages come back
+
+
+def make_runner(name, dtype, num_tokens=MAX_TOKENS):
+    from mercury_b200.engine.runner import ModelRunner
+
+    _raw, config, tensors = sharpened_model(name)
+    page = PAGE_SIZE[name]
+    return ModelRunner(config=config, tensors=tensors, dtype=dtype, device="cuda", page_size=page,
+                       num_pages=num_tokens // page, max_seqs=4, max_step_tokens=num_tokens,
+                       max_model_len=min(num_tokens, RAW[name]["max_position_embeddings"]))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
+def test_replay_matches_plain(name, dtype, mode):
+    lengths = LENGTHS[name]
+    requests = requests_for(name, lengths)
+    if mode == "whole":
+        steps, rows = replay_cases.whole(requests)
+    elif mode == "decode_tail":
+        steps, rows = replay_cases.decode_tail(requests)
+    elif mode == "portions":
+        steps, rows = replay_cases.portions(requests)
+    else:
+        steps, rows = replay_cases.mixed(requests, MAX_TOKENS, seed=3)
+    runner = make_runner(name, dtype)
+    run_and_check(runner, name, lengths, steps, rows, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_long_decoding(dtype):
+    """One request decoded token by token over many pages, after a two-token start."""
+    name, lengths = "A", (300,)
+    requests = requests_for(name, lengths)
+    steps, rows = replay_cases.decode_tail(requests, tail=298)
+    runner = make_runner(name, dtype)
+    run_and_check(runner, name, lengths, steps, rows, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens(name, dtype):
+    """The first positions of a sequence, one token per step from the very first."""
+    lengths = (6, 1, 2, 3)
+    requests = requests_for(name, lengths)
+    steps, rows = replay_cases.decode_tail(requests, tail=64)
+    runner = make_runner(name, dtype)
+    run_and_check(runner, name, lengths, steps, rows, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """The program itself, as a user runs it: a model folder, steps on standard input."""
+    from mercury_b200.weights import write_random_model
+
+    name = "B"
+    _raw, config, tensors = sharpened_model(name)
+    folder = tmp_path / "model"
+    write_random_model(folder, config, seed=0)
+    from safetensors.torch import save_file
+
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    lengths = LENGTHS[name][:4]
+    requests = requests_for(name, lengths)
+    steps, rows = replay_cases.mixed(requests, 512, seed=1)
+    root = Path(__file__).resolve().parent.parent
+    out = tmp_path / "out"
+    done = subprocess.run(
+        [str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out",
+         str(out), "--max-tokens", "512", "--block-size", str(PAGE_SIZE[name])],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+        timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert done.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    want = oracle(name, LENGTHS[name])
+    tol = TOLERANCE[torch.float32 if dtype == "float32" else torch.bfloat16]
+    for step, expected in rows.items():
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(expected), -1)
+        for row, (rid, pos) in enumerate(expected):
+            err = np.abs(got[row] - want[rid][pos]).max() / np.abs(want[rid]).max()
+            assert err <= tol, (step, rid, pos, err)
