@@ -1,0 +1,363 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl mercury_b200|reference]
+
+The default run has the layer sizes of Qwen2.5-0.5B (24 layers, hidden 896, 14 query heads,
+2 KV heads of 64, feed-forward 4864, vocabulary 151936, tied head) with seeded random
+weights in bfloat16, pages of 16 tokens, a model length of 4096, and decodes a batch of 8
+requests whose contexts hold 2048 tokens. One "step" is one decode step of the whole batch.
+
+It prints ONE JSON line:
+  value      decoded tokens per second, timed on the device with CUDA events over K steps
+             issued back to back (after W warm-up steps);
+  e2e        the same through `Engine.step()`: every step copies its inputs from pinned host
+             memory, samples on the device and reads the tokens back to the host;
+  prefill    one 2048-token prompt in one step: tokens/s, ms, and flops / time / peak;
+  roofline   for the decode step: bytes it has to read (every weight once, the cache of
+             the live requests) / time, against the measured copy bandwidth;
+  points     decode tokens per second at batch 1 and 64.
+Weights (about 1 GB) are far larger than the 126 MB L2, so every step streams them from
+HBM again; no extra L2 flush is needed ("l2" in config says so).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN25_05B = {
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 24, "hidden_size": 896,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64,
+    "intermediate_size": 4864, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "use_sliding_window": False,
+    "max_position_embeddings": 32768,
+}
+BATCH = 8
+CONTEXT = 2048        # tokens each request holds when decoding starts
+MODEL_LEN = 4096      # benchmark context length: the most a request may reach
+PREFILL_TOKENS = 2048
+BLOCK = 16
+SEED = 0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        raw = json.loads(path.read_text())
+        out = dict(FALLBACK_PEAKS)
+        for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if isinstance(raw.get(key), (int, float)):
+                out[key] = float(raw[key])
+        return out, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=fd, stderr=subprocess.DEVNULL)
+            os.close(fd)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        clocks, top, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6 or not parts[0].isdigit():
+                continue
+            clocks.append(int(parts[0]))
+            top = int(parts[1]) if parts[1].isdigit() else top
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": top,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(cfg: dict) -> dict:
+    """Bytes a decode step must read and flops a prefill must do, from the sizes alone."""
+    h, i, v, layers = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    n_q, n_kv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    qkv = (n_q + 2 * n_kv) * d
+    per_layer = qkv * h + qkv + n_q * d * h + 2 * i * h + h * i + 2 * h
+    head = v * h
+    params_read = layers * per_layer + head + h   # tied table read once by the head
+    if not cfg["tie_word_embeddings"]:
+        pass  # the embedding table is only gathered from, not streamed
+    kv_per_token = 2 * layers * n_kv * d * 2
+    gemm_flops_per_token = 2 * layers * (qkv * h + n_q * d * h + 3 * i * h)
+    return {"weight_bytes": 2 * params_read, "kv_bytes_per_token": kv_per_token,
+            "gemm_flops_per_token": gemm_flops_per_token,
+            "attn_flops": lambda t: 2 * t * t * n_q * d * layers, "head_flops_per_row": 2 * head}
+
+
+def make_runner(torch, config, tensors, batch, page_tokens):
+    from mercury_b200.engine.runner import ModelRunner
+
+    return ModelRunner(config=config, tensors=tensors, dtype=torch.bfloat16, device="cuda",
+                       page_size=BLOCK, num_pages=page_tokens // BLOCK, max_seqs=batch,
+                       max_step_tokens=max(PREFILL_TOKENS, batch), max_model_len=MODEL_LEN)
+
+
+def timed(torch, fn, reps: int) -> float:
+    """Milliseconds per call of fn over `reps` calls, by CUDA events."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(reps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / reps
+
+
+def fill_contexts(torch, runner, batch, context, vocab):
+    from mercury_b200.engine.batch import StepEntry
+
+    gen = torch.Generator().manual_seed(SEED + 1)
+    seqs = []
+    for b in range(batch):
+        seq = runner.open(f"bench-{b}")
+        tokens = torch.randint(0, vocab, (context,), generator=gen).tolist()
+        for at in range(0, context, PREFILL_TOKENS):
+            runner.step([StepEntry(seq, tokens[at:at + PREFILL_TOKENS], [])])
+        seqs.append(seq)
+    torch.cuda.synchronize()
+    return seqs
+
+
+def decode_rate(torch, runner, batch, context, vocab, steps, warmup):
+    """(tokens/s, ms per step, launches per step) of `steps` decode steps of `batch`."""
+    from mercury_b200.engine.batch import StepEntry
+
+    seqs = fill_contexts(torch, runner, batch, context, vocab)
+    out = torch.empty(batch, dtype=torch.int32, device="cuda")
+    gen = torch.Generator().manual_seed(SEED + 2)
+    feed = torch.randint(0, vocab, (steps + warmup + 1, batch), generator=gen).tolist()
+    turn = [0]
+
+    def one():
+        tokens = feed[turn[0]]
+        turn[0] += 1
+        logits = runner.step([StepEntry(s, [tokens[i]], [0]) for i, s in enumerate(seqs)])
+        runner.ops.argmax(logits, out)
+
+    for _ in range(warmup):
+        one()
+    before = runner.ops.launches + runner.ops.library_calls
+    ms = timed(torch, one, steps)
+    launches = (runner.ops.launches + runner.ops.library_calls - before) / steps
+    for s in seqs:
+        runner.close(s)
+    return batch * 1e3 / ms, ms, launches
+
+
+def prefill_rate(torch, runner, vocab, reps=5):
+    from mercury_b200.engine.batch import StepEntry
+
+    gen = torch.Generator().manual_seed(SEED + 3)
+    tokens = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+    times = []
+    for rep in range(reps + 2):
+        seq = runner.open(f"prefill-{rep}")
+        ms = timed(torch, lambda: runner.step([StepEntry(seq, tokens, [PREFILL_TOKENS - 1])]), 1)
+        runner.close(seq)
+        if rep >= 2:
+            times.append(ms)
+    return statistics.median(times)
+
+
+def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
+    """Decode tokens/s through Engine.step(): host tokens in, host tokens out."""
+    from mercury_b200 import Engine, EngineConfig, SamplingParams
+    from mercury_b200.engine.request import RequestState
+
+    runner = make_runner(torch, config, tensors, batch, batch * (context + 256))
+    cfg = EngineConfig(model="(in memory)", dtype="bfloat16", block_size=BLOCK,
+                       num_blocks=runner.cache.pools[0].num_pages, max_running=batch,
+                       max_batched_tokens=max(PREFILL_TOKENS, batch), prefill_chunk=PREFILL_TOKENS,
+                       max_model_len=MODEL_LEN, prefix_caching=False, seed=SEED)
+    engine = Engine(cfg, runner=runner)
+    gen = torch.Generator().manual_seed(SEED + 4)
+    produced = []
+    for b in range(batch):
+        prompt = torch.randint(0, vocab, (context,), generator=gen).tolist()
+        engine.submit(f"e2e-{b}", prompt, steps + warmup + 8, lambda ev: produced.append(ev.kind),
+                      SamplingParams(ignore_eos=True))
+    while any(r.seq_len - r.num_computed != 1 or r.state is not RequestState.RUNNING
+              for r in engine.sched.running + engine.sched.waiting) or not engine.sched.running:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    size_before = len(produced)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    tokens = sum(1 for kind in produced[size_before:] if kind == "token")
+    assert tokens == batch * steps, (tokens, batch, steps)
+    lay = runner.buffers._layout(batch, batch, -(-(context + steps + warmup + 8) // BLOCK), batch)
+    return tokens / seconds, lay["size"] * 4, batch * 4
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from mercury_b200.config import config_from_dict
+    from mercury_b200.weights import random_tensors
+
+    peak, peak_kind = peaks()
+    _entry, config = config_from_dict(QWEN25_05B)
+    tensors = random_tensors(config, SEED, torch.bfloat16)
+    vocab = QWEN25_05B["vocab_size"]
+    numbers = model_numbers(QWEN25_05B)
+
+    sampler = ClockSampler()
+    sampler.start()
+    runner = make_runner(torch, config, tensors, 64, 64 * (CONTEXT + 256))
+    value, ms, launches = decode_rate(torch, runner, BATCH, CONTEXT, vocab, args.steps, args.warmup)
+    clocks = sampler.stop()
+    b1, _, _ = decode_rate(torch, runner, 1, CONTEXT, vocab, args.steps, args.warmup)
+    b64, _, _ = decode_rate(torch, runner, 64, CONTEXT, vocab, args.steps, args.warmup)
+    prefill_ms = prefill_rate(torch, runner, vocab)
+    del runner
+    torch.cuda.empty_cache()
+    e2e, h2d, d2h = e2e_rate(torch, config, tensors, BATCH, CONTEXT, vocab, args.steps, args.warmup)
+
+    step_bytes = numbers["weight_bytes"] + BATCH * (CONTEXT + args.warmup + args.steps // 2) * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = (PREFILL_TOKENS * numbers["gemm_flops_per_token"] + numbers["attn_flops"](PREFILL_TOKENS)
+             + numbers["head_flops_per_row"])
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2048-token contexts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform-random token ids, random N(0,0.02) weights",
+        "config": {"model": "Qwen2.5-0.5B sizes", "layers": 24, "layers_of_model": 24, "hidden": 896,
+                   "q_heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864,
+                   "vocab": 151936, "tied": True, "global_batch": BATCH, "seq_len": CONTEXT,
+                   "max_model_len": MODEL_LEN, "kv_block": BLOCK, "parallelism": "single GPU",
+                   "l2": "inputs>L2 (1 GB of weights streamed per step)",
+                   "peaks": peak_kind},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(round(launches * args.steps)),
+        "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)},
+        "clocks": clocks,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference (installed under baseline/_ref) on the same model folder,
+    batch and context, through its own Engine.submit/step."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "mercury").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed on this box"}
+    try:
+        import torch
+
+        from mercury_b200.config import config_from_dict
+        from mercury_b200.weights import write_random_model
+
+        sys.path.insert(0, str(ref))
+        from mercury.config import EngineConfig as RefConfig
+        from mercury.engine import Engine as RefEngine
+        from mercury.request import SamplingParams as RefParams
+    except Exception as err:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import failed: {type(err).__name__}: {err}"}
+    _entry, config = config_from_dict(QWEN25_05B)
+    vocab = QWEN25_05B["vocab_size"]
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(Path(tmp) / "model", config, SEED)
+        cfg = RefConfig(model=str(folder), device="cuda", dtype="bfloat16", block_size=BLOCK,
+                        num_blocks=BATCH * (CONTEXT + 256) // BLOCK, max_running=BATCH,
+                        max_model_len=MODEL_LEN, prefill_budget=BATCH * CONTEXT, seed=SEED)
+        engine = RefEngine(cfg)
+        gen = torch.Generator().manual_seed(SEED + 4)
+        produced = []
+        for b in range(BATCH):
+            prompt = torch.randint(0, vocab, (CONTEXT,), generator=gen).tolist()
+            engine.submit(f"ref-{b}", prompt, args.steps + args.warmup + 8,
+                          lambda ev: produced.append(ev.kind), RefParams(ignore_eos=True))
+        engine.step()                       # admits and prefills every prompt
+        for _ in range(args.warmup):
+            engine.step()
+        sampler = ClockSampler()
+        sampler.start()
+        torch.cuda.synchronize()
+        before = len(produced)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            engine.step()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        clocks = sampler.stop()
+        tokens = sum(1 for kind in produced[before:] if kind == "token")
+    return {"impl": "reference", "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2048-token contexts)",
+            "value": round(tokens / seconds, 1), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(1e3 * seconds / args.steps, 4), "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random weights",
+            "config": {"model": "Qwen2.5-0.5B sizes", "global_batch": BATCH, "seq_len": CONTEXT,
+                       "kv_block": BLOCK, "timing": "wall clock around Engine.step, host tokens in and out"},
+            "clocks": clocks}
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="mercury_b200", choices=("mercury_b200", "reference"))
+    args = p.parse_args()
+    if args.gpus != 1:
+        print("bench.py measures a single-GPU engine; --gpus must be 1", flush=True)
+        return 2
+    args.warmup = max(3, args.warmup)
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,236 @@
+"""The engine loop: drain commands, schedule, run one step, sample, route tokens.
+
+`Engine.submit` / `step` / `abort` keep the reference's meaning (mercury/engine.py:104-113,
+:144, :154); `generate` is the offline entry point the reference's tests spell out by hand
+(tests/test_runner.py:65-77 of the reference): submit every prompt, step until nothing is
+left, return the tokens by request. The loop runs on the caller's thread; there is no
+server around it.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable
+
+from ..cache.hashing import extend_hashes
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, request_seed
+from .batch import StepEntry
+from .metrics import EngineMetrics, StepRecord
+from .request import Request, RequestState
+from .runner import ModelRunner
+from .scheduler import Plan, Scheduler
+
+
+@dataclass(slots=True)
+class StreamEvent:
+    """What a request's sink receives (mercury/engine.py:17-25): kind is "token", "done",
+    "error" or "preempted"."""
+
+    rid: str
+    kind: str
+    token: int | None = None
+    index: int = 0
+    finish_reason: str | None = None
+    message: str | None = None
+    t: float = 0.0
+
+
+Sink = Callable[[StreamEvent], None]
+
+
+class Engine:
+    def __init__(self, cfg: EngineConfig, runner: ModelRunner | None = None,
+                 clock: Callable[[], float] = time.perf_counter, ops=None):
+        self.cfg = cfg
+        self.clock = clock
+        if runner is None:
+            runner = ModelRunner(
+                cfg.model, dtype=cfg.torch_dtype, device=cfg.device, page_size=cfg.block_size,
+                num_pages=cfg.num_blocks, max_seqs=cfg.max_running,
+                max_step_tokens=cfg.max_batched_tokens, max_model_len=cfg.max_model_len, ops=ops)
+        self.runner = runner
+        cfg.validate_against(runner.spec.max_positions)
+        self.cache = runner.cache
+        # a mixer with state of its own cannot skip tokens that a cached prefix would cover
+        prefix_caching = cfg.prefix_caching and not runner.has_state
+        self.sched = Scheduler(
+            self.cache, policy=cfg.policy, max_running=cfg.max_running,
+            prefill_budget=cfg.prefill_budget, max_batched_tokens=cfg.max_batched_tokens,
+            prefill_chunk=cfg.prefill_chunk, aging_tokens_per_s=cfg.aging_tokens_per_s,
+            max_wait_s=cfg.max_wait_s, scan_limit=cfg.scan_limit, prefix_caching=prefix_caching,
+            cryptographic_hashes=cfg.cryptographic_hashes)
+        self.sampler = Sampler(runner.ops, runner.device, cfg.max_running)
+        self.metrics = EngineMetrics(cfg.max_step_records)
+        self.eos_ids = set(runner.spec.eos_token_ids or ())
+        self._commands: list[tuple[str, object]] = []
+        self._sinks: dict[str, Sink] = {}
+        self._submitted = 0
+
+    # ------------------------------------------------------------------ client side
+
+    def submit(self, rid: str, prompt_ids: list[int], max_tokens: int, sink: Sink,
+               params: SamplingParams | None = None, arrival: float | None = None) -> None:
+        params = params or SamplingParams()
+        arrival = self.clock() if arrival is None else arrival
+        ceiling = min(self.runner.max_model_len, self.cfg.kv_capacity_tokens)
+        if not prompt_ids:
+            return self._reject(rid, sink, "prompt must contain at least one token")
+        if max_tokens < 1:
+            return self._reject(rid, sink, "max_tokens must be at least 1")
+        if len(prompt_ids) + max_tokens > ceiling:
+            return self._reject(
+                rid, sink, f"prompt ({len(prompt_ids)}) + max_tokens ({max_tokens}) exceeds the "
+                           f"{ceiling}-token ceiling of this engine")
+        vocab = self.runner.vocab_size
+        if any(not 0 <= int(t) < vocab for t in prompt_ids):
+            return self._reject(rid, sink, f"a prompt token lies outside the vocabulary of {vocab}")
+        r = Request(rid=rid, prompt=[int(t) for t in prompt_ids], max_tokens=max_tokens,
+                    arrival=arrival, hashes=self.sched.hashes_of(prompt_ids), params=params,
+                    seed=request_seed(params, self.cfg.seed, rid))
+        self._sinks[rid] = sink
+        self._submitted += 1
+        self._commands.append(("add", r))
+
+    def abort(self, rid: str) -> None:
+        self._commands.append(("abort", rid))
+
+    def _reject(self, rid: str, sink: Sink, message: str) -> None:
+        self.metrics.counters["rejected_requests"] += 1
+        sink(StreamEvent(rid=rid, kind="error", message=message, t=self.clock()))
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]
+                 | None = None, max_tokens: int = 16) -> list[list[int]]:
+        """Generate for every prompt (token ids in, token ids out), batching them as the
+        scheduler sees fit. Raises if a prompt is refused."""
+        outs: dict[str, list[int]] = {}
+        errors: list[str] = []
+
+        def sink_for(rid):
+            def sink(event: StreamEvent) -> None:
+                if event.kind == "token":
+                    outs[rid].append(event.token)
+                elif event.kind == "error":
+                    errors.append(f"{rid}: {event.message}")
+            return sink
+
+        base = self._submitted
+        for i, prompt in enumerate(prompts):
+            rid = f"gen-{base + i}"
+            outs[rid] = []
+            p = params[i] if isinstance(params, list) else params
+            self.submit(rid, prompt, max_tokens, sink_for(rid), p, arrival=float(base + i))
+        if errors:
+            raise ValueError("; ".join(errors))
+        self.run_until_idle()
+        return [outs[f"gen-{base + i}"] for i in range(len(prompts))]
+
+    def run_until_idle(self) -> None:
+        self._drain_commands()
+        while self.sched.has_work() or self._commands:
+            if self.step() is None and not self._commands and self.sched.has_work():
+                raise RuntimeError("the scheduler has work but planned nothing: the pool is too "
+                                   "small for the waiting request")
+
+    # ------------------------------------------------------------------ the loop
+
+    def step(self) -> StepRecord | None:
+        t_start = time.perf_counter()
+        self._drain_commands()
+        plan: Plan = self.sched.schedule(self.clock())
+        for r in plan.preempted:
+            self._emit(r, StreamEvent(rid=r.rid, kind="preempted", t=self.clock()))
+        if not plan:
+            self.metrics.counters["idle_steps"] += 1
+            return None
+
+        entries, sampling = [], []
+        page = self.cache.page_size
+        for e in plan.entries:
+            r = e.request
+            tokens = r.tokens
+            hashes = None
+            if self.sched.prefix_caching:
+                extend_hashes(r.hashes, tokens, page, self.cfg.cryptographic_hashes)
+                hashes = r.hashes
+            entries.append(StepEntry(r.seq, tokens[e.start:e.start + e.count],
+                                     [e.count - 1] if e.samples else [], hashes))
+            if e.samples:
+                sampling.append(r)
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, [(r.params, r.seed, len(r.out)) for r in sampling]) \
+            if sampling else []
+        now = self.clock()
+        for r, token in zip(sampling, tokens):
+            self._accept(r, token, now)
+        if self.cfg.debug_invariants:
+            self.cache.check_invariants()
+        record = StepRecord(
+            t=now, num_entries=len(plan.entries), num_decode=plan.num_decode,
+            num_tokens=plan.num_tokens, sched_s=plan.sched_seconds,
+            step_s=time.perf_counter() - t_start, waiting=len(self.sched.waiting),
+            running=len(self.sched.running), free_pages=min(self.cache.num_available()),
+            preempted=len(plan.preempted))
+        self.metrics.add_step(record)
+        return record
+
+    def _drain_commands(self) -> None:
+        commands, self._commands = self._commands, []
+        for kind, payload in commands:
+            if kind == "add":
+                self.sched.add(payload)
+            elif kind == "abort":
+                r = self.sched.abort(payload)
+                if r is not None:
+                    self.metrics.counters["aborted_requests"] += 1
+                    r.finished_at = self.clock()
+                    self.metrics.finished.append(r.record())
+                    self._emit(r, StreamEvent(rid=r.rid, kind="done", finish_reason="abort",
+                                              t=r.finished_at), close=True)
+                else:
+                    self._sinks.pop(payload, None)
+
+    def _accept(self, r: Request, token: int, now: float) -> None:
+        index = len(r.out)
+        r.out.append(int(token))
+        if r.first_token_at is None:
+            r.first_token_at = now
+        self._emit(r, StreamEvent(rid=r.rid, kind="token", token=int(token), index=index, t=now))
+        if r.done:
+            return   # the sink raised and the request was aborted
+        if len(r.out) >= r.max_tokens:
+            self._finish(r, "length", now)
+        elif not r.params.ignore_eos and int(token) in self.eos_ids:
+            self._finish(r, "stop", now)
+
+    def _finish(self, r: Request, reason: str, now: float) -> None:
+        r.state = RequestState.FINISHED
+        r.finish_reason = reason
+        r.finished_at = now
+        self.sched.drop(r)
+        self.metrics.counters["finished_requests"] += 1
+        self.metrics.finished.append(r.record())
+        self._emit(r, StreamEvent(rid=r.rid, kind="done", finish_reason=reason, t=now), close=True)
+
+    def _emit(self, r: Request, event: StreamEvent, close: bool = False) -> None:
+        sink = self._sinks.pop(r.rid, None) if close else self._sinks.get(r.rid)
+        if sink is None:
+            return
+        try:
+            sink(event)
+        except Exception:
+            # a sink that raises loses its request, not the loop (mercury/engine.py:259-262)
+            self.abort(r.rid)
+
+    # ------------------------------------------------------------------ reporting
+
+    def leaked_pages(self) -> int:
+        return self.cache.leaked_pages()
+
+    def snapshot(self) -> dict:
+        return {"config": self.cfg.to_dict(), "scheduler": self.sched.snapshot(),
+                "cache": {**self.cache.stats, "available": self.cache.num_available(),
+                          "evictions": [p.evictions for p in self.cache.pools]},
+                "engine": self.metrics.summary(), "submitted": self._submitted}

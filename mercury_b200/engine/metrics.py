@@ -1,0 +1,56 @@
+"""Per-step timing rows and counters (mercury/metrics.py:7-20, :36-112)."""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass
+
+
+@dataclass(slots=True)
+class StepRecord:
+    t: float
+    num_entries: int
+    num_decode: int
+    num_tokens: int
+    sched_s: float
+    step_s: float
+    waiting: int
+    running: int
+    free_pages: int
+    preempted: int
+
+
+def percentile(values: list[float], q: float) -> float:
+    if not values:
+        return 0.0
+    ordered = sorted(values)
+    pos = (len(ordered) - 1) * q
+    low = int(pos)
+    high = min(low + 1, len(ordered) - 1)
+    return ordered[low] * (1 - (pos - low)) + ordered[high] * (pos - low)
+
+
+class EngineMetrics:
+    def __init__(self, max_steps: int = 500_000):
+        self.steps: deque[StepRecord] = deque(maxlen=max_steps)
+        self.finished: deque[dict] = deque(maxlen=200_000)
+        self.counters = {"steps": 0, "idle_steps": 0, "step_tokens": 0, "decode_tokens": 0,
+                         "finished_requests": 0, "aborted_requests": 0, "rejected_requests": 0,
+                         "preemptions": 0}
+
+    def add_step(self, record: StepRecord) -> None:
+        self.steps.append(record)
+        self.counters["steps"] += 1
+        self.counters["step_tokens"] += record.num_tokens
+        self.counters["decode_tokens"] += record.num_decode
+        self.counters["preemptions"] += record.preempted
+
+    def summary(self) -> dict:
+        step_s = [s.step_s for s in self.steps]
+        sched_s = [s.sched_s for s in self.steps]
+        total = sum(step_s) or 1e-9
+        return {**self.counters, "wall_seconds": sum(step_s),
+                "mean_step_ms": 1e3 * total / max(1, len(step_s)),
+                "p50_step_ms": 1e3 * percentile(step_s, 0.5),
+                "p99_step_ms": 1e3 * percentile(step_s, 0.99),
+                "sched_share": sum(sched_s) / total}

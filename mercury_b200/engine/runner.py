@@ -190,3 +190,11 @@ class ModelRunner:
         logits = self.run(batch)
         self.finish(entries)
         return logits
+
+
+def kv_bytes_per_token_of(folder, dtype: torch.dtype) -> int:
+    """Cache bytes per token of the model under `folder`, without loading its weights."""
+    entry, config = read_model_config(folder)
+    model = Model(entry.describe(config))
+    elem = torch.finfo(dtype).bits // 8
+    return sum(2 * l.need.num_kv_heads * l.need.head_dim * elem for l in model.cache_layers.values())

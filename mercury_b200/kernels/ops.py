@@ -28,7 +28,14 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 class CudaOps:
-    def __init__(self, device="cuda", decode_splits: int | None = None):
+    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library"):
+        """`gemm` picks the bfloat16 product: "library" (cuBLAS through torch.mm, where the
+        reference calls F.linear) or "simt" (this package's CUDA-core kernel). The float32
+        engine always runs the CUDA-core kernel: a library product would need its
+        reduced-precision mode switched off process-wide to be a true 32-bit product."""
+        if gemm not in ("library", "simt"):
+            raise KernelError(f"unknown gemm choice {gemm!r}")
+        self.gemm = gemm
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
                               "no CPU path")
@@ -41,6 +48,9 @@ class CudaOps:
         self.decode_splits = decode_splits
         self._scratch: torch.Tensor | None = None
         self.launches = 0
+        self.library_calls = 0
+        # split-K partial sums stay float32
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
     # ------------------------------------------------------------------ helpers
 
@@ -84,11 +94,28 @@ class CudaOps:
             raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> "
                               f"{tuple(out.shape)} do not fit")
         self._rows(x), self._rows(weight), self._rows(out)
+        if (self.gemm == "library" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and (bias is None or bias.dtype == torch.bfloat16)):
+            return self._library_linear(x, weight, bias, out)
         check(self.lib.mb_gemm_simt(_ptr(x), _flag(x.dtype), _ptr(weight), _flag(weight.dtype),
                                     _ptr(bias), _flag(bias.dtype) if bias is not None else 0,
                                     _ptr(out), _flag(out.dtype), m, n, k, self._stream()),
               "linear")
         self.launches += 1
+
+    def _library_linear(self, x, weight, bias, out):
+        """bfloat16 operands, float32 accumulation in cuBLAS; the result is rounded once, to
+        bfloat16 or (for logits) kept in float32."""
+        if out.dtype == torch.bfloat16:
+            if bias is None:
+                torch.mm(x, weight.t(), out=out)
+            else:
+                torch.addmm(bias, x, weight.t(), out=out)
+        else:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+            if bias is not None:
+                out.add_(bias.float())
+        self.library_calls += 1
 
     def swiglu(self, gate_up, out):
         check(self.lib.mb_swiglu(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],
