@@ -214,7 +214,7 @@ def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
     produced = []
     for b in range(batch):
         prompt = torch.randint(0, vocab, (context,), generator=gen).tolist()
-        engine.submit(f"e2e-{b}", prompt, steps + warmup + 8, lambda ev: produced.append(ev.kind),
+        engine.submit(f"e2e-{b}", prompt, steps + warmup + batch + 8, lambda ev: produced.append(ev.kind),
                       SamplingParams(ignore_eos=True))
     while any(r.seq_len - r.num_computed != 1 or r.state is not RequestState.RUNNING
               for r in engine.sched.running + engine.sched.waiting) or not engine.sched.running:
@@ -230,7 +230,7 @@ def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
     seconds = time.perf_counter() - t0
     tokens = sum(1 for kind in produced[size_before:] if kind == "token")
     assert tokens == batch * steps, (tokens, batch, steps)
-    lay = runner.buffers._layout(batch, batch, -(-(context + steps + warmup + 8) // BLOCK), batch)
+    lay = runner.buffers._layout(batch, batch, -(-(context + steps + warmup + batch + 8) // BLOCK), batch)
     return tokens / seconds, lay["size"] * 4, batch * 4
 
 
