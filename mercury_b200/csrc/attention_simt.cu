@@ -332,3 +332,46 @@ MB_EXPORT int mb_paged_attention_simt(const void* qkv, int q_row_stride, const v
             part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits);
     return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------
+// The variant for callers that cannot allocate: see no_alloc.h. The partial results of the
+// key splits live in this file-scope array instead of a buffer handed in by the caller.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_static_scratch[MB_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_address[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
+
+MB_EXPORT int mb_paged_attention_static(const void* qkv, int q_row_stride, const void* k_pages,
+                                        const void* v_pages, const int* table, int max_pages,
+                                        const int* q_start, const int* kv_len,
+                                        const int* seq_of_token, void* out, int tokens,
+                                        int num_seqs, int max_q_len, int n_q, int n_kv, int d,
+                                        int page_size, float scale, int window, int num_splits,
+                                        int dtype, void* stream) {
+    if (num_splits < 1) num_splits = 1;
+    if (tokens < 0 || n_q <= 0 || d <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    const long long need = (long long)tokens * n_q * num_splits * (d + 2);
+    if (need > MB_STATIC_SCRATCH_FLOATS) return MB_ERR_SCRATCH;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+        return MB_ERR_LAUNCH;
+    if (g_static_scratch_address[device] == nullptr) {
+        // In host code `g_static_scratch` is only a handle for the symbol; the address the
+        // kernels need comes from the runtime, for the device that is current now.
+        float* address = nullptr;
+        if (cudaGetSymbolAddress((void**)&address, g_static_scratch) != cudaSuccess ||
+            address == nullptr)
+            return MB_ERR_LAUNCH;
+        g_static_scratch_address[device] = address;
+    }
+    // The split kernel writes every (row, split) pair that the merge kernel reads, so the
+    // array needs no clearing between calls. With one split no scratch is touched at all.
+    return mb_paged_attention_simt(qkv, q_row_stride, k_pages, v_pages, table, max_pages, q_start,
+                                   kv_len, seq_of_token, out, g_static_scratch_address[device],
+                                   MB_STATIC_SCRATCH_FLOATS, tokens, num_seqs, max_q_len, n_q, n_kv,
+                                   d, page_size, scale, window, num_splits, dtype, stream);
+}
