@@ -54,6 +54,7 @@ class StepBatch:
     logit_rows: torch.Tensor
     tables: list[torch.Tensor]
     decode_only: bool = False
+    attention_splits: int | None = None   # fixed split of the keys, when a graph needs one
 
 
 class BatchBuffers:
@@ -85,18 +86,23 @@ class BatchBuffers:
         return out
 
     def build(self, entries: list[StepEntry], page_size: int, token_capacity: int | None = None,
-              seq_capacity: int | None = None, page_capacity: int | None = None) -> StepBatch:
+              seq_capacity: int | None = None, page_capacity: int | None = None,
+              row_capacity: int | None = None) -> StepBatch:
         """Fill the host buffer for `entries`, copy it, and return device views. The
         capacities (default: exactly what the entries need) fix the layout, so that a
-        captured graph can be replayed on batches of different content."""
+        captured graph can be replayed on batches of different content. With
+        `row_capacity` the entries' own `want` is set aside and logits are asked for at
+        the first `row_capacity` rows of the batch."""
         num_seqs = len(entries)
         num_tokens = sum(len(e.tokens) for e in entries)
-        rows = sum(len(e.want) for e in entries)
+        rows = 0 if row_capacity is not None else sum(len(e.want) for e in entries)
         pages = max((len(t) for e in entries for t in e.seq.tables), default=1)
         tc = num_tokens if token_capacity is None else token_capacity
         sc = num_seqs if seq_capacity is None else seq_capacity
         pc = max(1, pages) if page_capacity is None else page_capacity
-        rc = max(1, rows)
+        rc = max(1, rows) if row_capacity is None else row_capacity
+        if rows > rc:
+            raise ValueError("more logit rows are wanted than the capacity given")
         if tc > self.max_tokens or sc > self.max_seqs or pc > self.max_pages:
             raise ValueError(
                 f"step of {tc} tokens, {sc} sequences, {pc} pages per sequence exceeds the "
@@ -137,7 +143,7 @@ class BatchBuffers:
             slots[index] = e.seq.slot
             for group, table in enumerate(e.seq.tables):
                 tables[group, index, :len(table)] = table
-            for w in e.want:
+            for w in (e.want if row_capacity is None else ()):
                 if not 0 <= w < n:
                     raise ValueError(f"{e.seq.seq_id}: wanted place {w} is outside its {n} tokens")
                 logit_rows[row] = cursor + w
@@ -145,6 +151,9 @@ class BatchBuffers:
             cursor += n
             max_q = max(max_q, n)
             max_kv = max(max_kv, start + n)
+        if row_capacity is not None:
+            rows = rc
+            logit_rows[:rc] = np.arange(rc, dtype=np.int32)
         q_start[num_seqs:sc + 1] = cursor
         kv_len[num_seqs:] = 0
         slots[num_seqs:] = 0
@@ -162,7 +171,8 @@ class BatchBuffers:
             num_tokens=tc, num_seqs=sc, max_q_len=max_q, max_kv_len=max_kv, num_logit_rows=rows,
             token_ids=dview("token_ids"), positions=dview("positions"),
             seq_of_token=dview("seq_of_token"), q_start=dview("q_start"), kv_len=dview("kv_len"),
-            slots=dview("slots"), logit_rows=dview("logit_rows")[:rows],
+            slots=dview("slots"),
+            logit_rows=dview("logit_rows")[:rows if row_capacity is None else rc],
             tables=[t for t in dview("tables").view(self.num_groups, sc, pc)],
             decode_only=all(len(e.tokens) == 1 for e in entries),
         )

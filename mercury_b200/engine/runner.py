@@ -73,6 +73,7 @@ class ModelRunner:
         ops=None,
         config: ModelConfig | None = None,
         tensors: dict[str, torch.Tensor] | None = None,
+        cuda_graphs: bool = True,
     ):
         """`model` is a folder with config.json and safetensors; or pass `config` and
         `tensors` (a `{name: tensor}` dictionary) directly. `ops` is the kernel set; by
@@ -123,6 +124,10 @@ class ModelRunner:
         self.workspace = Workspace(self.device, dtype, max_step_tokens)
         self.ctx = StepContext(ops, self.workspace, page_size, dtype)
         self.steps = 0
+        self.max_pages = max_pages
+        self.use_graphs = cuda_graphs and self.device.type == "cuda"
+        self._graphs: dict[int, tuple] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ sizes
 
@@ -181,11 +186,61 @@ class ModelRunner:
             self.cache.advance(e.seq, e.seq.num_computed + len(e.tokens), e.hashes)
         self.steps += 1
 
+    # ------------------------------------------------------------------ decode graphs
+
+    def _bucket(self, count: int) -> int:
+        size = 1
+        while size < count:
+            size *= 2
+        return min(size, self.max_seqs)
+
+    def _graph_splits(self, bucket: int) -> int:
+        """How many ways the keys of each sequence are split in a captured decode step: the
+        grid is fixed at capture, so it is sized to fill the device for this many sequences
+        whatever their lengths turn out to be."""
+        kv_heads = max((l.need.num_kv_heads for l in self.model.cache_layers.values()), default=1)
+        sms = getattr(self.ops, "sm_count", 148)
+        return max(1, min(32, -(-2 * sms // max(1, bucket * kv_heads))))
+
+    def _decode_with_graph(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Decode-only steps (one token per entry) replay a CUDA graph captured once per
+        batch-size bucket: the launch sequence is fixed and everything that varies (tokens,
+        positions, block tables, lengths) is read by the kernels from the step's device
+        buffer, whose layout is fixed by the bucket."""
+        bucket = self._bucket(len(entries))
+        wanted = [i for i, e in enumerate(entries) if e.want]
+        capacities = dict(token_capacity=bucket, seq_capacity=bucket, page_capacity=self.max_pages,
+                          row_capacity=bucket)
+        # every row of the bucket gets logits; rows nobody asked for are dropped below
+        batch = self.prepare(entries, **capacities)
+        batch.attention_splits = self._graph_splits(bucket)
+        held = self._graphs.get(bucket)
+        if held is None:
+            self.run(batch)                       # warm-up: allocates buffers, loads kernels
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.run(batch)
+            held = self._graphs[bucket] = (graph, logits)
+        graph, logits = held
+        graph.replay()
+        self.graph_replays += 1
+        self.finish(entries)
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            return logits[:len(entries)]
+        return logits[torch.tensor(wanted, device=self.device)]
+
     @torch.inference_mode()
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run exactly the tokens given, as one batch, from the cache that earlier steps
         left; returns the logits at the wanted places in the order of the entries and of
-        each entry's `want` (None if nothing is wanted)."""
+        each entry's `want` (None if nothing is wanted). The tensor returned is a view of a
+        buffer that the next step overwrites."""
+        if (self.use_graphs and len(entries) <= self.max_seqs
+                and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries)):
+            return self._decode_with_graph(entries)
         batch = self.prepare(entries)
         logits = self.run(batch)
         self.finish(entries)

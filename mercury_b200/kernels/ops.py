@@ -142,6 +142,8 @@ class CudaOps:
     def _splits(self, batch, num_kv_heads, group) -> int:
         """Divide the keys of a decode-like batch over more blocks when the batch alone
         cannot fill the device."""
+        if getattr(batch, "attention_splits", None):
+            return batch.attention_splits
         if self.decode_splits is not None:
             return max(1, self.decode_splits)
         tiles = -(-batch.max_q_len * group // 16)
