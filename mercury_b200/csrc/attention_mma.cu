@@ -1,0 +1,358 @@
+// Paged attention in bfloat16 on the tensor cores (mma.sync m16n8k16), for head sizes 64
+// and 128: the serving path of prompt portions and of decode tokens.
+//
+// Same contract as the CUDA-core kernel in attention_simt.cu (ragged batch, block tables,
+// causal mask by absolute position, optional window, optional split over keys merged by
+// attention_combine_kernel); other head sizes are left to that kernel.
+//
+// The (query token, head of the group) pairs of one sequence and one KV head are laid out
+// as rows, so the query heads that share a KV head also share each key tile. A warp owns
+// 16 rows; a block has NWARPS warps (4 for prompt portions, 1 for decode-like batches,
+// where the split over keys provides the parallelism). Keys are walked in tiles of 64
+// aligned to absolute positions, brought in by 16-byte cp.async copies straight from the
+// pages into a two-stage, XOR-swizzled shared-memory ring. Scores, the running maximum and
+// sum, and the output accumulate in float32; probabilities are rounded to bfloat16 for the
+// P.V product (the usual flash-attention arrangement).
+#include "common.cuh"
+
+namespace mb {
+
+constexpr int MMA_BN = 64;  // keys per tile
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zeroed
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem),
+                 "r"(bytes));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+                     const __nv_bfloat16* __restrict__ k_pages,
+                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ table,
+                     int max_pages, const int* __restrict__ q_start,
+                     const int* __restrict__ kv_len_of, __nv_bfloat16* __restrict__ out,
+                     float* __restrict__ part_acc, float* __restrict__ part_ml, int n_q, int n_kv,
+                     int page_size, float scale, int window, int tiles_per_seq, int num_splits) {
+    constexpr int ROWS = NWARPS * 16;
+    constexpr int CH = D / 8;        // 16-byte chunks per row
+    constexpr int THREADS = NWARPS * 32;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [ROWS][D]
+    __nv_bfloat16* k_s = q_s + ROWS * D;                              // [2][MMA_BN][D]
+    __nv_bfloat16* v_s = k_s + 2 * MMA_BN * D;                        // [2][MMA_BN][D]
+
+    const int seq = blockIdx.x / tiles_per_seq;
+    // later row tiles see more keys: hand them out first
+    const int tile = tiles_per_seq - 1 - (blockIdx.x - seq * tiles_per_seq);
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int group = n_q / n_kv;
+    const int q_begin = q_start[seq];
+    const int q_len = q_start[seq + 1] - q_begin;
+    const int row0 = tile * ROWS;
+    if (row0 >= q_len * group) return;
+    const int kv_len = kv_len_of[seq];
+    const int first_pos = kv_len - q_len;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // ---- queries of this block's rows -> shared (swizzled) -> A fragments
+    for (int idx = tid; idx < ROWS * CH; idx += THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int row = row0 + r;
+        const int tok = row / group, hg = row - tok * group;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (tok < q_len)
+            val = *reinterpret_cast<const uint4*>(qkv + (int64_t)(q_begin + tok) * q_row_stride +
+                                                  (kvh * group + hg) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(qf[ks], q_s + r * D + ((c ^ (r & 7)) * 8));
+    }
+
+    // ---- rows of this thread: g and g + 8 of the warp's 16
+    const int g = lane >> 2, t4 = lane & 3;
+    int pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row0 + warp * 16 + g + h * 8;
+        const int tok = row / group;
+        row_ok[h] = tok < q_len;
+        pos[h] = first_pos + tok;
+    }
+
+    // ---- key tiles of this block
+    const int tok_min = row0 / group;
+    int tok_max = (row0 + ROWS - 1) / group;
+    if (tok_max > q_len - 1) tok_max = q_len - 1;
+    const int p_min = first_pos + tok_min, p_max = first_pos + tok_max;
+    int t_lo = 0;
+    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / MMA_BN;
+    int t_hi = p_max / MMA_BN + 1;
+    if (num_splits > 1) {
+        const int per = (t_hi - t_lo + num_splits - 1) / num_splits;
+        t_lo = t_lo + split * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+
+    auto load_tile = [&](int stage, int kt) {
+        __nv_bfloat16* kd = k_s + stage * MMA_BN * D;
+        __nv_bfloat16* vd = v_s + stage * MMA_BN * D;
+        for (int idx = tid; idx < MMA_BN * CH; idx += THREADS) {
+            const int j = idx / CH, c = idx - j * CH;
+            const int key = kt * MMA_BN + j;
+            int page = -1;
+            if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+            const bool valid = page >= 0;
+            const int64_t at =
+                valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D + c * 8 : 0;
+            const int sw = (c ^ (j & 7)) * 8;
+            cp_async_16(kd + j * D + sw, k_pages + at, valid);
+            cp_async_16(vd + j * D + sw, v_pages + at, valid);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float scale2 = scale * 1.4426950408889634f;  // scores in units of log2(e)
+
+    if (t_lo < t_hi) load_tile(0, t_lo);
+    for (int kt = t_lo; kt < t_hi; ++kt) {
+        const int stage = (kt - t_lo) & 1;
+        if (kt + 1 < t_hi) {
+            load_tile(stage ^ 1, kt + 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        const __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
+        const __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
+
+        // S = Q K^T : 16 rows x 64 keys per warp
+        float s[MMA_BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < MMA_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < MMA_BN / 16; ++n2) {
+                uint32_t b[4];
+                const int j = n2 * 16 + (lane & 7) + (lane >> 4) * 8;
+                const int c = ks * 2 + ((lane >> 3) & 1);
+                ldmatrix_x4(b, kt_s + j * D + ((c ^ (j & 7)) * 8));
+                mma_bf16(s[2 * n2], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * n2 + 1], qf[ks], b[2], b[3]);
+            }
+        }
+
+        // mask, scale, online softmax (float32)
+        float m_new[2] = {m[0], m[1]};
+#pragma unroll
+        for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int key = kt * MMA_BN + nt * 8 + 2 * t4 + (e & 1);
+                bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                if (window > 0) seen = seen && key > pos[h] - window;
+                s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
+                m_new[h] = fmaxf(m_new[h], s[nt][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            corr[h] = m_new[h] > -INFINITY ? exp2f(m[h] - m_new[h]) : 1.f;
+            m[h] = m_new[h];
+            l[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const float p = m[h] > -INFINITY ? exp2f(s[nt][e] - m[h]) : 0.f;
+                s[nt][e] = p;
+                l[h] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < MMA_BN / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int d2 = 0; d2 < D / 16; ++d2) {
+                uint32_t b[4];
+                const int j = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int c = d2 * 2 + (lane >> 4);
+                ldmatrix_x4_trans(b, vt_s + j * D + ((c ^ (j & 7)) * 8));
+                mma_bf16(o[2 * d2], a, b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();  // everyone is done with this stage before it is refilled
+    }
+
+    // ---- finish: per-thread partial sums of l over the quad, then write
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!row_ok[h]) continue;
+        const int row = row0 + warp * 16 + g + h * 8;
+        const int tok = row / group, hg = row - tok * group;
+        const int64_t flat = (int64_t)(q_begin + tok) * n_q + kvh * group + hg;
+        if (num_splits == 1) {
+            const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+                *reinterpret_cast<__nv_bfloat162*>(out + flat * D + i * 8 + 2 * t4) = v;
+            }
+        } else {
+            const int64_t at = flat * num_splits + split;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                float2 v = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+                *reinterpret_cast<float2*>(part_acc + at * D + i * 8 + 2 * t4) = v;
+            }
+            if (t4 == 0) {
+                // the merge kernel works with natural-log maxima
+                part_ml[at * 2] = m[h] * 0.6931471805599453f;
+                part_ml[at * 2 + 1] = l[h];
+            }
+        }
+    }
+}
+
+template <int D, int NWARPS>
+int launch_attention_mma(const void* qkv, int q_row_stride, const void* k_pages, const void* v_pages,
+                         const int* table, int max_pages, const int* q_start, const int* kv_len,
+                         void* out, float* part_acc, float* part_ml, int n_q, int n_kv,
+                         int page_size, float scale, int window, int num_seqs, int max_q_len,
+                         int num_splits, cudaStream_t s) {
+    constexpr int ROWS = NWARPS * 16;
+    const size_t smem = (size_t)(ROWS * D + 4 * MMA_BN * D) * sizeof(__nv_bfloat16);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(attention_mma_kernel<D, NWARPS>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = true;
+    }
+    const int group = n_q / n_kv;
+    const int tiles_per_seq = (max_q_len * group + ROWS - 1) / ROWS;
+    dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
+    typedef __nv_bfloat16 bf;
+    attention_mma_kernel<D, NWARPS><<<grid, NWARPS * 32, smem, s>>>(
+        (const bf*)qkv, q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages,
+        q_start, kv_len, (bf*)out, part_acc, part_ml, n_q, n_kv, page_size, scale, window,
+        tiles_per_seq, num_splits);
+    return launch_status();
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// 1 if this kernel takes the head size (bfloat16 only), else 0: the caller then uses the
+// CUDA-core kernel.
+MB_EXPORT int mb_attention_mma_supports(int d) { return d == 64 || d == 128; }
+
+// Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.
+MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
+                                     const void* v_pages, const int* table, int max_pages,
+                                     const int* q_start, const int* kv_len, const int* seq_of_token,
+                                     void* out, float* scratch, long long scratch_floats, int tokens,
+                                     int num_seqs, int max_q_len, int n_q, int n_kv, int d,
+                                     int page_size, float scale, int window, int num_splits,
+                                     void* stream) {
+    if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
+    if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
+    if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
+    if (q_row_stride % 8) return MB_ERR_ALIGNMENT;
+    if (num_splits < 1) num_splits = 1;
+    if (n_kv > 65535 || num_splits > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    float* part_acc = nullptr;
+    float* part_ml = nullptr;
+    if (num_splits > 1) {
+        const long long need = (long long)tokens * n_q * num_splits * (d + 2);
+        if (!scratch || scratch_floats < need) return MB_ERR_SCRATCH;
+        part_acc = scratch;
+        part_ml = scratch + (int64_t)tokens * n_q * num_splits * d;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int group = n_q / n_kv;
+    const bool small = max_q_len * group <= 16;  // decode-like: one warp of rows per block
+    int rc;
+#define MB_MMA_CASE(DD, NW)                                                                       \
+    rc = launch_attention_mma<DD, NW>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,      \
+                                      q_start, kv_len, out, part_acc, part_ml, n_q, n_kv,         \
+                                      page_size, scale, window, num_seqs, max_q_len, num_splits, s)
+    if (d == 64) {
+        if (small) { MB_MMA_CASE(64, 1); } else { MB_MMA_CASE(64, 4); }
+    } else {
+        if (small) { MB_MMA_CASE(128, 1); } else { MB_MMA_CASE(128, 4); }
+    }
+#undef MB_MMA_CASE
+    if (rc != MB_OK || num_splits == 1) return rc;
+    return launch_attention_combine(part_acc, part_ml, seq_of_token, out, tokens, n_q, d, num_splits,
+                                    MB_BF16, s);
+}

@@ -271,6 +271,24 @@ int dispatch_attention(int nc, const void* qkv, int q_row_stride, const void* k_
     return MB_ERR_UNSUPPORTED_SIZE;
 }
 
+// Launch the merge of `num_splits` partial results per (token, head); shared by every
+// attention kernel that splits keys. dtype: MB_F32 or MB_BF16 output.
+int launch_attention_combine(const float* part_acc, const float* part_ml, const int* seq_of_token,
+                             void* out, int tokens, int n_q, int d, int num_splits, int dtype,
+                             cudaStream_t s) {
+    if (n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(tokens, n_q);
+    if (dtype == MB_F32)
+        attention_combine_kernel<float><<<grid, 64, 0, s>>>(part_acc, part_ml, seq_of_token,
+                                                            (float*)out, n_q, d, num_splits);
+    else if (dtype == MB_BF16)
+        attention_combine_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>(
+            part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -322,15 +340,8 @@ MB_EXPORT int mb_paged_attention_simt(const void* qkv, int q_row_stride, const v
     else
         return MB_ERR_BAD_DTYPE;
     if (rc != MB_OK || num_splits == 1) return rc;
-    dim3 grid(tokens, n_q);
-    if (n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    if (dtype == MB_F32)
-        attention_combine_kernel<float><<<grid, 64, 0, s>>>(part_acc, part_ml, seq_of_token,
-                                                            (float*)out, n_q, d, num_splits);
-    else
-        attention_combine_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>(
-            part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits);
-    return launch_status();
+    return launch_attention_combine(part_acc, part_ml, seq_of_token, out, tokens, n_q, d,
+                                    num_splits, dtype, s);
 }
 
 // ------------------------------------------------------------------------------------------

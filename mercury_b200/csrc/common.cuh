@@ -85,6 +85,11 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// defined in attention_simt.cu
+int launch_attention_combine(const float* part_acc, const float* part_ml, const int* seq_of_token,
+                             void* out, int tokens, int n_q, int d, int num_splits, int dtype,
+                             cudaStream_t s);
+
 inline int launch_status() {
     return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

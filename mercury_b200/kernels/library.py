@@ -41,6 +41,9 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                 c_void_p],
+    "mb_paged_attention_mma": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
@@ -60,6 +63,8 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.mb_attention_mma_supports.argtypes = [c_int]
+    lib.mb_attention_mma_supports.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_attention_scratch_floats.restype = c_longlong
     _LIB = lib

@@ -139,34 +139,48 @@ class CudaOps:
             self._stream()), "rope_cache_write")
         self.launches += 1
 
-    def _splits(self, batch, num_kv_heads, group) -> int:
-        """Divide the keys of a decode-like batch over more blocks when the batch alone
-        cannot fill the device."""
+    def _splits(self, batch, num_kv_heads, group, rows_per_block, keys_per_tile) -> int:
+        """Divide the keys over more blocks when the batch alone cannot fill the device."""
         if getattr(batch, "attention_splits", None):
             return batch.attention_splits
         if self.decode_splits is not None:
             return max(1, self.decode_splits)
-        tiles = -(-batch.max_q_len * group // 16)
+        tiles = -(-batch.max_q_len * group // rows_per_block)
         blocks = batch.num_seqs * tiles * num_kv_heads
-        key_tiles = -(-batch.max_kv_len // 32)
-        if blocks >= self.sm_count or key_tiles < 8:
+        key_tiles = -(-batch.max_kv_len // keys_per_tile)
+        if blocks >= self.sm_count or key_tiles < 4:
             return 1
-        return max(1, min(key_tiles // 4, -(-2 * self.sm_count // blocks), 64))
+        return max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
-                        window, out):
+                        window, out, kernel: str | None = None):
+        """`kernel` forces "mma" or "simt"; by default bfloat16 with a head size the
+        tensor-core kernel takes runs there, everything else on the CUDA cores."""
         group = num_heads // num_kv_heads
-        splits = self._splits(batch, num_kv_heads, group)
         tokens = qkv.shape[0]
+        use_mma = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_mma_supports(head_dim)
+                   and kernel != "simt")
+        if kernel == "mma" and not use_mma:
+            raise KernelError(f"the tensor-core attention takes bfloat16 with head size 64 or "
+                              f"128, not {qkv.dtype} with {head_dim}")
+        if use_mma:
+            small = batch.max_q_len * group <= 16
+            splits = self._splits(batch, num_kv_heads, group, 16, 64) if small else 1
+        else:
+            splits = self._splits(batch, num_kv_heads, group, 16, 32)
         floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
         scratch = self._scratch_for(floats) if floats else None
-        check(self.lib.mb_paged_attention_simt(
-            _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
-            cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
-            _ptr(batch.seq_of_token), _ptr(out), _ptr(scratch),
-            scratch.numel() if scratch is not None else 0, tokens, batch.num_seqs,
-            batch.max_q_len, num_heads, num_kv_heads, head_dim, cache.page_size, float(scale),
-            int(window), splits, _flag(qkv.dtype), self._stream()), "paged_attention")
+        common = (_ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                  cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
+                  _ptr(batch.seq_of_token), _ptr(out), _ptr(scratch),
+                  scratch.numel() if scratch is not None else 0, tokens, batch.num_seqs,
+                  batch.max_q_len, num_heads, num_kv_heads, head_dim, cache.page_size, float(scale),
+                  int(window), splits)
+        if use_mma:
+            check(self.lib.mb_paged_attention_mma(*common, self._stream()), "paged_attention (mma)")
+        else:
+            check(self.lib.mb_paged_attention_simt(*common, _flag(qkv.dtype), self._stream()),
+                  "paged_attention")
         self.launches += 1 if splits == 1 else 2
 
     def argmax(self, logits, out):
