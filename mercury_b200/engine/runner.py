@@ -125,7 +125,7 @@ class ModelRunner:
         self.ctx = StepContext(ops, self.workspace, page_size, dtype)
         self.steps = 0
         self.max_pages = max_pages
-        self.use_graphs = cuda_graphs and self.device.type == "cuda"
+        self.use_graphs = cuda_graphs and self.device.type == "cuda" and self.model.capturable
         self._graphs: dict[int, tuple] = {}
         self.graph_replays = 0
 

@@ -30,6 +30,9 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = OutputHead(spec.vocab_size, spec.hidden_size, spec.head_weight)
         self._plan_caches()
+        self.capturable = all(part.capturable for part in self._parts()) and all(
+            getattr(block.mixer, "position", None) is None or block.mixer.position.capturable
+            for block in self.blocks)
 
     # ------------------------------------------------------------------ layout of caches
 

@@ -16,6 +16,8 @@ from .base import CacheNeed, Mixer, PartSpec, TensorSpec, build_part, register_m
 
 
 class GroupedQueryAttention(Mixer):
+    capturable = True
+
     def __init__(
         self,
         hidden_size: int,

@@ -12,6 +12,7 @@ Interfaces
 Every part:
     tensor_specs() -> list[TensorSpec]        the checkpoint tensors it reads, by full name
     load(tensors, setup)                      take (and pack) them; `setup` is a `PartSetup`
+    capturable                                True if forward() can be recorded in a CUDA graph
 
 Mixer (`register_mixer`):
     cache_need() -> CacheNeed | None          pages of keys and values it wants, if any
@@ -125,6 +126,11 @@ class LayerCache:
 
 
 class Part:
+    # Whether forward() may be recorded into a CUDA graph: it must launch the same kernels
+    # whatever the batch holds and never read device memory from the host. Parts that do
+    # not say so are assumed unsafe, and a model holding one runs without graphs.
+    capturable = False
+
     def tensor_specs(self) -> list[TensorSpec]:
         return []
 

@@ -11,6 +11,8 @@ from .base import Part, TensorSpec
 
 
 class TokenEmbedding(Part):
+    capturable = True
+
     def __init__(self, vocab_size: int, hidden_size: int, weight_name: str):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
@@ -30,6 +32,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    capturable = True
+
     def __init__(self, vocab_size: int, hidden_size: int, weight_name: str | None):
         """`weight_name` None ties the head to the embedding table."""
         self.vocab_size = vocab_size

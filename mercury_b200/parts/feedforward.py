@@ -10,6 +10,8 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 
 class GatedFeedForward(FeedForward):
+    capturable = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str,
                  activation: str = "silu"):
         if activation != "silu":

@@ -13,6 +13,8 @@ from .base import Norm, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, size: int, eps: float, weight_name: str, init_std: float = 0.05):
         self.size = size
         self.eps = eps

@@ -15,6 +15,8 @@ from .base import PositionEncoding, register_position_encoding
 
 
 class RotaryEncoding(PositionEncoding):
+    capturable = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
         self.head_dim = head_dim
         self.theta = float(theta)
@@ -37,6 +39,8 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPositionEncoding(PositionEncoding):
+    capturable = True
+
     def __init__(self, **_ignored):
         pass
 
