@@ -49,6 +49,14 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool v
                  "r"(bytes));
 }
 
+// 2^x by the special-function unit (ex2.approx: relative error about 2^-22, far below the
+// bfloat16 rounding that follows); 2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -115,6 +123,12 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
         row_ok[h] = tok < q_len;
         pos[h] = first_pos + tok;
     }
+
+    // first and last position among the rows of this warp (for whole-tile tests)
+    const int wrow0 = row0 + warp * 16;
+    const bool warp_rows_ok = (wrow0 + 15) / group < q_len;
+    const int warp_pos_min = first_pos + wrow0 / group;
+    const int warp_pos_max = first_pos + (wrow0 + 15) / group;
 
     // ---- key tiles of this block
     const int tok_min = row0 / group;
@@ -184,18 +198,34 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
             }
         }
 
-        // mask, scale, online softmax (float32)
+        // mask, scale, online softmax (float32). A tile that every row of the warp sees
+        // whole (all its keys at or before the warp's first position, inside every window)
+        // needs no per-element test.
         float m_new[2] = {m[0], m[1]};
+        const int tile_first = kt * MMA_BN, tile_last = tile_first + MMA_BN - 1;
+        const bool whole = warp_rows_ok && tile_last <= warp_pos_min && tile_last < kv_len &&
+                           (window <= 0 || tile_first > warp_pos_max - window);
+        if (whole) {
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+            for (int nt = 0; nt < MMA_BN / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int key = kt * MMA_BN + nt * 8 + 2 * t4 + (e & 1);
-                bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
-                if (window > 0) seen = seen && key > pos[h] - window;
-                s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
-                m_new[h] = fmaxf(m_new[h], s[nt][e]);
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= scale2;
+                    m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int key = tile_first + nt * 8 + 2 * t4 + (e & 1);
+                    bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                    if (window > 0) seen = seen && key > pos[h] - window;
+                    s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
+                    m_new[h] = fmaxf(m_new[h], s[nt][e]);
+                }
             }
         }
         float corr[2];
@@ -203,7 +233,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
         for (int h = 0; h < 2; ++h) {
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-            corr[h] = m_new[h] > -INFINITY ? exp2f(m[h] - m_new[h]) : 1.f;
+            corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
             m[h] = m_new[h];
             l[h] *= corr[h];
         }
@@ -212,7 +242,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int h = e >> 1;
-                const float p = m[h] > -INFINITY ? exp2f(s[nt][e] - m[h]) : 0.f;
+                const float p = m[h] > -INFINITY ? fast_exp2(s[nt][e] - m[h]) : 0.f;
                 s[nt][e] = p;
                 l[h] += p;
             }

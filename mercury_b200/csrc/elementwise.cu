@@ -133,6 +133,139 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
     }
 }
 
+// bfloat16, width a multiple of 8: eight features per thread through 16-byte accesses.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
+                                     __nv_bfloat16* __restrict__ out, int tokens, int width) {
+    const int chunks = width / 8;
+    const int64_t total = (int64_t)tokens * chunks;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / chunks;
+        const int c = (int)(i - t * chunks) * 8;
+        const uint4 gq = *reinterpret_cast<const uint4*>(gate_up + t * 2 * width + c);
+        const uint4 uq = *reinterpret_cast<const uint4*>(gate_up + t * 2 * width + width + c);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uq);
+        uint4 oq;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oq);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x,
+                                          g.y / (1.f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * width + c) = oq;
+    }
+}
+
+// bfloat16 activations and weight, hidden a multiple of 4 and at most 4 * ITEMS * threads:
+// each row is read once, kept in registers between the sum of squares and the scaling.
+template <int ITEMS>
+__global__ void add_rmsnorm_bf16_regs_kernel(float* __restrict__ h,
+                                             const __nv_bfloat16* __restrict__ delta,
+                                             const __nv_bfloat16* __restrict__ weight,
+                                             __nv_bfloat16* __restrict__ out,
+                                             const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int64_t src = (int64_t)(rows ? rows[r] : r) * hidden;
+    const int64_t dst = (int64_t)r * hidden;
+    float4 x[ITEMS];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        x[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < hidden) {
+            x[it] = *reinterpret_cast<const float4*>(h + src + c);
+            if (delta) {
+                const uint2 dq = *reinterpret_cast<const uint2*>(delta + src + c);
+                const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dq.x));
+                const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dq.y));
+                x[it].x += d0.x;
+                x[it].y += d0.y;
+                x[it].z += d1.x;
+                x[it].w += d1.y;
+                if (!rows) *reinterpret_cast<float4*>(h + src + c) = x[it];
+            }
+            ss += x[it].x * x[it].x + x[it].y * x[it].y + x[it].z * x[it].z + x[it].w * x[it].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        if (c < hidden) {
+            const uint2 wq = *reinterpret_cast<const uint2*>(weight + c);
+            const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.x));
+            const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.y));
+            uint2 oq;
+            *reinterpret_cast<__nv_bfloat162*>(&oq.x) =
+                __floats2bfloat162_rn(x[it].x * rstd * w0.x, x[it].y * rstd * w0.y);
+            *reinterpret_cast<__nv_bfloat162*>(&oq.y) =
+                __floats2bfloat162_rn(x[it].z * rstd * w1.x, x[it].w * rstd * w1.y);
+            *reinterpret_cast<uint2*>(out + dst + c) = oq;
+        }
+    }
+}
+
+// bfloat16, the whole head rotated, head size a multiple of 8: two pairs per thread
+// through 4-byte accesses, values copied in 16-byte pieces.
+__global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
+                                       const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ table, int max_pages,
+                                       __nv_bfloat16* __restrict__ k_pages,
+                                       __nv_bfloat16* __restrict__ v_pages, int n_q, int n_kv, int d,
+                                       int page_size, int store) {
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    if (seq < 0) return;
+    const int pos = positions[t];
+    const int half = d / 2, pairs2 = half / 2;
+    const int64_t row = (int64_t)t * (n_q + 2 * n_kv) * d;
+    int64_t slot = -1;
+    if (store) {
+        const int page = table[(int64_t)seq * max_pages + pos / page_size];
+        if (page >= 0) slot = (int64_t)page * n_kv * page_size + pos % page_size;
+    }
+    for (int w = threadIdx.x; w < (n_q + n_kv) * pairs2; w += blockDim.x) {
+        const int head = w / pairs2;
+        const int i = (w - head * pairs2) * 2;
+        __nv_bfloat16* x = qkv + row + (int64_t)head * d;
+        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
+        float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i + half));
+        if (cos_t) {
+            const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)pos * half + i);
+            const float2 sn = *reinterpret_cast<const float2*>(sin_t + (int64_t)pos * half + i);
+            const float2 ra = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+            const float2 rb = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+            a = ra;
+            b = rb;
+        }
+        const __nv_bfloat162 ta = __floats2bfloat162_rn(a.x, a.y), tb = __floats2bfloat162_rn(b.x, b.y);
+        *reinterpret_cast<__nv_bfloat162*>(x + i) = ta;
+        *reinterpret_cast<__nv_bfloat162*>(x + i + half) = tb;
+        if (head >= n_q && slot >= 0) {
+            __nv_bfloat16* dst = k_pages + (slot + (int64_t)(head - n_q) * page_size) * d;
+            *reinterpret_cast<__nv_bfloat162*>(dst + i) = ta;
+            *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = tb;
+        }
+    }
+    if (slot >= 0) {
+        const __nv_bfloat16* v = qkv + row + (int64_t)(n_q + n_kv) * d;
+        const int chunks = d / 8;
+        for (int w = threadIdx.x; w < n_kv * chunks; w += blockDim.x) {
+            const int head = w / chunks, c = (w - head * chunks) * 8;
+            *reinterpret_cast<uint4*>(v_pages + (slot + (int64_t)head * page_size) * d + c) =
+                *reinterpret_cast<const uint4*>(v + head * d + c);
+        }
+    }
+}
+
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, int64_t n) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -161,7 +294,18 @@ MB_EXPORT int mb_add_rmsnorm(float* h, const void* delta, const void* weight, in
     if (dtype == MB_F32)
         add_rmsnorm_kernel<float><<<count, threads, 0, s>>>(
             h, (const float*)delta, weight, weight_dtype, (float*)out, rows, hidden, eps);
-    else if (dtype == MB_BF16)
+    else if (dtype == MB_BF16 && weight_dtype == MB_BF16 && hidden % 4 == 0 && hidden <= 8192) {
+        typedef __nv_bfloat16 bf;
+        if (hidden <= 1024)
+            add_rmsnorm_bf16_regs_kernel<2><<<count, 128, 0, s>>>(
+                h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
+        else if (hidden <= 4096)
+            add_rmsnorm_bf16_regs_kernel<4><<<count, 256, 0, s>>>(
+                h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
+        else
+            add_rmsnorm_bf16_regs_kernel<8><<<count, 256, 0, s>>>(
+                h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
+    } else if (dtype == MB_BF16)
         add_rmsnorm_kernel<__nv_bfloat16><<<count, threads, 0, s>>>(
             h, (const __nv_bfloat16*)delta, weight, weight_dtype, (__nv_bfloat16*)out, rows, hidden,
             eps);
@@ -178,7 +322,12 @@ MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int tokens, int width, i
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
         swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, total, width);
-    else if (dtype == MB_BF16)
+    else if (dtype == MB_BF16 && width % 8 == 0) {
+        const int64_t work = total / 8;
+        const int grid = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+        swiglu_bf16x8_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up,
+                                                  (__nv_bfloat16*)out, tokens, width);
+    } else if (dtype == MB_BF16)
         swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total, width);
     else
@@ -197,6 +346,11 @@ MB_EXPORT int mb_rope_store(void* qkv, const float* cos_t, const float* sin_t, i
         rope_store_kernel<float><<<tokens, 256, 0, s>>>(
             (float*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (float*)k_pages, (float*)v_pages, n_q, n_kv, d, page_size, store);
+    else if (dtype == MB_BF16 && d % 8 == 0 && (rot == d || rot == 0))
+        rope_store_bf16_kernel<<<tokens, 256, 0, s>>>(
+            (__nv_bfloat16*)qkv, rot ? cos_t : nullptr, sin_t, positions, seq_of_token, table,
+            max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_q, n_kv, d, page_size,
+            store);
     else if (dtype == MB_BF16)
         rope_store_kernel<__nv_bfloat16><<<tokens, 256, 0, s>>>(
             (__nv_bfloat16*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
