@@ -1,0 +1,376 @@
+// Products with few rows of activations (decode steps): out[t, n] = sum_k x[t, k] w[n, k],
+// for up to 64 tokens, bfloat16 operands, float32 accumulation, on the tensor cores
+// (mma.sync m16n8k16) with the roles swapped: 16 weight rows are the M side of the MMA and
+// 8 tokens its N side, so that no tensor-core work is wasted on padding tokens.
+//
+// Such a product is bound by the time to stream the weight matrix once from HBM, and for
+// the small matrices of a layer by latency, so the kernel is laid out to have every byte
+// of the matrix in flight at once: a warp owns 16 weight rows over a share of K and reads
+// them with 16-byte loads straight into MMA fragments (the k order inside a 32-wide chunk
+// is permuted identically for weights and activations, which leaves dot products
+// unchanged); the activations are small and come through L1. Warps that split K meet in
+// shared memory, where the epilogue runs:
+//   plain    (+ bias) -> bfloat16 or float32 rows            (o-proj, down-proj, LM head)
+//   swiglu   silu(gate) * up for paired gate/up row tiles    (mercury/model/qwen2.py:42)
+//   rope     bias, rotary encoding of q and k, q written back, k and v stored into the
+//            token's cache page (mercury/model/rope.py:11-17, mercury/model/attention.py:35-45)
+// Sizes it takes: K a multiple of 32, N a multiple of 16, at most 64 tokens; the callers
+// fall back to the general kernels otherwise.
+#include "common.cuh"
+
+namespace mb {
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One warp: rows [n0, n0+16) of w against tokens [0, 8*NT) of x over chunks [c_begin, c_end)
+// of 32 k each. acc[nt] holds (row g, tokens 2t, 2t+1) and (row g+8, tokens 2t, 2t+1).
+// Loads are issued four chunks ahead of their use, so a warp whose share of K is four
+// chunks or fewer pays one trip to memory.
+template <int NT>
+__device__ __forceinline__ void skinny_mainloop(const __nv_bfloat16* __restrict__ x,
+                                                const __nv_bfloat16* __restrict__ w, int n0, int T,
+                                                int K, int c_begin, int c_end, float (&acc)[NT][4]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const __nv_bfloat16* wa = w + (int64_t)(n0 + g) * K + 8 * t4;
+    const __nv_bfloat16* wb = w + (int64_t)(n0 + g + 8) * K + 8 * t4;
+    const __nv_bfloat16* xr[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        int tok = nt * 8 + g;
+        if (tok > T - 1) tok = T - 1;  // padding tokens read a real row; their columns are dropped
+        xr[nt] = x + (int64_t)tok * K + 8 * t4;
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int c0 = c_begin; c0 < c_end; c0 += 4) {
+        uint4 a[4], b[4], xv[4][NT];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + j;
+            const bool ok = c < c_end;
+            a[j] = ok ? __ldg(reinterpret_cast<const uint4*>(wa + c * 32)) : zero;
+            b[j] = ok ? __ldg(reinterpret_cast<const uint4*>(wb + c * 32)) : zero;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                xv[j][nt] = ok ? *reinterpret_cast<const uint4*>(xr[nt] + c * 32) : zero;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma_bf16_16816(acc[nt], a[j].x, b[j].x, a[j].y, b[j].y, xv[j][nt].x, xv[j][nt].y);
+                mma_bf16_16816(acc[nt], a[j].z, b[j].z, a[j].w, b[j].w, xv[j][nt].z, xv[j][nt].w);
+            }
+        }
+    }
+}
+
+// Every warp leaves its 16 x (8 NT) partial tile in shared memory: red[warp][row][token].
+template <int NT>
+__device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT][4]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t4 = lane & 3;
+    float* mine = red + warp * 16 * (8 * NT);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        mine[g * (8 * NT) + nt * 8 + 2 * t4] = acc[nt][0];
+        mine[g * (8 * NT) + nt * 8 + 2 * t4 + 1] = acc[nt][1];
+        mine[(g + 8) * (8 * NT) + nt * 8 + 2 * t4] = acc[nt][2];
+        mine[(g + 8) * (8 * NT) + nt * 8 + 2 * t4 + 1] = acc[nt][3];
+    }
+}
+
+// A block holds `rowt` row tiles of 16 weight rows, each shared by `ksplit` warps that
+// split K between them (rowt * ksplit warps in all, warp = tile * ksplit + share).
+// EPI: 0 = bfloat16 out, 1 = float32 out, 2 = swiglu (bfloat16 out; the row tiles of a
+// block alternate gate / up, and `half_n` is the width of the result).
+template <int NT, int EPI>
+__global__ void __launch_bounds__(1024) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ bias, void* __restrict__ out,
+                                   int T, int N, int K, int half_n, int rowt, int ksplit) {
+    constexpr int TOK = 8 * NT;
+    extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
+    const int warp = threadIdx.x >> 5;
+    const int rt = warp / ksplit, ks = warp - rt * ksplit;
+    int n0;  // first weight row of this warp's tile
+    if (EPI == 2) {
+        const int pair = blockIdx.x * (rowt / 2) + rt / 2;
+        n0 = (rt & 1) * half_n + pair * 16;
+    } else {
+        n0 = (blockIdx.x * rowt + rt) * 16;
+    }
+    const int limit = EPI == 2 ? ((rt & 1) + 1) * half_n : N;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    if (n0 < limit) {
+        const int chunks = K / 32;
+        const int per = (chunks + ksplit - 1) / ksplit;
+        const int c_begin = ks * per;
+        const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
+        skinny_mainloop<NT>(x, w, n0, T, K, c_begin, c_end, acc);
+    }
+    store_partial<NT>(red, acc);
+    __syncthreads();
+
+    if (EPI == 2) {
+        // element (pair tile p, row r, token): silu(gate) * up
+        for (int idx = threadIdx.x; idx < (rowt / 2) * 16 * TOK; idx += blockDim.x) {
+            const int r = idx % 16, tok = (idx / 16) % TOK, p = idx / (16 * TOK);
+            const int n = (blockIdx.x * (rowt / 2) + p) * 16 + r;
+            if (tok >= T || n >= half_n) continue;
+            float gate = 0.f, up = 0.f;
+            for (int k = 0; k < ksplit; ++k) {
+                gate += red[((2 * p) * ksplit + k) * 16 * TOK + r * TOK + tok];
+                up += red[((2 * p + 1) * ksplit + k) * 16 * TOK + r * TOK + tok];
+            }
+            // the separate kernels round gate and up to bfloat16 between product and gate
+            gate = __bfloat162float(__float2bfloat16_rn(gate));
+            up = __bfloat162float(__float2bfloat16_rn(up));
+            reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * half_n + n] =
+                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < rowt * 16 * TOK; idx += blockDim.x) {
+            const int r = idx % 16, tok = (idx / 16) % TOK, tile = idx / (16 * TOK);
+            const int n = (blockIdx.x * rowt + tile) * 16 + r;
+            if (tok >= T || n >= N) continue;
+            float v = 0.f;
+            for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
+            if (bias) v += __bfloat162float(bias[n]);
+            if (EPI == 0)
+                reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+            else
+                reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+        }
+    }
+}
+
+// One block per head of the packed q/k/v projection: D/16 row tiles, each shared by
+// `ksplit` warps. After the product: bias, rotation of q and k heads (pairs i, i + D/2),
+// q written to the qkv buffer, k and v written to the token's slot of the cache page.
+// Where each token goes (position, page) is looked up before the product starts, so that
+// those loads overlap the weight stream.
+template <int NT, int D>
+__global__ void __launch_bounds__(1024) skinny_qkv_rope_kernel(const __nv_bfloat16* __restrict__ x,
+                                       const __nv_bfloat16* __restrict__ w,
+                                       const __nv_bfloat16* __restrict__ bias,
+                                       __nv_bfloat16* __restrict__ qkv,
+                                       const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ table, int max_pages,
+                                       __nv_bfloat16* __restrict__ k_pages,
+                                       __nv_bfloat16* __restrict__ v_pages, int T, int K, int n_q,
+                                       int n_kv, int page_size, int store, int ksplit) {
+    constexpr int ROWT = D / 16;
+    constexpr int TOK = 8 * NT;
+    extern __shared__ float red[];          // [ROWT * ksplit][16][TOK]
+    float* val = red + ROWT * ksplit * 16 * TOK;  // [TOK][D]
+    __shared__ int tok_pos[TOK];
+    __shared__ int tok_page[TOK];           // -2: padding token, -1: no page
+    const int head = blockIdx.x;  // 0..n_q-1 q heads, then k heads, then v heads
+    if (threadIdx.x < TOK) {
+        const int tok = threadIdx.x;
+        int pos = 0, page = -2;
+        if (tok < T) {
+            const int seq = seq_of_token[tok];
+            if (seq >= 0) {
+                pos = positions[tok];
+                page = (store && head >= n_q) ? table[(int64_t)seq * max_pages + pos / page_size] : -1;
+            }
+        }
+        tok_pos[tok] = pos;
+        tok_page[tok] = page;
+    }
+    const int warp = threadIdx.x >> 5;
+    const int rt = warp / ksplit, ks = warp - rt * ksplit;
+    const int n0 = head * D + rt * 16;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const int chunks = K / 32;
+    const int per = (chunks + ksplit - 1) / ksplit;
+    const int c_begin = ks * per;
+    const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
+    skinny_mainloop<NT>(x, w, n0, T, K, c_begin, c_end, acc);
+    store_partial<NT>(red, acc);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < D * TOK; idx += blockDim.x) {
+        const int r = idx % D, tok = idx / D;
+        const int tile = r / 16, rr = r % 16;
+        float v = 0.f;
+        for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + rr * TOK + tok];
+        if (bias) v += __bfloat162float(bias[head * D + r]);
+        // the separate kernels round the projection to bfloat16 before rotating it
+        val[tok * D + r] = __bfloat162float(__float2bfloat16_rn(v));
+    }
+    __syncthreads();
+    const int total_heads = n_q + 2 * n_kv;
+    const bool is_v = head >= n_q + n_kv;
+    const bool is_k = head >= n_q && !is_v;
+    for (int idx = threadIdx.x; idx < (D / 2) * TOK; idx += blockDim.x) {
+        const int i = idx % (D / 2), tok = idx / (D / 2);
+        const int page = tok_page[tok];
+        if (page == -2) continue;
+        const int pos = tok_pos[tok];
+        float a = val[tok * D + i], b = val[tok * D + i + D / 2];
+        if (!is_v && cos_t) {
+            const float c = cos_t[(int64_t)pos * (D / 2) + i], s = sin_t[(int64_t)pos * (D / 2) + i];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+        }
+        const __nv_bfloat16 ta = __float2bfloat16_rn(a), tb = __float2bfloat16_rn(b);
+        if (!is_k && !is_v) {
+            __nv_bfloat16* q = qkv + (int64_t)tok * total_heads * D + head * D;
+            q[i] = ta;
+            q[i + D / 2] = tb;
+        } else if (page >= 0) {
+            const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+            __nv_bfloat16* dst = (is_k ? k_pages : v_pages) +
+                                 (((int64_t)page * n_kv + kvh) * page_size + pos % page_size) * D;
+            dst[i] = ta;
+            dst[i + D / 2] = tb;
+        }
+    }
+}
+
+// How many warps share the K of one row tile: enough that no warp walks more than about
+// four chunks while the device is not yet full, never fewer than two chunks per warp.
+static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
+    int want = (148 * 32) / (tiles > 0 ? tiles : 1);
+    if (want > max_ksplit) want = max_ksplit;
+    if (want > chunks / 2) want = chunks / 2;
+    return want < 1 ? 1 : want;
+}
+
+// Dynamic shared memory beyond 48 KB has to be asked for once per kernel (and again only
+// when a larger amount is needed).
+template <typename KernelT>
+static int raise_smem(KernelT kernel, size_t bytes) {
+    static size_t raised = 48 * 1024;  // one per kernel instantiation
+    if (bytes <= raised) return MB_OK;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
+        cudaSuccess)
+        return MB_ERR_UNSUPPORTED_SIZE;
+    raised = bytes;
+    return MB_OK;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// At most 16 tokens: beyond that the activations no longer come cheaply through L1 and the
+// library product (or a tensor-core tile kernel) is the better tool.
+MB_EXPORT int mb_gemm_skinny_supports(int T, int N, int K) {
+    return T >= 1 && T <= 16 && K > 0 && K % 32 == 0 && N > 0 && N % 16 == 0;
+}
+
+#define MB_SK_NT_SWITCH(NTV, ...)                            \
+    if (NTV <= 1) { constexpr int NT = 1; __VA_ARGS__ }        \
+    else { constexpr int NT = 2; __VA_ARGS__ }
+
+// out dtype MB_BF16 or MB_F32; bias may be null.
+MB_EXPORT int mb_gemm_skinny(const void* x, const void* w, const void* bias, void* out,
+                             int out_dtype, int T, int N, int K, void* stream) {
+    if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
+    typedef __nv_bfloat16 bf;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = (T + 7) / 8;
+    const int tiles = N / 16;
+    const int ksplit = pick_ksplit(tiles, K / 32, 32);
+    const int rowt = ksplit >= 8 ? 1 : 8 / ksplit;
+    const int blocks = (tiles + rowt - 1) / rowt;
+    const int threads = rowt * ksplit * 32;
+    int rc = MB_OK;
+    MB_SK_NT_SWITCH(nt, {
+        const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
+        if (out_dtype == MB_BF16) {
+            rc = raise_smem(skinny_gemm_kernel<NT, 0>, smem);
+            if (rc == MB_OK)
+                skinny_gemm_kernel<NT, 0><<<blocks, threads, smem, s>>>(
+                    (const bf*)x, (const bf*)w, (const bf*)bias, out, T, N, K, 0, rowt, ksplit);
+        } else {
+            rc = raise_smem(skinny_gemm_kernel<NT, 1>, smem);
+            if (rc == MB_OK)
+                skinny_gemm_kernel<NT, 1><<<blocks, threads, smem, s>>>(
+                    (const bf*)x, (const bf*)w, (const bf*)bias, out, T, N, K, 0, rowt, ksplit);
+        }
+    })
+    return rc != MB_OK ? rc : launch_status();
+}
+
+// w: [2 * width, K] with the gate rows first; out: [T, width] bfloat16.
+MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const void* w, void* out, int T, int width, int K,
+                                    void* stream) {
+    if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
+    typedef __nv_bfloat16 bf;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = (T + 7) / 8;
+    const int pairs = width / 16;
+    const int ksplit = pick_ksplit(2 * pairs, K / 32, 16);
+    const int pairs_per_block = ksplit >= 4 ? 1 : 4 / ksplit;
+    const int rowt = 2 * pairs_per_block;
+    const int blocks = (pairs + pairs_per_block - 1) / pairs_per_block;
+    const int threads = rowt * ksplit * 32;
+    int rc = MB_OK;
+    MB_SK_NT_SWITCH(nt, {
+        const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
+        rc = raise_smem(skinny_gemm_kernel<NT, 2>, smem);
+        if (rc == MB_OK)
+            skinny_gemm_kernel<NT, 2><<<blocks, threads, smem, s>>>(
+                (const bf*)x, (const bf*)w, nullptr, out, T, 2 * width, K, width, rowt, ksplit);
+    })
+    return rc != MB_OK ? rc : launch_status();
+}
+
+MB_EXPORT int mb_gemm_skinny_qkv_supports(int T, int K, int d, int rot) {
+    return T >= 1 && T <= 16 && K > 0 && K % 32 == 0 && (d == 64 || d == 128) && (rot == d || rot == 0);
+}
+
+// The packed q/k/v projection of a few tokens with bias, rotation and cache store fused.
+MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const void* w, const void* bias, void* qkv,
+                                      const float* cos_t, const float* sin_t, int rot,
+                                      const int* positions, const int* seq_of_token,
+                                      const int* table, int max_pages, void* k_pages, void* v_pages,
+                                      int T, int K, int n_q, int n_kv, int d, int page_size,
+                                      int store, void* stream) {
+    if (!mb_gemm_skinny_qkv_supports(T, K, d, rot)) return MB_ERR_UNSUPPORTED_SIZE;
+    typedef __nv_bfloat16 bf;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = (T + 7) / 8;
+    const int heads = n_q + 2 * n_kv;
+    const int rowt = d / 16;
+    const int ksplit = pick_ksplit(heads * rowt, K / 32, 32 / rowt);
+    const int threads = rowt * ksplit * 32;
+    const float* c = rot ? cos_t : nullptr;
+    int rc = MB_OK;
+    MB_SK_NT_SWITCH(nt, {
+        const size_t smem = ((size_t)rowt * ksplit * 16 + d) * 8 * NT * sizeof(float);
+        if (d == 64) {
+            rc = raise_smem(skinny_qkv_rope_kernel<NT, 64>, smem);
+            if (rc == MB_OK)
+                skinny_qkv_rope_kernel<NT, 64><<<heads, threads, smem, s>>>(
+                    (const bf*)x, (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions,
+                    seq_of_token, table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv,
+                    page_size, store, ksplit);
+        } else {
+            rc = raise_smem(skinny_qkv_rope_kernel<NT, 128>, smem);
+            if (rc == MB_OK)
+                skinny_qkv_rope_kernel<NT, 128><<<heads, threads, smem, s>>>(
+                    (const bf*)x, (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions,
+                    seq_of_token, table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv,
+                    page_size, store, ksplit);
+        }
+    })
+    return rc != MB_OK ? rc : launch_status();
+}

@@ -44,6 +44,11 @@ _SIGNATURES = {
     "mb_paged_attention_mma": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "mb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_gemm_skinny_qkv_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
@@ -63,6 +68,10 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.mb_gemm_skinny_supports.argtypes = [c_int, c_int, c_int]
+    lib.mb_gemm_skinny_supports.restype = c_int
+    lib.mb_gemm_skinny_qkv_supports.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mb_gemm_skinny_qkv_supports.restype = c_int
     lib.mb_attention_mma_supports.argtypes = [c_int]
     lib.mb_attention_mma_supports.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]

@@ -36,6 +36,7 @@ class CudaOps:
         if gemm not in ("library", "simt"):
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
+        self.skinny = True     # few-token products go to the weight-streaming kernels
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
                               "no CPU path")
@@ -94,8 +95,15 @@ class CudaOps:
             raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> "
                               f"{tuple(out.shape)} do not fit")
         self._rows(x), self._rows(weight), self._rows(out)
-        if (self.gemm == "library" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-                and (bias is None or bias.dtype == torch.bfloat16)):
+        all_bf16 = (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                    and (bias is None or bias.dtype == torch.bfloat16))
+        if all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k):
+            check(self.lib.mb_gemm_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out),
+                                          _flag(out.dtype), m, n, k, self._stream()),
+                  "linear (skinny)")
+            self.launches += 1
+            return
+        if self.gemm == "library" and all_bf16:
             return self._library_linear(x, weight, bias, out)
         check(self.lib.mb_gemm_simt(_ptr(x), _flag(x.dtype), _ptr(weight), _flag(weight.dtype),
                                     _ptr(bias), _flag(bias.dtype) if bias is not None else 0,
@@ -116,6 +124,43 @@ class CudaOps:
             if bias is not None:
                 out.add_(bias.float())
         self.library_calls += 1
+
+    def linear_swiglu(self, x, weight, out, ctx):
+        """out = silu(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]: one kernel
+        for few tokens, product then gate otherwise."""
+        m, k = x.shape
+        width = out.shape[1]
+        if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and self.lib.mb_gemm_skinny_supports(m, width, k)):
+            check(self.lib.mb_gemm_skinny_swiglu(_ptr(x), _ptr(weight), _ptr(out), m, width, k,
+                                                 self._stream()), "linear_swiglu (skinny)")
+            self.launches += 1
+            return
+        gate_up = ctx.buffer("gate_up", m, 2 * width)
+        self.linear(x, weight, None, gate_up)
+        self.swiglu(gate_up, out)
+
+    def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
+                       batch, cache):
+        """The packed q/k/v projection with bias, then rotation of q and k and the store of
+        k and v into the cache pages: one kernel for few tokens, two otherwise."""
+        m, k = x.shape
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
+                and cache.k.dtype == torch.bfloat16
+                and self.lib.mb_gemm_skinny_qkv_supports(m, k, head_dim, rot)):
+            check(self.lib.mb_gemm_skinny_qkv_rope(
+                _ptr(x), _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
+                _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table),
+                cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), m, k, num_heads, num_kv_heads,
+                head_dim, cache.page_size, int(cache.write), self._stream()),
+                "qkv_rope_store (skinny)")
+            self.launches += 1
+            return
+        self.linear(x, weight, bias, qkv)
+        self.rope_cache_write(qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache)
 
     def swiglu(self, gate_up, out):
         check(self.lib.mb_swiglu(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from .base import CacheNeed, Mixer, PartSpec, TensorSpec, build_part, register_mixer
+from .rotary import NoPositionEncoding
 
 
 class GroupedQueryAttention(Mixer):
@@ -88,13 +89,16 @@ class GroupedQueryAttention(Mixer):
         tokens = x.shape[0]
         ops = ctx.ops
         qkv = ctx.buffer("qkv", tokens, self.q_size + 2 * self.kv_size)
-        ops.linear(x, self.qkv_weight, self.qkv_b, qkv)
         tables = self.position.rotary_tables()
-        if tables is None:
+        if tables is not None or isinstance(self.position, NoPositionEncoding):
+            # projection, bias, rotation and the store into the pages, fused where it pays
+            ops.qkv_rope_store(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads,
+                               self.num_kv_heads, self.head_dim, tables, ctx.batch, cache)
+        else:
+            ops.linear(x, self.qkv_weight, self.qkv_b, qkv)
             self.position.apply(qkv, (self.num_heads, self.num_kv_heads, self.head_dim), ctx)
-        ops.rope_cache_write(
-            qkv, self.num_heads, self.num_kv_heads, self.head_dim, tables, ctx.batch, cache
-        )
+            ops.rope_cache_write(qkv, self.num_heads, self.num_kv_heads, self.head_dim, None,
+                                 ctx.batch, cache)
         attended = ctx.buffer("attended", tokens, self.q_size)
         ops.paged_attention(
             qkv, self.num_heads, self.num_kv_heads, self.head_dim, ctx.batch, cache,

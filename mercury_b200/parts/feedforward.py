@@ -39,10 +39,8 @@ class GatedFeedForward(FeedForward):
 
     def forward(self, x, ctx):
         tokens = x.shape[0]
-        gate_up = ctx.buffer("gate_up", tokens, 2 * self.intermediate_size)
-        ctx.ops.linear(x, self.gate_up_weight, None, gate_up)
         act = ctx.buffer("ff_act", tokens, self.intermediate_size)
-        ctx.ops.swiglu(gate_up, act)
+        ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx)
         out = ctx.buffer("ff_out", tokens, self.hidden_size)
         ctx.ops.linear(act, self.down_weight, None, out)
         return out

@@ -43,6 +43,16 @@ class TorchOps:
             y = y + bias.to(self.acc)
         out.copy_(y.to(out.dtype))
 
+    def linear_swiglu(self, x, weight, out, ctx=None):
+        gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        self.linear(x, weight, None, gate_up)
+        self.swiglu(gate_up, out)
+
+    def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
+                       batch, cache):
+        self.linear(x, weight, bias, qkv)
+        self.rope_cache_write(qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache)
+
     def swiglu(self, gate_up, out):
         width = out.shape[-1]
         gate = gate_up[:, :width].to(self.acc)

@@ -100,7 +100,10 @@ def test_add_rmsnorm_zero_row(ops):
 # ------------------------------------------------------------------------------ products
 
 @pytest.mark.parametrize("m,n,k", [(1, 151, 70), (5, 130, 896), (77, 1152, 96), (130, 64, 4864),
-                                   (64, 64, 16), (3, 1000, 1)])
+                                   (64, 64, 16), (3, 1000, 1),
+                                   # few tokens, K % 32 == 0, N % 16 == 0: the skinny kernels
+                                   (1, 1152, 896), (8, 896, 4864), (16, 9728, 896), (33, 9728, 896),
+                                   (9, 4112, 320), (13, 48, 96), (2, 151936, 64), (3, 896, 64)])
 @pytest.mark.parametrize("x_dtype,w_dtype,o_dtype", [
     (torch.float32, torch.float32, torch.float32),
     (torch.bfloat16, torch.bfloat16, torch.bfloat16),
@@ -116,6 +119,55 @@ def test_linear(ops, twin, m, n, k, x_dtype, w_dtype, o_dtype):
     ops.linear(x, w, bias, got)
     twin.linear(x, w, bias, want)
     close(got, want, o_dtype, terms=k)
+
+
+@pytest.mark.parametrize("m,width,k", [(1, 4864, 896), (8, 128, 64), (12, 336, 96), (16, 4864, 896),
+                                       (70, 320, 96), (5, 200, 80), (3, 48, 4864)])
+def test_linear_swiglu(ops, twin, m, width, k):
+    """Few tokens take the fused kernel, the others the product followed by the gate."""
+    x = rand((m, k), torch.bfloat16, 21)
+    w = rand((2 * width, k), torch.bfloat16, 22, 0.1)
+    got = torch.empty((m, width), dtype=torch.bfloat16, device="cuda")
+    want = torch.empty_like(got)
+    ctx = SimpleNamespace(buffer=lambda name, rows, cols, dtype=None: torch.empty(
+        (rows, cols), dtype=torch.bfloat16, device="cuda"))
+    ops.linear_swiglu(x, w, got, ctx)
+    twin.linear_swiglu(x, w, want)
+    # gate and up are rounded to bfloat16 before the gate, then the result once more
+    err = float((got.double() - want.double()).abs().max() / want.double().abs().max())
+    assert err <= 3 * 2.0 ** -8, err
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,hidden", [(14, 2, 64, 16, 896), (12, 2, 128, 16, 1536),
+                                                    (3, 1, 64, 8, 96), (4, 4, 128, 32, 64)])
+@pytest.mark.parametrize("q_lens,kv_lens", [((1, 1, 1), (40, 17, 300)), ((1,) * 9, tuple(range(5, 50, 5))),
+                                            ((20, 1, 2), (20, 64, 33))])
+def test_qkv_rope_store_fused(ops, twin, n_q, n_kv, d, page, hidden, q_lens, kv_lens):
+    num_pages = sum(-(-kv // page) for kv in kv_lens) + 4
+    batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=2, seed=3)
+    k, v = fill_cache(batch, table, kv_lens, q_lens, n_kv, d, page, num_pages, torch.bfloat16, 4, True)
+    tokens = batch.num_tokens
+    x = rand((tokens, hidden), torch.bfloat16, 23)
+    w = rand(((n_q + 2 * n_kv) * d, hidden), torch.bfloat16, 24, 0.1)
+    bias = rand(((n_q + 2 * n_kv) * d,), torch.bfloat16, 25)
+    angles = torch.rand((max(kv_lens) + 1, d // 2), generator=torch.Generator().manual_seed(5)) * 6
+    tables = (angles.cos().cuda(), angles.sin().cuda())
+    qkv = torch.zeros((tokens, (n_q + 2 * n_kv) * d), dtype=torch.bfloat16, device="cuda")
+    qkv_twin = qkv.clone()
+    k_twin, v_twin = k.clone(), v.clone()
+    ops.qkv_rope_store(x, w, bias, qkv, n_q, n_kv, d, tables, batch, LayerCache(k, v, page, table, True))
+    twin.qkv_rope_store(x, w, bias, qkv_twin, n_q, n_kv, d, tables, batch,
+                        LayerCache(k_twin, v_twin, page, table, True))
+    live = batch.seq_of_token >= 0
+    q_got, q_want = qkv[live][:, :n_q * d], qkv_twin[live][:, :n_q * d]
+    # the projection is rounded to bfloat16, rotated, and rounded again
+    tol = 3 * 2.0 ** -8
+    assert float((q_got.double() - q_want.double()).abs().max() / q_want.double().abs().max()) <= tol
+    assert torch.equal(torch.isnan(k), torch.isnan(k_twin)), "keys stored in the wrong slots"
+    assert torch.equal(torch.isnan(v), torch.isnan(v_twin))
+    for got, want in ((k, k_twin), (v, v_twin)):
+        got, want = torch.nan_to_num(got).double(), torch.nan_to_num(want).double()
+        assert float((got - want).abs().max() / want.abs().max()) <= tol
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
