@@ -311,6 +311,327 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
     }
 }
 
+// Decode-like batches: at most 16 rows per (sequence, KV head), so one m16 tile of queries.
+// The four warps of a block share each 64-key tile, 16 keys per warp, and merge their
+// running (max, sum, output) through shared memory at the end; with one warp alone the
+// kernel is bound by the latency of its own instruction stream. When `counters` is given,
+// the block that finishes last among the splits of a (sequence, KV head) merges them and
+// writes the output itself, which saves the separate merge launch; the merge walks the
+// splits in index order, so the result does not depend on which block came last.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+                        const __nv_bfloat16* __restrict__ k_pages,
+                        const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ table,
+                        int max_pages, const int* __restrict__ q_start,
+                        const int* __restrict__ kv_len_of, __nv_bfloat16* __restrict__ out,
+                        float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        int* __restrict__ counters, int n_q, int n_kv, int page_size, float scale,
+                        int window, int num_splits) {
+    constexpr int CH = D / 8;
+    constexpr int STAGES = 3;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][D]
+    __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
+    __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
+    float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][D], after the loop
+    __shared__ float ml_red[4][16][2];
+    __shared__ int last_flag;
+
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int group = n_q / n_kv;
+    const int q_begin = q_start[seq];
+    const int q_len = q_start[seq + 1] - q_begin;
+    if (q_len <= 0) return;
+    const int rows = q_len * group;          // <= 16
+    const int kv_len = kv_len_of[seq];
+    const int first_pos = kv_len - q_len;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int tok = r / group, hg = r - tok * group;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r < rows)
+            val = *reinterpret_cast<const uint4*>(qkv + (int64_t)(q_begin + tok) * q_row_stride +
+                                                  (kvh * group + hg) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
+    }
+
+    int pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        row_ok[h] = r < rows;
+        pos[h] = first_pos + r / group;
+    }
+    const int p_min = first_pos, p_max = kv_len - 1;
+    int t_lo = 0;
+    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / MMA_BN;
+    int t_hi = p_max / MMA_BN + 1;
+    if (num_splits > 1) {
+        const int per = (t_hi - t_lo + num_splits - 1) / num_splits;
+        t_lo = t_lo + split * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+
+    // each thread copies half a key row of K and of V: one table lookup per tile
+    const int lj = tid >> 1, lc0 = (tid & 1) * (CH / 2);
+    auto load_tile = [&](int stage, int kt) {
+        const int key = kt * MMA_BN + lj;
+        int page = -1;
+        if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+        const bool valid = page >= 0;
+        const int64_t at =
+            valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
+        __nv_bfloat16* kd = k_s + (stage * MMA_BN + lj) * D;
+        __nv_bfloat16* vd = v_s + (stage * MMA_BN + lj) * D;
+#pragma unroll
+        for (int c = 0; c < CH / 2; ++c) {
+            const int sw = ((lc0 + c) ^ (lj & 7)) * 8;
+            cp_async_16(kd + sw, k_pages + at + (lc0 + c) * 8, valid);
+            cp_async_16(vd + sw, v_pages + at + (lc0 + c) * 8, valid);
+        }
+    };
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float scale2 = scale * 1.4426950408889634f;
+
+    // prologue: STAGES - 1 tiles in flight (empty groups keep the accounting uniform)
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (t_lo + st < t_hi) load_tile(st, t_lo + st);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(qf[ks], q_s + r * D + ((c ^ (r & 7)) * 8));
+    }
+
+    for (int kt = t_lo; kt < t_hi; ++kt) {
+        const int it = kt - t_lo;
+        const int stage = it % STAGES;
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+        __syncthreads();   // tile kt has landed for everyone; tile kt-1's stage is free
+        if (kt + STAGES - 1 < t_hi) load_tile((it + STAGES - 1) % STAGES, kt + STAGES - 1);
+        asm volatile("cp.async.commit_group;\n" ::);
+        const __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
+        const __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
+
+        // this warp's 16 keys of the tile
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t b[4];
+            const int j = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+            const int c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, kt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        float m_new[2] = {m[0], m[1]};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int key = kt * MMA_BN + warp * 16 + nt * 8 + 2 * t4 + (e & 1);
+                bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                if (window > 0) seen = seen && key > pos[h] - window;
+                s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
+                m_new[h] = fmaxf(m_new[h], s[nt][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
+            m[h] = m_new[h];
+            l[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const float p = m[h] > -INFINITY ? fast_exp2(s[nt][e] - m[h]) : 0.f;
+                s[nt][e] = p;
+                l[h] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+        uint32_t a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2) {
+            uint32_t b[4];
+            const int j = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int c = d2 * 2 + (lane >> 4);
+            ldmatrix_x4_trans(b, vt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(o[2 * d2], a, b[0], b[1]);
+            mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();   // every warp is done with the key tiles: their memory becomes o_red
+
+    // ---- merge the four warps (each saw a quarter of the keys)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        if (t4 == 0) {
+            ml_red[warp][g + h * 8][0] = m[h];
+            ml_red[warp][g + h * 8][1] = l[h];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
+        const float mine = m[h] > -INFINITY ? fast_exp2(m[h] - big) : 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            float2 v = make_float2(o[i][2 * h] * mine, o[i][2 * h + 1] * mine);
+            *reinterpret_cast<float2*>(o_red + (warp * 16 + r) * D + i * 8 + 2 * t4) = v;
+        }
+    }
+    __syncthreads();
+    // 128 threads: thread -> (row = tid / 8, 8 threads across D)
+    {
+        const int r = tid >> 3;
+        const int tok = r / group, hg = r - tok * group;
+        const int64_t flat = (int64_t)(q_begin + tok) * n_q + kvh * group + hg;
+        float big = -INFINITY, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (ml_red[w][r][0] > -INFINITY) sum += ml_red[w][r][1] * fast_exp2(ml_red[w][r][0] - big);
+        if (r < rows) {
+            for (int c = (tid & 7); c < D; c += 8) {
+                const float v = o_red[(0 * 16 + r) * D + c] + o_red[(1 * 16 + r) * D + c] +
+                                o_red[(2 * 16 + r) * D + c] + o_red[(3 * 16 + r) * D + c];
+                if (num_splits == 1)
+                    out[flat * D + c] = __float2bfloat16_rn(sum > 0.f ? v / sum : 0.f);
+                else
+                    part_acc[(flat * num_splits + split) * D + c] = v;
+            }
+            if (num_splits > 1 && (tid & 7) == 0) {
+                part_ml[(flat * num_splits + split) * 2] = big * 0.6931471805599453f;
+                part_ml[(flat * num_splits + split) * 2 + 1] = sum;
+            }
+        }
+    }
+    if (num_splits == 1 || counters == nullptr) return;
+
+    // ---- the last block of this (sequence, KV head) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int ticket = atomicAdd(&counters[seq * n_kv + kvh], 1);
+        last_flag = ticket == num_splits - 1;
+        if (last_flag) counters[seq * n_kv + kvh] = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    // weights of the splits per row, then the weighted sum with independent loads
+    float* wz = o_red;                      // [16][64] reuses the tile memory once more
+    const int r = tid >> 3, j = tid & 7;
+    const int tok = r / group, hg = r - tok * group;
+    const int64_t flat = (int64_t)(q_begin + (r < rows ? tok : 0)) * n_q + kvh * group +
+                         (r < rows ? hg : 0);
+    __syncthreads();                        // o_red is no longer read by anyone
+    for (int z = j; z < num_splits; z += 8)
+        wz[r * 64 + z] = __ldcg(part_ml + (flat * num_splits + z) * 2);
+    __syncthreads();
+    float big = -INFINITY;
+    for (int z = 0; z < num_splits; ++z) big = fmaxf(big, wz[r * 64 + z]);
+    __syncthreads();
+    for (int z = j; z < num_splits; z += 8) {
+        const float mz = wz[r * 64 + z];
+        const float lz = __ldcg(part_ml + (flat * num_splits + z) * 2 + 1);
+        wz[r * 64 + z] = mz > -INFINITY ? expf(mz - big) : 0.f;
+        wz[16 * 64 + r * 64 + z] = mz > -INFINITY ? lz * expf(mz - big) : 0.f;
+    }
+    __syncthreads();
+    if (r >= rows) return;
+    float denom = 0.f;
+    for (int z = 0; z < num_splits; ++z) denom += wz[16 * 64 + r * 64 + z];
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    // thread j of a row owns columns [j * D/8, (j + 1) * D/8)
+    constexpr int COLS = D / 8;
+    float acc[COLS];
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) acc[c] = 0.f;
+#pragma unroll 4
+    for (int z = 0; z < num_splits; ++z) {
+        const float w = wz[r * 64 + z];
+        const float4* src =
+            reinterpret_cast<const float4*>(part_acc + (flat * num_splits + z) * D + j * COLS);
+#pragma unroll
+        for (int c4 = 0; c4 < COLS / 4; ++c4) {
+            const float4 v = __ldcg(src + c4);
+            acc[4 * c4] += w * v.x;
+            acc[4 * c4 + 1] += w * v.y;
+            acc[4 * c4 + 2] += w * v.z;
+            acc[4 * c4 + 3] += w * v.w;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < COLS; c += 2)
+        *reinterpret_cast<__nv_bfloat162*>(out + flat * D + j * COLS + c) =
+            __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+}
+
+template <int D>
+int launch_attention_decode(const void* qkv, int q_row_stride, const void* k_pages,
+                            const void* v_pages, const int* table, int max_pages, const int* q_start,
+                            const int* kv_len, void* out, float* part_acc, float* part_ml,
+                            int* counters, int n_q, int n_kv, int page_size, float scale, int window,
+                            int num_seqs, int num_splits, cudaStream_t s) {
+    const size_t smem = (size_t)(16 * D + 2 * 3 * MMA_BN * D) * sizeof(__nv_bfloat16);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(attention_decode_kernel<D>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = true;
+    }
+    dim3 grid(num_seqs, n_kv, num_splits);
+    typedef __nv_bfloat16 bf;
+    attention_decode_kernel<D><<<grid, 128, smem, s>>>(
+        (const bf*)qkv, q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages,
+        q_start, kv_len, (bf*)out, part_acc, part_ml, counters, n_q, n_kv, page_size, scale, window,
+        num_splits);
+    return launch_status();
+}
+
 template <int D, int NWARPS>
 int launch_attention_mma(const void* qkv, int q_row_stride, const void* k_pages, const void* v_pages,
                          const int* table, int max_pages, const int* q_start, const int* kv_len,
@@ -353,7 +674,9 @@ MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const vo
                                      void* out, float* scratch, long long scratch_floats, int tokens,
                                      int num_seqs, int max_q_len, int n_q, int n_kv, int d,
                                      int page_size, float scale, int window, int num_splits,
-                                     void* stream) {
+                                     int* counters, void* stream) {
+    // counters: num_seqs * n_kv zeroed ints (left zeroed) to let the last split block merge
+    // in the same launch; null selects the separate merge kernel.
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
@@ -372,14 +695,29 @@ MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const vo
     const int group = n_q / n_kv;
     const bool small = max_q_len * group <= 16;  // decode-like: one warp of rows per block
     int rc;
+    if (small) {
+        if (num_splits > 64) counters = nullptr;   // the in-kernel merge holds 64 splits
+        if (d == 64)
+            rc = launch_attention_decode<64>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                             q_start, kv_len, out, part_acc, part_ml, counters, n_q,
+                                             n_kv, page_size, scale, window, num_seqs, num_splits, s);
+        else
+            rc = launch_attention_decode<128>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                              q_start, kv_len, out, part_acc, part_ml, counters, n_q,
+                                              n_kv, page_size, scale, window, num_seqs, num_splits,
+                                              s);
+        if (rc != MB_OK || num_splits == 1 || counters != nullptr) return rc;
+        return launch_attention_combine(part_acc, part_ml, seq_of_token, out, tokens, n_q, d,
+                                        num_splits, MB_BF16, s);
+    }
 #define MB_MMA_CASE(DD, NW)                                                                       \
     rc = launch_attention_mma<DD, NW>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,      \
                                       q_start, kv_len, out, part_acc, part_ml, n_q, n_kv,         \
                                       page_size, scale, window, num_seqs, max_q_len, num_splits, s)
     if (d == 64) {
-        if (small) { MB_MMA_CASE(64, 1); } else { MB_MMA_CASE(64, 4); }
+        MB_MMA_CASE(64, 4);
     } else {
-        if (small) { MB_MMA_CASE(128, 1); } else { MB_MMA_CASE(128, 4); }
+        MB_MMA_CASE(128, 4);
     }
 #undef MB_MMA_CASE
     if (rc != MB_OK || num_splits == 1) return rc;

@@ -48,6 +48,7 @@ class CudaOps:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_splits = decode_splits
         self._scratch: torch.Tensor | None = None
+        self._counters: torch.Tensor | None = None   # zeroed tickets of the in-kernel split merge
         self.launches = 0
         self.library_calls = 0
         # split-K partial sums stay float32
@@ -222,7 +223,17 @@ class CudaOps:
                   batch.max_q_len, num_heads, num_kv_heads, head_dim, cache.page_size, float(scale),
                   int(window), splits)
         if use_mma:
-            check(self.lib.mb_paged_attention_mma(*common, self._stream()), "paged_attention (mma)")
+            counters = None
+            if splits > 1 and small:
+                need = batch.num_seqs * num_kv_heads
+                if self._counters is None or self._counters.numel() < need:
+                    self._counters = torch.zeros(max(need, 4096), dtype=torch.int32,
+                                                 device=self.device)
+                counters = self._counters
+            check(self.lib.mb_paged_attention_mma(*common, _ptr(counters), self._stream()),
+                  "paged_attention (mma)")
+            self.launches += 1 if (splits == 1 or counters is not None) else 2
+            return
         else:
             check(self.lib.mb_paged_attention_simt(*common, _flag(qkv.dtype), self._stream()),
                   "paged_attention")
