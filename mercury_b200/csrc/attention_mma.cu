@@ -71,6 +71,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                      const int* __restrict__ kv_len_of, __nv_bfloat16* __restrict__ out,
                      float* __restrict__ part_acc, float* __restrict__ part_ml, int n_q, int n_kv,
                      int page_size, float scale, int window, int tiles_per_seq, int num_splits) {
+    grid_dependency_sync();
     constexpr int ROWS = NWARPS * 16;
     constexpr int CH = D / 8;        // 16-byte chunks per row
     constexpr int THREADS = NWARPS * 32;
@@ -328,6 +329,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         int* __restrict__ counters, int n_q, int n_kv, int page_size, float scale,
                         int window, int num_splits) {
+    grid_dependency_sync();
     constexpr int CH = D / 8;
     constexpr int STAGES = 3;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -625,7 +627,7 @@ int launch_attention_decode(const void* qkv, int q_row_stride, const void* k_pag
     }
     dim3 grid(num_seqs, n_kv, num_splits);
     typedef __nv_bfloat16 bf;
-    attention_decode_kernel<D><<<grid, 128, smem, s>>>(
+    MB_LAUNCH((attention_decode_kernel<D>), grid, 128, smem, s, 
         (const bf*)qkv, q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages,
         q_start, kv_len, (bf*)out, part_acc, part_ml, counters, n_q, n_kv, page_size, scale, window,
         num_splits);
@@ -652,7 +654,7 @@ int launch_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
     const int tiles_per_seq = (max_q_len * group + ROWS - 1) / ROWS;
     dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
     typedef __nv_bfloat16 bf;
-    attention_mma_kernel<D, NWARPS><<<grid, NWARPS * 32, smem, s>>>(
+    MB_LAUNCH((attention_mma_kernel<D, NWARPS>), grid, NWARPS * 32, smem, s, 
         (const bf*)qkv, q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages,
         q_start, kv_len, (bf*)out, part_acc, part_ml, n_q, n_kv, page_size, scale, window,
         tiles_per_seq, num_splits);

@@ -34,6 +34,7 @@ paged_attention_kernel(const T* __restrict__ qkv, int q_row_stride, const T* __r
                        T* __restrict__ out, float* __restrict__ part_acc,
                        float* __restrict__ part_ml, int n_q, int n_kv, int d, int page_size,
                        float scale, int window, int tiles_per_seq, int num_splits) {
+    grid_dependency_sync();
     extern __shared__ float smem[];
     const int seq = blockIdx.x / tiles_per_seq;
     const int tile = blockIdx.x - seq * tiles_per_seq;
@@ -197,6 +198,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml,
                                          const int* __restrict__ seq_of_token, T* __restrict__ out,
                                          int n_q, int d, int num_splits) {
+    grid_dependency_sync();
     const int tok = blockIdx.x, head = blockIdx.y;
     const int64_t flat = (int64_t)tok * n_q + head;
     if (seq_of_token[tok] < 0) {
@@ -238,7 +240,7 @@ int launch_attention(const void* qkv, int q_row_stride, const void* k_pages, con
         raised = true;
     }
     dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
-    paged_attention_kernel<T, NC><<<grid, ATT_WARPS * 32, smem, s>>>(
+    MB_LAUNCH((paged_attention_kernel<T, NC>), grid, ATT_WARPS * 32, smem, s, 
         (const T*)qkv, q_row_stride, (const T*)k_pages, (const T*)v_pages, table, max_pages, q_start,
         kv_len, (T*)out, part_acc, part_ml, n_q, n_kv, d, page_size, scale, window, tiles_per_seq,
         num_splits);
@@ -279,10 +281,10 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, const 
     if (n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(tokens, n_q);
     if (dtype == MB_F32)
-        attention_combine_kernel<float><<<grid, 64, 0, s>>>(part_acc, part_ml, seq_of_token,
+        MB_LAUNCH((attention_combine_kernel<float>), grid, 64, 0, s, part_acc, part_ml, seq_of_token,
                                                             (float*)out, n_q, d, num_splits);
     else if (dtype == MB_BF16)
-        attention_combine_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>(
+        MB_LAUNCH((attention_combine_kernel<__nv_bfloat16>), grid, 64, 0, s, 
             part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits);
     else
         return MB_ERR_BAD_DTYPE;

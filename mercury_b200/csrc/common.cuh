@@ -90,6 +90,45 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, const 
                              void* out, int tokens, int n_q, int d, int num_splits, int dtype,
                              cudaStream_t s);
 
+// ---- programmatic dependent launch -----------------------------------------------------
+// Every kernel of this library starts with grid_dependency_sync(): when the launch carries
+// the programmatic-serialization attribute, the kernel may be scheduled while its
+// predecessor in the stream is still draining, and this call is where it waits for the
+// predecessor's memory to be complete; without the attribute it does nothing. Right after
+// it the kernel lets its own successor be scheduled. This hides most of the launch latency
+// between the many small kernels of a decode step.
+__device__ __forceinline__ void grid_dependency_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// set by mb_set_dependent_launch (elementwise.cu)
+extern int g_dependent_launch;
+
+inline cudaLaunchConfig_t launch_config(dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    static cudaLaunchAttribute attribute = [] {
+        cudaLaunchAttribute a = {};
+        a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        a.val.programmaticStreamSerializationAllowed = 1;
+        return a;
+    }();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    config.attrs = &attribute;
+    config.numAttrs = g_dependent_launch ? 1 : 0;
+    return config;
+}
+
+// MB_LAUNCH((kernel<T>), grid, block, smem, stream, args...)
+#define MB_LAUNCH(kernel, grid, block, smem, stream, ...)                              \
+    do {                                                                               \
+        cudaLaunchConfig_t config_ = mb::launch_config(grid, block, smem, stream);     \
+        cudaLaunchKernelEx(&config_, kernel, __VA_ARGS__);                             \
+    } while (0)
+
 inline int launch_status() {
     return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

@@ -12,6 +12,7 @@ namespace mb {
 // mercury/model/qwen2.py:109 (nn.Embedding, no scaling).
 __global__ void embed_kernel(const int* __restrict__ ids, const void* __restrict__ table,
                              int table_dtype, float* __restrict__ out, int hidden, int vocab) {
+    grid_dependency_sync();
     const int t = blockIdx.x;
     int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -30,6 +31,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    const void* __restrict__ weight, int weight_dtype,
                                    T* __restrict__ out, const int* __restrict__ rows,
                                    int hidden, float eps) {
+    grid_dependency_sync();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int64_t src = (int64_t)(rows ? rows[r] : r) * hidden;
@@ -58,6 +60,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t total,
                               int width) {
+    grid_dependency_sync();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / width;
@@ -84,6 +87,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
                                   const int* __restrict__ table, int max_pages,
                                   T* __restrict__ k_pages, T* __restrict__ v_pages,
                                   int n_q, int n_kv, int d, int page_size, int store) {
+    grid_dependency_sync();
     const int t = blockIdx.x;
     const int seq = seq_of_token[t];
     if (seq < 0) return;
@@ -136,6 +140,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
 // bfloat16, width a multiple of 8: eight features per thread through 16-byte accesses.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
                                      __nv_bfloat16* __restrict__ out, int tokens, int width) {
+    grid_dependency_sync();
     const int chunks = width / 8;
     const int64_t total = (int64_t)tokens * chunks;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -166,6 +171,7 @@ __global__ void add_rmsnorm_bf16_regs_kernel(float* __restrict__ h,
                                              const __nv_bfloat16* __restrict__ weight,
                                              __nv_bfloat16* __restrict__ out,
                                              const int* __restrict__ rows, int hidden, float eps) {
+    grid_dependency_sync();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int64_t src = (int64_t)(rows ? rows[r] : r) * hidden;
@@ -221,6 +227,7 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
                                        __nv_bfloat16* __restrict__ k_pages,
                                        __nv_bfloat16* __restrict__ v_pages, int n_q, int n_kv, int d,
                                        int page_size, int store) {
+    grid_dependency_sync();
     const int t = blockIdx.x;
     const int seq = seq_of_token[t];
     if (seq < 0) return;
@@ -268,6 +275,7 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
 
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, int64_t n) {
+    grid_dependency_sync();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (int64_t)gridDim.x * blockDim.x)
         out[i] = from_float<TO>(to_float(in[i]));
@@ -275,12 +283,19 @@ __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, 
 
 }  // namespace mb
 
+namespace mb {
+int g_dependent_launch = 0;
+}
+
 using namespace mb;
+
+// 1: launch every kernel with the programmatic-serialization attribute (see common.cuh).
+MB_EXPORT void mb_set_dependent_launch(int enabled) { g_dependent_launch = enabled ? 1 : 0; }
 
 MB_EXPORT int mb_embed(const int* ids, const void* table, int table_dtype, float* out, int tokens,
                        int hidden, int vocab, void* stream) {
     if (tokens <= 0) return MB_OK;
-    embed_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(ids, table, table_dtype, out, hidden,
+    MB_LAUNCH((embed_kernel), tokens, 256, 0, (cudaStream_t)stream, ids, table, table_dtype, out, hidden,
                                                             vocab);
     return launch_status();
 }
@@ -292,21 +307,21 @@ MB_EXPORT int mb_add_rmsnorm(float* h, const void* delta, const void* weight, in
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
-        add_rmsnorm_kernel<float><<<count, threads, 0, s>>>(
+        MB_LAUNCH((add_rmsnorm_kernel<float>), count, threads, 0, s, 
             h, (const float*)delta, weight, weight_dtype, (float*)out, rows, hidden, eps);
     else if (dtype == MB_BF16 && weight_dtype == MB_BF16 && hidden % 4 == 0 && hidden <= 8192) {
         typedef __nv_bfloat16 bf;
         if (hidden <= 1024)
-            add_rmsnorm_bf16_regs_kernel<2><<<count, 128, 0, s>>>(
+            MB_LAUNCH((add_rmsnorm_bf16_regs_kernel<2>), count, 128, 0, s, 
                 h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
         else if (hidden <= 4096)
-            add_rmsnorm_bf16_regs_kernel<4><<<count, 256, 0, s>>>(
+            MB_LAUNCH((add_rmsnorm_bf16_regs_kernel<4>), count, 256, 0, s, 
                 h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
         else
-            add_rmsnorm_bf16_regs_kernel<8><<<count, 256, 0, s>>>(
+            MB_LAUNCH((add_rmsnorm_bf16_regs_kernel<8>), count, 256, 0, s, 
                 h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
     } else if (dtype == MB_BF16)
-        add_rmsnorm_kernel<__nv_bfloat16><<<count, threads, 0, s>>>(
+        MB_LAUNCH((add_rmsnorm_kernel<__nv_bfloat16>), count, threads, 0, s, 
             h, (const __nv_bfloat16*)delta, weight, weight_dtype, (__nv_bfloat16*)out, rows, hidden,
             eps);
     else
@@ -321,14 +336,14 @@ MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int tokens, int width, i
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, total, width);
+        MB_LAUNCH((swiglu_kernel<float>), blocks, 256, 0, s, (const float*)gate_up, (float*)out, total, width);
     else if (dtype == MB_BF16 && width % 8 == 0) {
         const int64_t work = total / 8;
         const int grid = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
-        swiglu_bf16x8_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up,
+        MB_LAUNCH((swiglu_bf16x8_kernel), grid, 256, 0, s, (const __nv_bfloat16*)gate_up,
                                                   (__nv_bfloat16*)out, tokens, width);
     } else if (dtype == MB_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
+        MB_LAUNCH((swiglu_kernel<__nv_bfloat16>), blocks, 256, 0, s, 
             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total, width);
     else
         return MB_ERR_BAD_DTYPE;
@@ -343,16 +358,16 @@ MB_EXPORT int mb_rope_store(void* qkv, const float* cos_t, const float* sin_t, i
     if (rot < 0 || rot > d || (rot & 1)) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
-        rope_store_kernel<float><<<tokens, 256, 0, s>>>(
+        MB_LAUNCH((rope_store_kernel<float>), tokens, 256, 0, s, 
             (float*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (float*)k_pages, (float*)v_pages, n_q, n_kv, d, page_size, store);
     else if (dtype == MB_BF16 && d % 8 == 0 && (rot == d || rot == 0))
-        rope_store_bf16_kernel<<<tokens, 256, 0, s>>>(
+        MB_LAUNCH((rope_store_bf16_kernel), tokens, 256, 0, s, 
             (__nv_bfloat16*)qkv, rot ? cos_t : nullptr, sin_t, positions, seq_of_token, table,
             max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_q, n_kv, d, page_size,
             store);
     else if (dtype == MB_BF16)
-        rope_store_kernel<__nv_bfloat16><<<tokens, 256, 0, s>>>(
+        MB_LAUNCH((rope_store_kernel<__nv_bfloat16>), tokens, 256, 0, s, 
             (__nv_bfloat16*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_q, n_kv, d, page_size, store);
     else
@@ -366,9 +381,9 @@ MB_EXPORT int mb_convert(const void* in, int in_dtype, void* out, int out_dtype,
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == MB_BF16 && out_dtype == MB_F32)
-        convert_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)in, (float*)out, (int64_t)n);
+        MB_LAUNCH((convert_kernel<__nv_bfloat16, float>), blocks, 256, 0, s, (const __nv_bfloat16*)in, (float*)out, (int64_t)n);
     else if (in_dtype == MB_F32 && out_dtype == MB_BF16)
-        convert_kernel<<<blocks, 256, 0, s>>>((const float*)in, (__nv_bfloat16*)out, (int64_t)n);
+        MB_LAUNCH((convert_kernel<float, __nv_bfloat16>), blocks, 256, 0, s, (const float*)in, (__nv_bfloat16*)out, (int64_t)n);
     else
         return MB_ERR_BAD_DTYPE;
     return launch_status();

@@ -18,6 +18,7 @@ template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void* __restrict__ bias,
                  int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
+    grid_dependency_sync();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -69,7 +70,7 @@ int launch_gemm(const void* x, const void* w, const void* bias, int bias_dtype, 
                 int N, int K, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    gemm_simt_kernel<TX, TW, TO><<<grid, 256, 0, s>>>((const TX*)x, (const TW*)w, bias, bias_dtype,
+    MB_LAUNCH((gemm_simt_kernel<TX, TW, TO>), grid, 256, 0, s, (const TX*)x, (const TW*)w, bias, bias_dtype,
                                                      (TO*)out, M, N, K);
     return launch_status();
 }

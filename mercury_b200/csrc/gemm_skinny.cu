@@ -10,10 +10,16 @@
 // is permuted identically for weights and activations, which leaves dot products
 // unchanged); the activations are small and come through L1. Warps that split K meet in
 // shared memory, where the epilogue runs:
-//   plain    (+ bias) -> bfloat16 or float32 rows            (o-proj, down-proj, LM head)
+//   plain    (+ bias) -> bfloat16 or float32 rows            (LM head)
+//   residual (+ bias) added into the float32 residual stream (o-proj, down-proj), each
+//            element by the one thread that owns it
 //   swiglu   silu(gate) * up for paired gate/up row tiles    (mercury/model/qwen2.py:42)
 //   rope     bias, rotary encoding of q and k, q written back, k and v stored into the
 //            token's cache page (mercury/model/rope.py:11-17, mercury/model/attention.py:35-45)
+// The activations may also be given as the float32 residual stream plus an RMSNorm weight:
+// then every block first computes the rows' 1/rms itself (the stream is a few KB) and
+// builds the normalised bfloat16 activations on the fly, which saves the norm's own launch
+// (mercury/model/qwen2.py:29-31 for the formula).
 // Sizes it takes: K a multiple of 32, N a multiple of 16, at most 64 tokens; the callers
 // fall back to the general kernels otherwise.
 #include "common.cuh"
@@ -29,23 +35,60 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One warp: rows [n0, n0+16) of w against tokens [0, 8*NT) of x over chunks [c_begin, c_end)
+// Where the activations of a product come from: bfloat16 rows `x`, or (norm_w != null) the
+// float32 stream `h` to be normalised with `norm_w`; `rows` optionally picks the rows.
+struct SkinnyInput {
+    const __nv_bfloat16* x;
+    const float* h;
+    const __nv_bfloat16* norm_w;
+    const int* rows;
+    float eps;
+};
+
+// 1/rms of each of the T rows of the stream, by the whole block, into rstd_s[T].
+__device__ __forceinline__ void skinny_row_rstd(const SkinnyInput& in, int T, int K, float* rstd_s) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int tok = warp; tok < T; tok += warps) {
+        const float* row = in.h + (int64_t)(in.rows ? in.rows[tok] : tok) * K;
+        float ss = 0.f;
+        for (int k = lane * 4; k < K; k += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(row + k);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) rstd_s[tok] = rsqrtf(ss / (float)K + in.eps);
+    }
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One warp: rows [n0, n0+16) of w against tokens [0, 8*NT) over chunks [c_begin, c_end)
 // of 32 k each. acc[nt] holds (row g, tokens 2t, 2t+1) and (row g+8, tokens 2t, 2t+1).
 // Loads are issued four chunks ahead of their use, so a warp whose share of K is four
 // chunks or fewer pays one trip to memory.
-template <int NT>
-__device__ __forceinline__ void skinny_mainloop(const __nv_bfloat16* __restrict__ x,
+template <int NT, bool NORM>
+__device__ __forceinline__ void skinny_mainloop(const SkinnyInput& in, const float* rstd_s,
                                                 const __nv_bfloat16* __restrict__ w, int n0, int T,
                                                 int K, int c_begin, int c_end, float (&acc)[NT][4]) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const __nv_bfloat16* wa = w + (int64_t)(n0 + g) * K + 8 * t4;
     const __nv_bfloat16* wb = w + (int64_t)(n0 + g + 8) * K + 8 * t4;
     const __nv_bfloat16* xr[NT];
+    const float* hr[NT];
+    float rs[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         int tok = nt * 8 + g;
         if (tok > T - 1) tok = T - 1;  // padding tokens read a real row; their columns are dropped
-        xr[nt] = x + (int64_t)tok * K + 8 * t4;
+        if (NORM) {
+            hr[nt] = in.h + (int64_t)(in.rows ? in.rows[tok] : tok) * K + 8 * t4;
+            rs[nt] = rstd_s[tok];
+        } else {
+            xr[nt] = in.x + (int64_t)tok * K + 8 * t4;
+        }
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int c0 = c_begin; c0 < c_end; c0 += 4) {
@@ -56,9 +99,30 @@ __device__ __forceinline__ void skinny_mainloop(const __nv_bfloat16* __restrict_
             const bool ok = c < c_end;
             a[j] = ok ? __ldg(reinterpret_cast<const uint4*>(wa + c * 32)) : zero;
             b[j] = ok ? __ldg(reinterpret_cast<const uint4*>(wb + c * 32)) : zero;
+            if (NORM) {
+                uint4 nq = zero;
+                if (ok) nq = __ldg(reinterpret_cast<const uint4*>(in.norm_w + c * 32 + 8 * t4));
+                const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nq);
+                const float2 w0 = __bfloat1622float2(n2[0]), w1 = __bfloat1622float2(n2[1]);
+                const float2 w2 = __bfloat1622float2(n2[2]), w3 = __bfloat1622float2(n2[3]);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-                xv[j][nt] = ok ? *reinterpret_cast<const uint4*>(xr[nt] + c * 32) : zero;
+                for (int nt = 0; nt < NT; ++nt) {
+                    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+                    if (ok) {
+                        lo = *reinterpret_cast<const float4*>(hr[nt] + c * 32);
+                        hi = *reinterpret_cast<const float4*>(hr[nt] + c * 32 + 4);
+                    }
+                    const float r = rs[nt];
+                    xv[j][nt].x = pack2(lo.x * r * w0.x, lo.y * r * w0.y);
+                    xv[j][nt].y = pack2(lo.z * r * w1.x, lo.w * r * w1.y);
+                    xv[j][nt].z = pack2(hi.x * r * w2.x, hi.y * r * w2.y);
+                    xv[j][nt].w = pack2(hi.z * r * w3.x, hi.w * r * w3.y);
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    xv[j][nt] = ok ? *reinterpret_cast<const uint4*>(xr[nt] + c * 32) : zero;
+            }
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -88,14 +152,21 @@ __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT]
 // A block holds `rowt` row tiles of 16 weight rows, each shared by `ksplit` warps that
 // split K between them (rowt * ksplit warps in all, warp = tile * ksplit + share).
 // EPI: 0 = bfloat16 out, 1 = float32 out, 2 = swiglu (bfloat16 out; the row tiles of a
-// block alternate gate / up, and `half_n` is the width of the result).
-template <int NT, int EPI>
-__global__ void __launch_bounds__(1024) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x,
+// block alternate gate / up, and `half_n` is the width of the result), 3 = added into the
+// float32 rows of `out`.
+template <int NT, int EPI, bool NORM>
+__global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyInput in,
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ bias, void* __restrict__ out,
                                    int T, int N, int K, int half_n, int rowt, int ksplit) {
+    grid_dependency_sync();
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
+    __shared__ float rstd_s[TOK];
+    if (NORM) {
+        skinny_row_rstd(in, T, K, rstd_s);
+        __syncthreads();
+    }
     const int warp = threadIdx.x >> 5;
     const int rt = warp / ksplit, ks = warp - rt * ksplit;
     int n0;  // first weight row of this warp's tile
@@ -114,7 +185,7 @@ __global__ void __launch_bounds__(1024) skinny_gemm_kernel(const __nv_bfloat16* 
         const int per = (chunks + ksplit - 1) / ksplit;
         const int c_begin = ks * per;
         const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
-        skinny_mainloop<NT>(x, w, n0, T, K, c_begin, c_end, acc);
+        skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
     }
     store_partial<NT>(red, acc);
     __syncthreads();
@@ -146,6 +217,8 @@ __global__ void __launch_bounds__(1024) skinny_gemm_kernel(const __nv_bfloat16* 
             if (bias) v += __bfloat162float(bias[n]);
             if (EPI == 0)
                 reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+            else if (EPI == 3)
+                reinterpret_cast<float*>(out)[(int64_t)tok * N + n] += v;
             else
                 reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
         }
@@ -157,8 +230,8 @@ __global__ void __launch_bounds__(1024) skinny_gemm_kernel(const __nv_bfloat16* 
 // q written to the qkv buffer, k and v written to the token's slot of the cache page.
 // Where each token goes (position, page) is looked up before the product starts, so that
 // those loads overlap the weight stream.
-template <int NT, int D>
-__global__ void __launch_bounds__(1024) skinny_qkv_rope_kernel(const __nv_bfloat16* __restrict__ x,
+template <int NT, int D, bool NORM>
+__global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(SkinnyInput in,
                                        const __nv_bfloat16* __restrict__ w,
                                        const __nv_bfloat16* __restrict__ bias,
                                        __nv_bfloat16* __restrict__ qkv,
@@ -170,12 +243,14 @@ __global__ void __launch_bounds__(1024) skinny_qkv_rope_kernel(const __nv_bfloat
                                        __nv_bfloat16* __restrict__ k_pages,
                                        __nv_bfloat16* __restrict__ v_pages, int T, int K, int n_q,
                                        int n_kv, int page_size, int store, int ksplit) {
+    grid_dependency_sync();
     constexpr int ROWT = D / 16;
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];          // [ROWT * ksplit][16][TOK]
     float* val = red + ROWT * ksplit * 16 * TOK;  // [TOK][D]
     __shared__ int tok_pos[TOK];
     __shared__ int tok_page[TOK];           // -2: padding token, -1: no page
+    __shared__ float rstd_s[TOK];
     const int head = blockIdx.x;  // 0..n_q-1 q heads, then k heads, then v heads
     if (threadIdx.x < TOK) {
         const int tok = threadIdx.x;
@@ -190,6 +265,10 @@ __global__ void __launch_bounds__(1024) skinny_qkv_rope_kernel(const __nv_bfloat
         tok_pos[tok] = pos;
         tok_page[tok] = page;
     }
+    if (NORM) {
+        skinny_row_rstd(in, T, K, rstd_s);
+        __syncthreads();
+    }
     const int warp = threadIdx.x >> 5;
     const int rt = warp / ksplit, ks = warp - rt * ksplit;
     const int n0 = head * D + rt * 16;
@@ -200,7 +279,7 @@ __global__ void __launch_bounds__(1024) skinny_qkv_rope_kernel(const __nv_bfloat
     const int per = (chunks + ksplit - 1) / ksplit;
     const int c_begin = ks * per;
     const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
-    skinny_mainloop<NT>(x, w, n0, T, K, c_begin, c_end, acc);
+    skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
     store_partial<NT>(red, acc);
     __syncthreads();
     for (int idx = threadIdx.x; idx < D * TOK; idx += blockDim.x) {
@@ -279,56 +358,82 @@ MB_EXPORT int mb_gemm_skinny_supports(int T, int N, int K) {
     if (NTV <= 1) { constexpr int NT = 1; __VA_ARGS__ }        \
     else { constexpr int NT = 2; __VA_ARGS__ }
 
-// out dtype MB_BF16 or MB_F32; bias may be null.
-MB_EXPORT int mb_gemm_skinny(const void* x, const void* w, const void* bias, void* out,
-                             int out_dtype, int T, int N, int K, void* stream) {
+static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_w, const int* rows,
+                                float eps) {
+    SkinnyInput in;
+    in.x = (const __nv_bfloat16*)x;
+    in.h = h;
+    in.norm_w = (const __nv_bfloat16*)norm_w;
+    in.rows = rows;
+    in.eps = eps;
+    return in;
+}
+
+#define MB_SK_LAUNCH_GEMM(EPI_)                                                                  \
+    do {                                                                                         \
+        if (norm_w) {                                                                            \
+            rc = raise_smem(skinny_gemm_kernel<NT, EPI_, true>, smem);                           \
+            if (rc == MB_OK)                                                                     \
+                MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, true>), blocks, threads, smem, s, in,    \
+                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit);    \
+        } else {                                                                                 \
+            rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
+            if (rc == MB_OK)                                                                     \
+                MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, false>), blocks, threads, smem, s, in,   \
+                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit);    \
+        }                                                                                        \
+    } while (0)
+
+// The activations are either `x` (bfloat16 [T, K]) or, when `norm_w` is given, the float32
+// stream `h` [*, K] normalised with `norm_w` and `eps`, rows picked by `rows` if not null.
+// mode: 0 = bfloat16 out, 1 = float32 out, 3 = add into the float32 rows of `out`.
+// bias may be null.
+MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, const int* rows,
+                             float eps, const void* w, const void* bias, void* out, int mode, int T,
+                             int N, int K, void* stream) {
     if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
+    if (mode != 0 && mode != 1 && mode != 3) return MB_ERR_BAD_DTYPE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
+    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps);
     const int nt = (T + 7) / 8;
     const int tiles = N / 16;
-    const int ksplit = pick_ksplit(tiles, K / 32, 32);
+    const int ksplit = pick_ksplit(tiles, K / 32, norm_w ? 16 : 32);
     const int rowt = ksplit >= 8 ? 1 : 8 / ksplit;
     const int blocks = (tiles + rowt - 1) / rowt;
     const int threads = rowt * ksplit * 32;
+    const int half_n = 0;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
-        if (out_dtype == MB_BF16) {
-            rc = raise_smem(skinny_gemm_kernel<NT, 0>, smem);
-            if (rc == MB_OK)
-                skinny_gemm_kernel<NT, 0><<<blocks, threads, smem, s>>>(
-                    (const bf*)x, (const bf*)w, (const bf*)bias, out, T, N, K, 0, rowt, ksplit);
-        } else {
-            rc = raise_smem(skinny_gemm_kernel<NT, 1>, smem);
-            if (rc == MB_OK)
-                skinny_gemm_kernel<NT, 1><<<blocks, threads, smem, s>>>(
-                    (const bf*)x, (const bf*)w, (const bf*)bias, out, T, N, K, 0, rowt, ksplit);
-        }
+        if (mode == 0) MB_SK_LAUNCH_GEMM(0);
+        else if (mode == 1) MB_SK_LAUNCH_GEMM(1);
+        else MB_SK_LAUNCH_GEMM(3);
     })
     return rc != MB_OK ? rc : launch_status();
 }
 
-// w: [2 * width, K] with the gate rows first; out: [T, width] bfloat16.
-MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const void* w, void* out, int T, int width, int K,
-                                    void* stream) {
+// w: [2 * width, K] with the gate rows first; out: [T, width] bfloat16. Input as above.
+MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* norm_w,
+                                    const int* rows, float eps, const void* w, void* out, int T,
+                                    int width, int K, void* stream) {
     if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
+    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps);
     const int nt = (T + 7) / 8;
     const int pairs = width / 16;
-    const int ksplit = pick_ksplit(2 * pairs, K / 32, 16);
+    const int ksplit = pick_ksplit(2 * pairs, K / 32, norm_w ? 8 : 16);
     const int pairs_per_block = ksplit >= 4 ? 1 : 4 / ksplit;
     const int rowt = 2 * pairs_per_block;
     const int blocks = (pairs + pairs_per_block - 1) / pairs_per_block;
     const int threads = rowt * ksplit * 32;
+    const int N = 2 * width, half_n = width;
+    const void* bias = nullptr;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
-        rc = raise_smem(skinny_gemm_kernel<NT, 2>, smem);
-        if (rc == MB_OK)
-            skinny_gemm_kernel<NT, 2><<<blocks, threads, smem, s>>>(
-                (const bf*)x, (const bf*)w, nullptr, out, T, 2 * width, K, width, rowt, ksplit);
+        MB_SK_LAUNCH_GEMM(2);
     })
     return rc != MB_OK ? rc : launch_status();
 }
@@ -337,8 +442,20 @@ MB_EXPORT int mb_gemm_skinny_qkv_supports(int T, int K, int d, int rot) {
     return T >= 1 && T <= 16 && K > 0 && K % 32 == 0 && (d == 64 || d == 128) && (rot == d || rot == 0);
 }
 
+#define MB_SK_LAUNCH_QKV(DD, NORM_)                                                              \
+    do {                                                                                         \
+        rc = raise_smem(skinny_qkv_rope_kernel<NT, DD, NORM_>, smem);                            \
+        if (rc == MB_OK)                                                                         \
+            MB_LAUNCH((skinny_qkv_rope_kernel<NT, DD, NORM_>), heads, threads, smem, s, in,      \
+                      (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions, seq_of_token, \
+                      table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv, page_size,  \
+                      store, ksplit);                                                            \
+    } while (0)
+
 // The packed q/k/v projection of a few tokens with bias, rotation and cache store fused.
-MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const void* w, const void* bias, void* qkv,
+// Input as for mb_gemm_skinny (rows is not used here).
+MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const float* h, const void* norm_w, float eps,
+                                      const void* w, const void* bias, void* qkv,
                                       const float* cos_t, const float* sin_t, int rot,
                                       const int* positions, const int* seq_of_token,
                                       const int* table, int max_pages, void* k_pages, void* v_pages,
@@ -347,29 +464,20 @@ MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const void* w, const void* 
     if (!mb_gemm_skinny_qkv_supports(T, K, d, rot)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
+    const SkinnyInput in = skinny_input(x, h, norm_w, nullptr, eps);
     const int nt = (T + 7) / 8;
     const int heads = n_q + 2 * n_kv;
     const int rowt = d / 16;
-    const int ksplit = pick_ksplit(heads * rowt, K / 32, 32 / rowt);
+    const int ksplit = pick_ksplit(heads * rowt, K / 32, (norm_w ? 16 : 32) / rowt);
     const int threads = rowt * ksplit * 32;
     const float* c = rot ? cos_t : nullptr;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = ((size_t)rowt * ksplit * 16 + d) * 8 * NT * sizeof(float);
         if (d == 64) {
-            rc = raise_smem(skinny_qkv_rope_kernel<NT, 64>, smem);
-            if (rc == MB_OK)
-                skinny_qkv_rope_kernel<NT, 64><<<heads, threads, smem, s>>>(
-                    (const bf*)x, (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions,
-                    seq_of_token, table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv,
-                    page_size, store, ksplit);
+            if (norm_w) MB_SK_LAUNCH_QKV(64, true); else MB_SK_LAUNCH_QKV(64, false);
         } else {
-            rc = raise_smem(skinny_qkv_rope_kernel<NT, 128>, smem);
-            if (rc == MB_OK)
-                skinny_qkv_rope_kernel<NT, 128><<<heads, threads, smem, s>>>(
-                    (const bf*)x, (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions,
-                    seq_of_token, table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv,
-                    page_size, store, ksplit);
+            if (norm_w) MB_SK_LAUNCH_QKV(128, true); else MB_SK_LAUNCH_QKV(128, false);
         }
     })
     return rc != MB_OK ? rc : launch_status();

@@ -16,6 +16,7 @@ constexpr int SAMPLE_THREADS = 1024;
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    grid_dependency_sync();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (int64_t)blockIdx.x * vocab;
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ out, int vocab) {
+    grid_dependency_sync();
     __shared__ float scratch[33];
     __shared__ float sums[SAMPLE_THREADS];
     __shared__ int chosen;
@@ -179,7 +181,7 @@ using namespace mb;
 MB_EXPORT int mb_argmax(const float* logits, int* out, int rows, int vocab, void* stream) {
     if (rows <= 0) return MB_OK;
     if (vocab <= 0) return MB_ERR_UNSUPPORTED_SIZE;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    MB_LAUNCH((argmax_kernel), rows, SAMPLE_THREADS, 0, (cudaStream_t)stream, logits, out, vocab);
     return launch_status();
 }
 
@@ -187,7 +189,7 @@ MB_EXPORT int mb_sample(const float* logits, const float* temperature, const flo
                         const float* uniform, int* out, int rows, int vocab, void* stream) {
     if (rows <= 0) return MB_OK;
     if (vocab <= 0) return MB_ERR_UNSUPPORTED_SIZE;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, top_p,
+    MB_LAUNCH((sample_kernel), rows, SAMPLE_THREADS, 0, (cudaStream_t)stream, logits, temperature, top_p,
                                                                     uniform, out, vocab);
     return launch_status();
 }

@@ -45,9 +45,12 @@ _SIGNATURES = {
                                c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
                                c_void_p],
-    "mb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "mb_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "mb_gemm_skinny_qkv_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+    "mb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                       c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_void_p],
+    "mb_gemm_skinny_qkv_rope": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -69,6 +72,8 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.mb_set_dependent_launch.argtypes = [c_int]
+    lib.mb_set_dependent_launch.restype = None
     lib.mb_gemm_skinny_supports.argtypes = [c_int, c_int, c_int]
     lib.mb_gemm_skinny_supports.restype = c_int
     lib.mb_gemm_skinny_qkv_supports.argtypes = [c_int, c_int, c_int, c_int]

@@ -28,7 +28,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 class CudaOps:
-    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library"):
+    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library",
+                 dependent_launch: bool = False):
         """`gemm` picks the bfloat16 product: "library" (cuBLAS through torch.mm, where the
         reference calls F.linear) or "simt" (this package's CUDA-core kernel). The float32
         engine always runs the CUDA-core kernel: a library product would need its
@@ -37,6 +38,10 @@ class CudaOps:
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
+        # Normalising inside the consuming product saves a launch but makes every block
+        # redo the row statistics; measured on B200 the separate norm kernel is faster for
+        # the Qwen2 shapes, so the fusion is off unless asked for.
+        self.fuse_norm = False
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
                               "no CPU path")
@@ -45,6 +50,8 @@ class CudaOps:
         if major != 10:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}x")
         self.lib = library.load()
+        # let each kernel be scheduled while its predecessor drains (see csrc/common.cuh)
+        self.lib.mb_set_dependent_launch(int(dependent_launch))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_splits = decode_splits
         self._scratch: torch.Tensor | None = None
@@ -89,21 +96,62 @@ class CudaOps:
                                       _flag(out.dtype), self._stream()), "add_rmsnorm")
         self.launches += 1
 
+    # -- inputs that may still be an unevaluated norm (parts/norm.py: PendingNorm)
+
+    def can_fuse_norm(self, rows: int, hidden: int, weight) -> bool:
+        """Whether a few-token product can normalise its own input for this shape."""
+        return (self.fuse_norm and self.skinny and rows <= 16 and hidden % 32 == 0
+                and weight.dtype == torch.bfloat16)
+
+    @staticmethod
+    def _pending(x):
+        return x if hasattr(x, "materialize") else None
+
+    def _skinny_input(self, x):
+        """(x, h, norm weight, rows, eps) pointers/values of the C interface."""
+        pending = self._pending(x)
+        if pending is None:
+            return _ptr(x), None, None, None, 0.0
+        return None, _ptr(pending.h), _ptr(pending.weight), _ptr(pending.rows), float(pending.eps)
+
+    def linear_residual(self, x, weight, bias, h, ctx, name):
+        """h += x . weight^T (+ bias) in the float32 stream when the few-token kernel takes
+        the shape (returns None); otherwise the product lands in the buffer `name` and is
+        returned for the next norm to add."""
+        m, k = x.shape
+        n = weight.shape[0]
+        if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and (bias is None or bias.dtype == torch.bfloat16) and h.dtype == torch.float32
+                and self.lib.mb_gemm_skinny_supports(m, n, k)):
+            check(self.lib.mb_gemm_skinny(_ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(bias),
+                                          _ptr(h), 3, m, n, k, self._stream()),
+                  "linear_residual (skinny)")
+            self.launches += 1
+            return None
+        out = ctx.buffer(name, m, n)
+        self.linear(x, weight, bias, out)
+        return out
+
     def linear(self, x, weight, bias, out):
+        pending = self._pending(x)
         m, k = x.shape
         n = weight.shape[0]
         if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
             raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> "
                               f"{tuple(out.shape)} do not fit")
-        self._rows(x), self._rows(weight), self._rows(out)
+        self._rows(weight), self._rows(out)
         all_bf16 = (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                     and (bias is None or bias.dtype == torch.bfloat16))
         if all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k):
-            check(self.lib.mb_gemm_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out),
-                                          _flag(out.dtype), m, n, k, self._stream()),
+            check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
+                                          _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
+                                          self._stream()),
                   "linear (skinny)")
             self.launches += 1
             return
+        if pending is not None:
+            x = pending.materialize()
+        self._rows(x)
         if self.gemm == "library" and all_bf16:
             return self._library_linear(x, weight, bias, out)
         check(self.lib.mb_gemm_simt(_ptr(x), _flag(x.dtype), _ptr(weight), _flag(weight.dtype),
@@ -133,10 +181,13 @@ class CudaOps:
         width = out.shape[1]
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_supports(m, width, k)):
-            check(self.lib.mb_gemm_skinny_swiglu(_ptr(x), _ptr(weight), _ptr(out), m, width, k,
-                                                 self._stream()), "linear_swiglu (skinny)")
+            check(self.lib.mb_gemm_skinny_swiglu(*self._skinny_input(x), _ptr(weight), _ptr(out),
+                                                 m, width, k, self._stream()),
+                  "linear_swiglu (skinny)")
             self.launches += 1
             return
+        if self._pending(x) is not None:
+            x = x.materialize()
         gate_up = ctx.buffer("gate_up", m, 2 * width)
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
@@ -152,14 +203,17 @@ class CudaOps:
                 and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
                 and cache.k.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_qkv_supports(m, k, head_dim, rot)):
+            xp, hp, wp, _rows, eps = self._skinny_input(x)
             check(self.lib.mb_gemm_skinny_qkv_rope(
-                _ptr(x), _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
+                xp, hp, wp, eps, _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
                 _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table),
                 cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), m, k, num_heads, num_kv_heads,
                 head_dim, cache.page_size, int(cache.write), self._stream()),
                 "qkv_rope_store (skinny)")
             self.launches += 1
             return
+        if self._pending(x) is not None:
+            x = x.materialize()
         self.linear(x, weight, bias, qkv)
         self.rope_cache_write(qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache)
 

@@ -121,5 +121,5 @@ class Model:
             delta = block.forward(h, delta, ctx, cache, states.get(index))
         if batch.num_logit_rows == 0:
             return None
-        rows = self.final_norm.add_norm(h, delta, ctx, rows=batch.logit_rows)
+        rows = self.final_norm.add_norm(h, delta, ctx, rows=batch.logit_rows, defer=True)
         return self.head.forward(rows, ctx)

@@ -18,6 +18,8 @@ from .rotary import NoPositionEncoding
 
 class GroupedQueryAttention(Mixer):
     capturable = True
+    accepts_pending_norm = True
+    adds_to_residual = True
 
     def __init__(
         self,
@@ -85,7 +87,7 @@ class GroupedQueryAttention(Mixer):
         self.out_b = setup.place(tensors[p + "o_proj.bias"]) if self.out_bias else None
         self.position.load(tensors, setup)
 
-    def forward(self, x, ctx, cache, state):
+    def forward(self, x, ctx, cache, state, residual=None):
         tokens = x.shape[0]
         ops = ctx.ops
         qkv = ctx.buffer("qkv", tokens, self.q_size + 2 * self.kv_size)
@@ -95,6 +97,8 @@ class GroupedQueryAttention(Mixer):
             ops.qkv_rope_store(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads,
                                self.num_kv_heads, self.head_dim, tables, ctx.batch, cache)
         else:
+            if hasattr(x, "materialize"):
+                x = x.materialize()
             ops.linear(x, self.qkv_weight, self.qkv_b, qkv)
             self.position.apply(qkv, (self.num_heads, self.num_kv_heads, self.head_dim), ctx)
             ops.rope_cache_write(qkv, self.num_heads, self.num_kv_heads, self.head_dim, None,
@@ -104,6 +108,9 @@ class GroupedQueryAttention(Mixer):
             qkv, self.num_heads, self.num_kv_heads, self.head_dim, ctx.batch, cache,
             self.scale, self.window, attended,
         )
+        if residual is not None:
+            return ops.linear_residual(attended, self.out_weight, self.out_b, residual, ctx,
+                                       "mixer_out")
         out = ctx.buffer("mixer_out", tokens, self.hidden_size)
         ops.linear(attended, self.out_weight, self.out_b, out)
         return out

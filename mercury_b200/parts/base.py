@@ -24,8 +24,15 @@ Mixer (`register_mixer`):
 FeedForward (`register_feed_forward`):
     forward(x, ctx) -> Tensor
 
+Two optional protocols let a mixer or feed-forward fuse with its neighbours; a part that
+declares neither is handed a plain tensor and returns its output, as above.
+    accepts_pending_norm = True    x may be a `PendingNorm` (parts/norm.py): the norm before
+                                   the part has not run, the part's first kernel does it
+    adds_to_residual = True        forward(..., residual=h) may add the output into the
+                                   float32 stream itself and return None
+
 Norm (`register_norm`):
-    add_norm(h, delta, ctx, rows=None) -> Tensor
+    add_norm(h, delta, ctx, rows=None, defer=False) -> Tensor | PendingNorm
         h: [T, hidden] float32 residual stream, updated in place to h + delta when delta is
         given; returns norm(h) in the activation dtype. With `rows` (int32 indices) only
         those rows are normalised and returned, and h is left as it was.

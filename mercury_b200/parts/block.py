@@ -22,10 +22,18 @@ class PreNormBlock:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
     def forward(self, h, delta, ctx, cache, state):
-        x = self.mixer_norm.add_norm(h, delta, ctx)
-        mixed = self.mixer.forward(x, ctx, cache, state)
-        x = self.feed_forward_norm.add_norm(h, mixed, ctx)
-        return self.feed_forward.forward(x, ctx)
+        mixer, ff = self.mixer, self.feed_forward
+        x = self.mixer_norm.add_norm(h, delta, ctx,
+                                     defer=getattr(mixer, "accepts_pending_norm", False))
+        if getattr(mixer, "adds_to_residual", False):
+            mixed = mixer.forward(x, ctx, cache, state, residual=h)
+        else:
+            mixed = mixer.forward(x, ctx, cache, state)
+        x = self.feed_forward_norm.add_norm(h, mixed, ctx,
+                                            defer=getattr(ff, "accepts_pending_norm", False))
+        if getattr(ff, "adds_to_residual", False):
+            return ff.forward(x, ctx, residual=h)
+        return ff.forward(x, ctx)
 
 
 register_arrangement("pre_norm", PreNormBlock)

@@ -11,6 +11,8 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 class GatedFeedForward(FeedForward):
     capturable = True
+    accepts_pending_norm = True
+    adds_to_residual = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str,
                  activation: str = "silu"):
@@ -37,10 +39,12 @@ class GatedFeedForward(FeedForward):
         self.gate_up_weight = torch.cat([gate.to(widest), up.to(widest)], dim=0).contiguous()
         self.down_weight = setup.place(tensors[p + "down_proj.weight"])
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, residual=None):
         tokens = x.shape[0]
         act = ctx.buffer("ff_act", tokens, self.intermediate_size)
         ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx)
+        if residual is not None:
+            return ctx.ops.linear_residual(act, self.down_weight, None, residual, ctx, "ff_out")
         out = ctx.buffer("ff_out", tokens, self.hidden_size)
         ctx.ops.linear(act, self.down_weight, None, out)
         return out

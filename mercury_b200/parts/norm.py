@@ -12,6 +12,24 @@ from __future__ import annotations
 from .base import Norm, TensorSpec, register_norm
 
 
+class PendingNorm:
+    """A norm that has not run yet: the float32 stream, the weight and eps (and optionally
+    which rows). A consumer whose kernel can normalise its input on the fly takes this
+    instead of a tensor and saves the norm's own launch; any other consumer calls
+    `materialize()` and gets the normalised rows."""
+
+    def __init__(self, h, weight, eps, rows, ctx, size):
+        self.h, self.weight, self.eps, self.rows, self.ctx, self.size = h, weight, eps, rows, ctx, size
+        self.shape = ((h.shape[0] if rows is None else rows.shape[0]), size)
+        self.dtype = ctx.dtype
+
+    def materialize(self):
+        count = self.shape[0]
+        out = self.ctx.buffer("normed" if self.rows is None else "normed_rows", count, self.size)
+        self.ctx.ops.add_rmsnorm(self.h, None, self.weight, self.eps, out, self.rows)
+        return out
+
+
 class RMSNorm(Norm):
     capturable = True
 
@@ -28,8 +46,13 @@ class RMSNorm(Norm):
     def load(self, tensors, setup):
         self.weight = setup.place(tensors[self.weight_name])
 
-    def add_norm(self, h, delta, ctx, rows=None):
+    def add_norm(self, h, delta, ctx, rows=None, defer=False):
+        """`defer=True` says that the consumer takes a `PendingNorm`; one is returned when
+        nothing has to be added first and the kernels can fuse the norm for this many rows."""
         count = h.shape[0] if rows is None else rows.shape[0]
+        if (defer and delta is None
+                and getattr(ctx.ops, "can_fuse_norm", lambda *a: False)(count, self.size, self.weight)):
+            return PendingNorm(h, self.weight, self.eps, rows, ctx, self.size)
         out = ctx.buffer("normed" if rows is None else "normed_rows", count, self.size)
         ctx.ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         return out

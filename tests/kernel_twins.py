@@ -37,19 +37,38 @@ class TorchOps:
 
     # ---------------------------------------------------------------- products
 
+    # inputs may be an unevaluated norm (PendingNorm); the twin simply evaluates it
+
+    def can_fuse_norm(self, rows, hidden, weight):
+        return rows <= 16
+
+    @staticmethod
+    def _x(x):
+        return x.materialize() if hasattr(x, "materialize") else x
+
+    def linear_residual(self, x, weight, bias, h, ctx, name):
+        y = self._x(x).to(self.acc) @ weight.to(self.acc).T
+        if bias is not None:
+            y = y + bias.to(self.acc)
+        h.add_(y.to(h.dtype))
+        return None
+
     def linear(self, x, weight, bias, out):
+        x = self._x(x)
         y = x.to(self.acc) @ weight.to(self.acc).T
         if bias is not None:
             y = y + bias.to(self.acc)
         out.copy_(y.to(out.dtype))
 
     def linear_swiglu(self, x, weight, out, ctx=None):
+        x = self._x(x)
         gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
 
     def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
                        batch, cache):
+        x = self._x(x)
         self.linear(x, weight, bias, qkv)
         self.rope_cache_write(qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache)
 

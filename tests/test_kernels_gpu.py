@@ -138,6 +138,76 @@ def test_linear_swiglu(ops, twin, m, width, k):
     assert err <= 3 * 2.0 ** -8, err
 
 
+def fake_ctx(ops):
+    return SimpleNamespace(ops=ops, dtype=torch.bfloat16, buffer=lambda name, rows, cols, dtype=None:
+                           torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 896, 896), (8, 896, 4864), (16, 1536, 320), (40, 896, 896),
+                                   (5, 100, 70)])
+def test_linear_residual(ops, twin, m, n, k):
+    """Few tokens: the product is added into the float32 stream by the kernel itself; other
+    shapes hand the product back for the next norm to add."""
+    x = rand((m, k), torch.bfloat16, 31)
+    w = rand((n, k), torch.bfloat16, 32, 0.1)
+    bias = rand((n,), torch.bfloat16, 33) if m % 2 else None
+    h = rand((m, n), torch.float32, 34)
+    want = h.double() + x.double() @ w.double().T + (bias.double() if bias is not None else 0)
+    got = ops.linear_residual(x, w, bias, h, fake_ctx(ops), "tmp")
+    result = h.double() if got is None else h.double() + got.double()
+    assert (got is None) == (m <= 16 and n % 16 == 0 and k % 32 == 0)
+    tol = 2 * k ** 0.5 * 2.0 ** -24 + (0 if got is None else 2.0 ** -8)
+    assert float((result - want).abs().max() / want.abs().max()) <= tol
+
+
+@pytest.mark.parametrize("m,hidden", [(1, 896), (8, 896), (13, 1536), (16, 320)])
+def test_products_that_normalise_their_own_input(ops, twin, m, hidden):
+    """linear, linear_swiglu and qkv_rope_store given a PendingNorm against the same ops given
+    the norm's output."""
+    from mercury_b200.parts.norm import PendingNorm
+
+    h = rand((m + 3, hidden), torch.float32, 41)
+    norm_w = rand((hidden,), torch.bfloat16, 42, 0.1) + 1
+    ctx = fake_ctx(ops)
+    rows = torch.tensor(list(range(m + 2, 2, -1)), dtype=torch.int32).cuda()   # m rows, reversed
+    for use_rows in (False, True):
+        pending = PendingNorm(h[:m] if not use_rows else h, norm_w, 1e-6, rows if use_rows else None,
+                              ctx, hidden)
+        normed = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+        twin.add_rmsnorm((h[:m] if not use_rows else h).clone(), None, norm_w, 1e-6, normed,
+                         rows if use_rows else None)
+        w = rand((1024, hidden), torch.bfloat16, 43, 0.1)
+        got = torch.empty((m, 1024), dtype=torch.float32, device="cuda")
+        want = torch.empty_like(got)
+        ops.linear(pending, w, None, got)
+        twin.linear(normed, w, None, want)
+        # the norm's output is rounded to bfloat16 either way; its last bit may differ
+        assert float((got - want).abs().max() / want.abs().max()) <= 2.0 ** -7
+    pending = PendingNorm(h[:m], norm_w, 1e-6, None, ctx, hidden)
+    twin.add_rmsnorm(h[:m].clone(), None, norm_w, 1e-6, normed)
+    w2 = rand((2 * 336, hidden), torch.bfloat16, 44, 0.1)
+    got = torch.empty((m, 336), dtype=torch.bfloat16, device="cuda")
+    want = torch.empty_like(got)
+    ops.linear_swiglu(pending, w2, got, ctx)
+    twin.linear_swiglu(normed, w2, want)
+    assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 4 * 2.0 ** -8
+    n_q, n_kv, d, page = 3, 1, 64, 16
+    kv_lens = tuple(range(20, 20 + m))
+    batch, table = make_batch((1,) * m, kv_lens, page, 64, seed=7)
+    k, v = fill_cache(batch, table, kv_lens, (1,) * m, n_kv, d, page, 64, torch.bfloat16, 8, False)
+    k2, v2 = k.clone(), v.clone()
+    w3 = rand(((n_q + 2 * n_kv) * d, hidden), torch.bfloat16, 45, 0.1)
+    b3 = rand(((n_q + 2 * n_kv) * d,), torch.bfloat16, 46)
+    angles = torch.rand((64, d // 2), generator=torch.Generator().manual_seed(9)) * 6
+    tables = (angles.cos().cuda(), angles.sin().cuda())
+    qkv = torch.zeros((m, (n_q + 2 * n_kv) * d), dtype=torch.bfloat16, device="cuda")
+    qkv2 = qkv.clone()
+    ops.qkv_rope_store(pending, w3, b3, qkv, n_q, n_kv, d, tables, batch, LayerCache(k, v, page, table, True))
+    twin.qkv_rope_store(normed, w3, b3, qkv2, n_q, n_kv, d, tables, batch, LayerCache(k2, v2, page, table, True))
+    for got, want in ((qkv[:, :n_q * d], qkv2[:, :n_q * d]), (k, k2), (v, v2)):
+        assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 4 * 2.0 ** -8
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,page,hidden", [(14, 2, 64, 16, 896), (12, 2, 128, 16, 1536),
                                                     (3, 1, 64, 8, 96), (4, 4, 128, 32, 64)])
 @pytest.mark.parametrize("q_lens,kv_lens", [((1, 1, 1), (40, 17, 300)), ((1,) * 9, tuple(range(5, 50, 5))),
