@@ -243,6 +243,9 @@ class ModelRunner:
             return self._decode_with_graph(entries)
         batch = self.prepare(entries)
         logits = self.run(batch)
+        check = getattr(self.ops, "check_errors", None)
+        if check is not None:
+            check()
         self.finish(entries)
         return logits
 

@@ -53,6 +53,8 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                        c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
@@ -72,6 +74,8 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.mb_gemm_tcgen05_supports.argtypes = [c_int, c_int, c_int]
+    lib.mb_gemm_tcgen05_supports.restype = c_int
     lib.mb_set_dependent_launch.argtypes = [c_int]
     lib.mb_set_dependent_launch.restype = None
     lib.mb_gemm_skinny_supports.argtypes = [c_int, c_int, c_int]

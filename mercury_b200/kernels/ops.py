@@ -28,13 +28,17 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 class CudaOps:
-    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library",
+    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "auto",
                  dependent_launch: bool = False):
-        """`gemm` picks the bfloat16 product: "library" (cuBLAS through torch.mm, where the
-        reference calls F.linear) or "simt" (this package's CUDA-core kernel). The float32
-        engine always runs the CUDA-core kernel: a library product would need its
-        reduced-precision mode switched off process-wide to be a true 32-bit product."""
-        if gemm not in ("library", "simt"):
+        """`gemm` picks the bfloat16 product on many tokens: "tcgen05" (this package's
+        TMA + tensor-memory kernel wherever it takes the shape), "library" (cuBLAS through
+        torch.mm, where the reference calls F.linear), "auto" (tcgen05 for the narrow
+        products where it is the faster of the two on B200, the library for the wide ones)
+        or "simt" (the CUDA-core kernel). Few tokens always take the weight-streaming
+        kernels. The float32 engine always runs the CUDA-core kernel: a library product
+        would need its reduced-precision mode switched off process-wide to be a true 32-bit
+        product."""
+        if gemm not in ("library", "simt", "tcgen05", "auto"):
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
@@ -56,6 +60,8 @@ class CudaOps:
         self.decode_splits = decode_splits
         self._scratch: torch.Tensor | None = None
         self._counters: torch.Tensor | None = None   # zeroed tickets of the in-kernel split merge
+        self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
+        self._tc_pending = False
         self.launches = 0
         self.library_calls = 0
         # split-K partial sums stay float32
@@ -95,6 +101,19 @@ class CudaOps:
                                       _ptr(out), _ptr(rows), count, h.shape[1], float(eps),
                                       _flag(out.dtype), self._stream()), "add_rmsnorm")
         self.launches += 1
+
+    def check_errors(self) -> None:
+        """Raise if a bounded wait inside a tcgen05 kernel ran out since the last check
+        (reads one word from the device, so it synchronises)."""
+        if not self._tc_pending:
+            return
+        self._tc_pending = False
+        code = int(self._tc_error.item())
+        if code:
+            self._tc_error.zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue",
+                    4: "the producer's drain"}.get(code, f"code {code}")
+            raise KernelError(f"a tcgen05 product gave up waiting in {role}; its output is invalid")
 
     # -- inputs that may still be an unevaluated norm (parts/norm.py: PendingNorm)
 
@@ -152,7 +171,19 @@ class CudaOps:
         if pending is not None:
             x = pending.materialize()
         self._rows(x)
-        if self.gemm == "library" and all_bf16:
+        if all_bf16 and self.gemm in ("tcgen05", "auto") and self.lib.mb_gemm_tcgen05_supports(m, n, k):
+            narrow = n <= 2048 and k <= 2048
+            if self.gemm == "tcgen05" or narrow:
+                if self._tc_error is None:
+                    self._tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)
+                check(self.lib.mb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out),
+                                               int(out.dtype == torch.float32), m, n, k,
+                                               _ptr(self._tc_error), 0, self._stream()),
+                      "linear (tcgen05)")
+                self.launches += 1
+                self._tc_pending = True
+                return
+        if self.gemm != "simt" and all_bf16:
             return self._library_linear(x, weight, bias, out)
         check(self.lib.mb_gemm_simt(_ptr(x), _flag(x.dtype), _ptr(weight), _flag(weight.dtype),
                                     _ptr(bias), _flag(bias.dtype) if bias is not None else 0,

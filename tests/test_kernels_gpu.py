@@ -121,6 +121,36 @@ def test_linear(ops, twin, m, n, k, x_dtype, w_dtype, o_dtype):
     close(got, want, o_dtype, terms=k)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (2048, 1152, 896), (130, 200, 72), (300, 9728, 896),
+                                   (17, 151936, 64), (1000, 896, 4864), (129, 257, 8)])
+@pytest.mark.parametrize("tile", [1, 2], ids=["128x128", "128x256"])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32], ids=["bf16out", "f32out"])
+def test_tcgen05_product(twin, m, n, k, tile, out_dtype):
+    """The TMA + tensor-memory kernel called directly, both tile shapes, edges in M, N and K."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 51)
+    w = rand((n, k), torch.bfloat16, 52, 0.1)
+    bias = rand((n,), torch.bfloat16, 53) if n % 2 else None
+    got = torch.zeros((m, n), dtype=out_dtype, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.mb_gemm_tcgen05(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                             got.data_ptr(), int(out_dtype == torch.float32), m, n, k,
+                             error.data_ptr(), tile, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert int(error.item()) == 0, "a bounded wait in the kernel ran out"
+    want = torch.empty_like(got)
+    twin.linear(x, w, bias, want)
+    close(got, want, out_dtype, terms=k)
+
+
+def test_tcgen05_refuses_an_odd_k():
+    from mercury_b200.kernels import library
+
+    assert library.load().mb_gemm_tcgen05_supports(128, 128, 100) == 0
+
+
 @pytest.mark.parametrize("m,width,k", [(1, 4864, 896), (8, 128, 64), (12, 336, 96), (16, 4864, 896),
                                        (70, 320, 96), (5, 200, 80), (3, 48, 4864)])
 def test_linear_swiglu(ops, twin, m, width, k):
