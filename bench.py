@@ -123,12 +123,13 @@ def model_numbers(cfg: dict) -> dict:
             "attn_flops": lambda t: 2 * t * t * n_q * d * layers, "head_flops_per_row": 2 * head}
 
 
-def make_runner(torch, config, tensors, batch, page_tokens):
+def make_runner(torch, config, tensors, batch, page_tokens, graphs=True):
     from mercury_b200.engine.runner import ModelRunner
 
     return ModelRunner(config=config, tensors=tensors, dtype=torch.bfloat16, device="cuda",
                        page_size=BLOCK, num_pages=page_tokens // BLOCK, max_seqs=batch,
-                       max_step_tokens=max(PREFILL_TOKENS, batch), max_model_len=MODEL_LEN)
+                       max_step_tokens=max(PREFILL_TOKENS, batch), max_model_len=MODEL_LEN,
+                       cuda_graphs=graphs)
 
 
 def timed(torch, fn, reps: int) -> float:
@@ -287,6 +288,45 @@ def run_ours(args) -> dict:
     }
 
 
+def run_part(args) -> dict:
+    """`--only decode|prefill|products`: one small workload for profilers, with the same
+    model, weights and shapes as the full run. Prints what it measured, not the bench line."""
+    import torch
+
+    from mercury_b200.config import config_from_dict
+    from mercury_b200.weights import random_tensors
+
+    _entry, config = config_from_dict(QWEN25_05B)
+    vocab = QWEN25_05B["vocab_size"]
+    if args.only == "products":
+        from mercury_b200.kernels.ops import CudaOps
+
+        out = {}
+        for name, (m, n, k) in {"qkv": (2048, 1152, 896), "o": (2048, 896, 896),
+                                "gate_up": (2048, 9728, 896), "down": (2048, 896, 4864)}.items():
+            x = torch.randn(m, k).bfloat16().cuda()
+            w = torch.randn(n, k).bfloat16().cuda()
+            y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            for gemm in ("library", "tcgen05"):
+                ops = CudaOps("cuda", gemm=gemm)
+                for _ in range(3):
+                    ops.linear(x, w, None, y)
+                ms = timed(torch, lambda: ops.linear(x, w, None, y), args.steps)
+                ops.check_errors()
+                out[f"{name}_{gemm}_us"] = round(ms * 1e3, 1)
+                out[f"{name}_{gemm}_tflops"] = round(2 * m * n * k / ms / 1e9, 1)
+        return out
+    tensors = random_tensors(config, SEED, torch.bfloat16)
+    batch = args.batch
+    runner = make_runner(torch, config, tensors, max(batch, 2), max(batch, 2) * (CONTEXT + 256),
+                         graphs=not args.no_graphs)
+    if args.only == "prefill":
+        return {"prefill_ms": round(prefill_rate(torch, runner, vocab, reps=args.steps), 3)}
+    rate, ms, launches = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps, args.warmup)
+    return {"decode_tokens_per_s": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch,
+            "launches_per_step": launches, "graphs": not args.no_graphs}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference (installed under baseline/_ref) on the same model folder,
     batch and context, through its own Engine.submit/step."""
@@ -349,10 +389,17 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=64)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="mercury_b200", choices=("mercury_b200", "reference"))
+    p.add_argument("--only", default="all", choices=("all", "decode", "prefill", "products"),
+                   help="run one part only (for profilers); prints its own small JSON")
+    p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")
+    p.add_argument("--no-graphs", action="store_true", help="launch kernels one by one")
     args = p.parse_args()
     if args.gpus != 1:
         print("bench.py measures a single-GPU engine; --gpus must be 1", flush=True)
         return 2
+    if args.only != "all":
+        print(json.dumps(run_part(args)), flush=True)
+        return 0
     args.warmup = max(3, args.warmup)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result), flush=True)

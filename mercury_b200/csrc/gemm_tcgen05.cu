@@ -16,6 +16,9 @@
 // 16-byte aligned.
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace mb {
@@ -283,16 +286,50 @@ static EncodeTiledFn encode_tiled() {
 }
 
 // A [rows, K] bfloat16 row-major matrix as tiles of box_rows x 64 with 128-byte swizzle.
+// Encoding a map costs microseconds on the host and the same few matrices come back every
+// step, so encoded maps are kept (a map depends only on address, sizes and box).
+struct MapKey {
+    const void* base;
+    int rows, K, box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && K == o.K && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        h ^= std::hash<long long>()(((long long)k.rows << 32) ^ ((long long)k.K << 8) ^ k.box_rows) +
+             0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+
 static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex guard;
+    const MapKey key{base, rows, K, box_rows};
+    {
+        std::lock_guard<std::mutex> lock(guard);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *map = it->second;
+            return true;
+        }
+    }
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> lock(guard);
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *map;
+    return true;
 }
 
 }  // namespace mb

@@ -178,7 +178,14 @@ class ModelRunner:
     def run(self, batch: StepBatch) -> torch.Tensor | None:
         """The model pass over a prepared batch; float32 logits `[wanted, vocab]` or None."""
         self.ctx.batch = batch
-        return self.model.forward(self.ctx, self.kv_layers, self.states)
+        pin = getattr(self.ops, "pin_stream", None)
+        if pin is None:
+            return self.model.forward(self.ctx, self.kv_layers, self.states)
+        pin()
+        try:
+            return self.model.forward(self.ctx, self.kv_layers, self.states)
+        finally:
+            self.ops.unpin_stream()
 
     def finish(self, entries: list[StepEntry]) -> None:
         """Book the tokens as computed: full pages become shareable, passed pages go back."""

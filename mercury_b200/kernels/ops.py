@@ -28,13 +28,14 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 class CudaOps:
-    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "auto",
+    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library",
                  dependent_launch: bool = False):
         """`gemm` picks the bfloat16 product on many tokens: "tcgen05" (this package's
         TMA + tensor-memory kernel wherever it takes the shape), "library" (cuBLAS through
-        torch.mm, where the reference calls F.linear), "auto" (tcgen05 for the narrow
-        products where it is the faster of the two on B200, the library for the wide ones)
-        or "simt" (the CUDA-core kernel). Few tokens always take the weight-streaming
+        torch.mm, where the reference calls F.linear; the default, because inside a whole
+        prompt step it is still ahead of this package's first tcgen05 kernel), "auto"
+        (tcgen05 for the narrow products, where it wins when timed alone, the library for
+        the wide ones) or "simt" (the CUDA-core kernel). Few tokens always take the weight-streaming
         kernels. The float32 engine always runs the CUDA-core kernel: a library product
         would need its reduced-precision mode switched off process-wide to be a true 32-bit
         product."""
@@ -62,6 +63,7 @@ class CudaOps:
         self._counters: torch.Tensor | None = None   # zeroed tickets of the in-kernel split merge
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
+        self._pinned_stream: int | None = None
         self.launches = 0
         self.library_calls = 0
         # split-K partial sums stay float32
@@ -70,7 +72,16 @@ class CudaOps:
     # ------------------------------------------------------------------ helpers
 
     def _stream(self) -> int:
+        if self._pinned_stream is not None:
+            return self._pinned_stream
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def pin_stream(self) -> None:
+        """Look the current stream up once for the many launches of a step."""
+        self._pinned_stream = torch.cuda.current_stream(self.device).cuda_stream
+
+    def unpin_stream(self) -> None:
+        self._pinned_stream = None
 
     def _scratch_for(self, floats: int) -> torch.Tensor:
         if self._scratch is None or self._scratch.numel() < floats:
@@ -172,7 +183,8 @@ class CudaOps:
             x = pending.materialize()
         self._rows(x)
         if all_bf16 and self.gemm in ("tcgen05", "auto") and self.lib.mb_gemm_tcgen05_supports(m, n, k):
-            narrow = n <= 2048 and k <= 2048
+            # measured on B200: ahead of the library for M >= 256 with N, K up to about 2048
+            narrow = m >= 256 and n <= 2048 and k <= 2048
             if self.gemm == "tcgen05" or narrow:
                 if self._tc_error is None:
                     self._tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)
