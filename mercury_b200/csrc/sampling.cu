@@ -59,6 +59,79 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     }
 }
 
+// Large vocabularies: a row is cut into `parts` slices, one block each, which leave their
+// (maximum, lowest index of it) in `partial`; argmax_merge_kernel picks the winner. One
+// block per row cannot pull a 600 KB row fast enough to stay out of a decode step's way.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ partial_v,
+                      int* __restrict__ partial_i, int vocab, int parts) {
+    grid_dependency_sync();
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    const int r = blockIdx.y, part = blockIdx.x;
+    const float* row = logits + (int64_t)r * vocab;
+    const int per = (vocab + parts - 1) / parts;
+    const int begin = part * per, end = begin + per < vocab ? begin + per : vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        best_v[warp] = bv;
+        best_i[warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) {
+                bv = best_v[w];
+                bi = best_i[w];
+            }
+        partial_v[r * parts + part] = bv;
+        partial_i[r * parts + part] = bi;
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ partial_v,
+                                    const int* __restrict__ partial_i, int* __restrict__ out,
+                                    int parts) {
+    grid_dependency_sync();
+    const int r = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int p = threadIdx.x; p < parts; p += 32) {
+        const float v = partial_v[r * parts + p];
+        const int i = partial_i[r * parts + p];
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
 // One block per row. Each thread owns a contiguous run of the vocabulary so that prefix
 // sums follow index order.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
@@ -178,9 +251,22 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 using namespace mb;
 
-MB_EXPORT int mb_argmax(const float* logits, int* out, int rows, int vocab, void* stream) {
+// `scratch`: room for rows * 64 floats and rows * 64 ints (8 bytes per slot), or null to use
+// the one-block-per-row kernel.
+MB_EXPORT int mb_argmax(const float* logits, int* out, int rows, int vocab, void* scratch,
+                        void* stream) {
     if (rows <= 0) return MB_OK;
     if (vocab <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    if (scratch && vocab >= 16384 && rows <= 65535) {
+        const int parts = 64;
+        float* pv = reinterpret_cast<float*>(scratch);
+        int* pi = reinterpret_cast<int*>(pv + (size_t)rows * parts);
+        MB_LAUNCH((argmax_partial_kernel), dim3(parts, rows), 256, 0, (cudaStream_t)stream, logits, pv,
+                  pi, vocab, parts);
+        MB_LAUNCH((argmax_merge_kernel), rows, 32, 0, (cudaStream_t)stream, (const float*)pv,
+                  (const int*)pi, out, parts);
+        return launch_status();
+    }
     MB_LAUNCH((argmax_kernel), rows, SAMPLE_THREADS, 0, (cudaStream_t)stream, logits, out, vocab);
     return launch_status();
 }

@@ -63,6 +63,7 @@ class CudaOps:
         self._counters: torch.Tensor | None = None   # zeroed tickets of the in-kernel split merge
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
+        self._argmax_scratch: torch.Tensor | None = None
         self._pinned_stream: int | None = None
         self.launches = 0
         self.library_calls = 0
@@ -337,9 +338,13 @@ class CudaOps:
         self.launches += 1 if splits == 1 else 2
 
     def argmax(self, logits, out):
-        check(self.lib.mb_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
-                                 self._stream()), "argmax")
-        self.launches += 1
+        rows = logits.shape[0]
+        if self._argmax_scratch is None or self._argmax_scratch.numel() < rows * 128:
+            self._argmax_scratch = torch.empty(max(rows, 64) * 128, dtype=torch.float32,
+                                               device=self.device)
+        check(self.lib.mb_argmax(_ptr(logits), _ptr(out), rows, logits.shape[1],
+                                 _ptr(self._argmax_scratch), self._stream()), "argmax")
+        self.launches += 2 if logits.shape[1] >= 16384 else 1
 
     def sample(self, logits, temperature, top_p, u, out):
         check(self.lib.mb_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(out),

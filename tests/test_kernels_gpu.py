@@ -437,9 +437,11 @@ def test_attention_refuses_what_it_cannot_do(ops):
 
 # ------------------------------------------------------------------------------ sampling
 
-def test_argmax_lowest_index_wins(ops):
-    logits = rand((9, 1517), torch.float32, 11)
+@pytest.mark.parametrize("vocab", [1517, 151936])
+def test_argmax_lowest_index_wins(ops, vocab):
+    logits = rand((9, vocab), torch.float32, 11)
     logits[3, 700] = logits[3, 20] = 50.0
+    logits[5, vocab - 1] = 60.0
     out = torch.empty(9, dtype=torch.int32, device="cuda")
     ops.argmax(logits, out)
     assert out.tolist() == torch.argmax(logits, dim=-1).tolist()
