@@ -177,9 +177,9 @@ def decode_rate(torch, runner, batch, context, vocab, steps, warmup):
 
     for _ in range(warmup):
         one()
-    before = runner.ops.launches + runner.ops.library_calls
+    before = runner.launch_count()
     ms = timed(torch, one, steps)
-    launches = (runner.ops.launches + runner.ops.library_calls - before) / steps
+    launches = (runner.launch_count() - before) / steps
     for s in seqs:
         runner.close(s)
     return batch * 1e3 / ms, ms, launches

@@ -158,11 +158,15 @@ template <int NT, int EPI, bool NORM>
 __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyInput in,
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ bias, void* __restrict__ out,
-                                   int T, int N, int K, int half_n, int rowt, int ksplit) {
+                                   int T, int N, int K, int half_n, int rowt, int ksplit,
+                                   const __nv_bfloat16* __restrict__ next_norm_w, float next_eps,
+                                   __nv_bfloat16* __restrict__ next_normed,
+                                   int* __restrict__ ticket) {
     grid_dependency_sync();
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
     __shared__ float rstd_s[TOK];
+    __shared__ int is_last;
     if (NORM) {
         skinny_row_rstd(in, T, K, rstd_s);
         __syncthreads();
@@ -221,6 +225,42 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
                 reinterpret_cast<float*>(out)[(int64_t)tok * N + n] += v;
             else
                 reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+        }
+    }
+    if (EPI == 3 && next_norm_w != nullptr) {
+        // The block that finishes last sees the whole updated stream and normalises its T
+        // rows for the product that follows, which saves the norm's own launch.
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int t = atomicAdd(ticket, 1);
+            is_last = t == (int)gridDim.x - 1;
+            if (is_last) *ticket = 0;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        const float* h = reinterpret_cast<const float*>(out);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+        for (int tok = warp; tok < T; tok += warps) {
+            const float* row = h + (int64_t)tok * N;
+            float ss = 0.f;
+            for (int k = lane * 4; k < N; k += 128) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / (float)N + next_eps);
+            for (int k = lane * 4; k < N; k += 128) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
+                const uint2 wq = *reinterpret_cast<const uint2*>(next_norm_w + k);
+                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.x));
+                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.y));
+                uint2 oq;
+                oq.x = pack2(v.x * rstd * w0.x, v.y * rstd * w0.y);
+                oq.y = pack2(v.z * rstd * w1.x, v.w * rstd * w1.y);
+                *reinterpret_cast<uint2*>(next_normed + (int64_t)tok * N + k) = oq;
+            }
         }
     }
 }
@@ -375,22 +415,28 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, true>, smem);                           \
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, true>), blocks, threads, smem, s, in,    \
-                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit);    \
+                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
+                          (const bf*)next_w, next_eps, (bf*)next_out, ticket);                   \
         } else {                                                                                 \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, false>), blocks, threads, smem, s, in,   \
-                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit);    \
+                          (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
+                          (const bf*)next_w, next_eps, (bf*)next_out, ticket);                   \
         }                                                                                        \
     } while (0)
 
 // The activations are either `x` (bfloat16 [T, K]) or, when `norm_w` is given, the float32
 // stream `h` [*, K] normalised with `norm_w` and `eps`, rows picked by `rows` if not null.
 // mode: 0 = bfloat16 out, 1 = float32 out, 3 = add into the float32 rows of `out`.
-// bias may be null.
+// bias may be null. With mode 3 and `next_w` given, the last block to finish also writes
+// RMSNorm(out rows) * next_w as bfloat16 into `next_out` [T, N]; `ticket` is one zeroed
+// int on the device (left zeroed); N must then be a multiple of 4.
 MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, const int* rows,
                              float eps, const void* w, const void* bias, void* out, int mode, int T,
-                             int N, int K, void* stream) {
+                             int N, int K, const void* next_w, float next_eps, void* next_out,
+                             int* ticket, void* stream) {
+    if (next_w && (mode != 3 || !next_out || !ticket || N % 4)) return MB_ERR_UNSUPPORTED_SIZE;
     if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
     if (mode != 0 && mode != 1 && mode != 3) return MB_ERR_BAD_DTYPE;
     typedef __nv_bfloat16 bf;
@@ -430,6 +476,10 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     const int threads = rowt * ksplit * 32;
     const int N = 2 * width, half_n = width;
     const void* bias = nullptr;
+    const void* next_w = nullptr;
+    void* next_out = nullptr;
+    int* ticket = nullptr;
+    const float next_eps = 0.f;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);

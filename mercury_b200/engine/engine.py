@@ -150,12 +150,12 @@ class Engine:
         page = self.cache.page_size
         for e in plan.entries:
             r = e.request
-            tokens = r.tokens
             hashes = None
             if self.sched.prefix_caching:
-                extend_hashes(r.hashes, tokens, page, self.cfg.cryptographic_hashes)
+                if r.seq_len // page > len(r.hashes):
+                    extend_hashes(r.hashes, r.tokens, page, self.cfg.cryptographic_hashes)
                 hashes = r.hashes
-            entries.append(StepEntry(r.seq, tokens[e.start:e.start + e.count],
+            entries.append(StepEntry(r.seq, r.token_slice(e.start, e.count),
                                      [e.count - 1] if e.samples else [], hashes))
             if e.samples:
                 sampling.append(r)

@@ -43,6 +43,15 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt + self.out
 
+    def token_slice(self, start: int, count: int) -> list[int]:
+        """tokens[start : start + count] without building the whole list."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.out[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.out[:start + count - n]
+
     @property
     def seq_len(self) -> int:
         return len(self.prompt) + len(self.out)

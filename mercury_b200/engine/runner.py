@@ -53,6 +53,7 @@ class StepContext:
         self.page_size = page_size
         self.dtype = dtype
         self.batch: StepBatch | None = None
+        self.prenormed = None      # (norm part, its output) left by the product before it
 
     def buffer(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
         return self.workspace.get(name, rows, cols, dtype)
@@ -128,6 +129,7 @@ class ModelRunner:
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and self.model.capturable
         self._graphs: dict[int, tuple] = {}
         self.graph_replays = 0
+        self.graph_launches = 0      # kernels run by replayed graphs
 
     # ------------------------------------------------------------------ sizes
 
@@ -193,6 +195,12 @@ class ModelRunner:
             self.cache.advance(e.seq, e.seq.num_computed + len(e.tokens), e.hashes)
         self.steps += 1
 
+    def launch_count(self, replayed: bool = True) -> int:
+        """Kernels launched so far by this runner's kernel set: its own and the library's,
+        and (with `replayed`) those inside replayed graphs, which no Python call sees."""
+        direct = getattr(self.ops, "launches", 0) + getattr(self.ops, "library_calls", 0)
+        return direct + (self.graph_launches if replayed else 0)
+
     # ------------------------------------------------------------------ decode graphs
 
     def _bucket(self, count: int) -> int:
@@ -226,12 +234,15 @@ class ModelRunner:
             self.run(batch)                       # warm-up: allocates buffers, loads kernels
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
+            before = self.launch_count(replayed=False)
             with torch.cuda.graph(graph):
                 logits = self.run(batch)
-            held = self._graphs[bucket] = (graph, logits)
-        graph, logits = held
+            kernels = self.launch_count(replayed=False) - before
+            held = self._graphs[bucket] = (graph, logits, kernels)
+        graph, logits, kernels = held
         graph.replay()
         self.graph_replays += 1
+        self.graph_launches += kernels
         self.finish(entries)
         if not wanted:
             return None

@@ -47,6 +47,12 @@ class CudaOps:
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
         # the Qwen2 shapes, so the fusion is off unless asked for.
         self.fuse_norm = False
+        # The product that adds into the stream can let its last block compute the norm
+        # that follows (one launch less per norm). Measured on B200 inside a captured decode
+        # step this is slower than the separate norm kernel (one block works alone at the
+        # end of every product), so it is off unless asked for.
+        self.fuse_next_norm = False
+        self._norm_ticket: torch.Tensor | None = None
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
                               "no CPU path")
@@ -145,19 +151,33 @@ class CudaOps:
             return _ptr(x), None, None, None, 0.0
         return None, _ptr(pending.h), _ptr(pending.weight), _ptr(pending.rows), float(pending.eps)
 
-    def linear_residual(self, x, weight, bias, h, ctx, name):
+    def linear_residual(self, x, weight, bias, h, ctx, name, then_norm=None):
         """h += x . weight^T (+ bias) in the float32 stream when the few-token kernel takes
         the shape (returns None); otherwise the product lands in the buffer `name` and is
-        returned for the next norm to add."""
+        returned for the next norm to add. `then_norm` names the norm part that follows
+        (it has `weight`, `eps`, `size`): the kernel's last block then also leaves that
+        norm's output in `ctx.prenormed`, where the norm part picks it up instead of
+        launching."""
         m, k = x.shape
         n = weight.shape[0]
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                 and (bias is None or bias.dtype == torch.bfloat16) and h.dtype == torch.float32
                 and self.lib.mb_gemm_skinny_supports(m, n, k)):
-            check(self.lib.mb_gemm_skinny(_ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(bias),
-                                          _ptr(h), 3, m, n, k, self._stream()),
-                  "linear_residual (skinny)")
+            fuse = (then_norm is not None and self.fuse_next_norm and n % 4 == 0
+                    and getattr(then_norm, "size", None) == n
+                    and getattr(then_norm, "weight", None) is not None
+                    and then_norm.weight.dtype == torch.bfloat16)
+            normed = ctx.buffer("normed", m, n) if fuse else None
+            if fuse and self._norm_ticket is None:
+                self._norm_ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
+            check(self.lib.mb_gemm_skinny(
+                _ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(bias), _ptr(h), 3, m, n, k,
+                _ptr(then_norm.weight) if fuse else None, float(then_norm.eps) if fuse else 0.0,
+                _ptr(normed), _ptr(self._norm_ticket) if fuse else None, self._stream()),
+                "linear_residual (skinny)")
             self.launches += 1
+            if fuse:
+                ctx.prenormed = (then_norm, normed)
             return None
         out = ctx.buffer(name, m, n)
         self.linear(x, weight, bias, out)
@@ -176,7 +196,7 @@ class CudaOps:
         if all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k):
             check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
                                           _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
-                                          self._stream()),
+                                          None, 0.0, None, None, self._stream()),
                   "linear (skinny)")
             self.launches += 1
             return

@@ -118,7 +118,16 @@ class Model:
                 k, v = kv_layers[call.cache]
                 group = self.cache_layers[call.cache].group
                 cache = LayerCache(k, v, ctx.page_size, batch.tables[group], call.writes_cache)
-            delta = block.forward(h, delta, ctx, cache, states.get(index))
+            # the norm that opens the next call's block, which this block's last product
+            # may compute ahead (the final norm picks rows, so it is left alone)
+            following = None
+            if index + 1 < len(self.spec.schedule):
+                nxt = self.blocks[self.spec.schedule[index + 1].block]
+                following = getattr(nxt, "first_norm", lambda: None)()
+            if following is not None:
+                delta = block.forward(h, delta, ctx, cache, states.get(index), next_norm=following)
+            else:
+                delta = block.forward(h, delta, ctx, cache, states.get(index))
         if batch.num_logit_rows == 0:
             return None
         rows = self.final_norm.add_norm(h, delta, ctx, rows=batch.logit_rows, defer=True)

@@ -87,7 +87,7 @@ class GroupedQueryAttention(Mixer):
         self.out_b = setup.place(tensors[p + "o_proj.bias"]) if self.out_bias else None
         self.position.load(tensors, setup)
 
-    def forward(self, x, ctx, cache, state, residual=None):
+    def forward(self, x, ctx, cache, state, residual=None, then_norm=None):
         tokens = x.shape[0]
         ops = ctx.ops
         qkv = ctx.buffer("qkv", tokens, self.q_size + 2 * self.kv_size)
@@ -110,7 +110,7 @@ class GroupedQueryAttention(Mixer):
         )
         if residual is not None:
             return ops.linear_residual(attended, self.out_weight, self.out_b, residual, ctx,
-                                       "mixer_out")
+                                       "mixer_out", then_norm=then_norm)
         out = ctx.buffer("mixer_out", tokens, self.hidden_size)
         ops.linear(attended, self.out_weight, self.out_b, out)
         return out

@@ -28,8 +28,9 @@ Two optional protocols let a mixer or feed-forward fuse with its neighbours; a p
 declares neither is handed a plain tensor and returns its output, as above.
     accepts_pending_norm = True    x may be a `PendingNorm` (parts/norm.py): the norm before
                                    the part has not run, the part's first kernel does it
-    adds_to_residual = True        forward(..., residual=h) may add the output into the
-                                   float32 stream itself and return None
+    adds_to_residual = True        forward(..., residual=h, then_norm=norm) may add the output
+                                   into the float32 stream itself and return None; it may
+                                   also leave `then_norm`'s output in `ctx.prenormed`
 
 Norm (`register_norm`):
     add_norm(h, delta, ctx, rows=None, defer=False) -> Tensor | PendingNorm
@@ -43,7 +44,9 @@ PositionEncoding (`register_position_encoding`):
     apply(qkv, layout, ctx)                   for encodings the fused kernel does not cover
 
 Arrangement (`register_arrangement`): how mixer, feed-forward and norms sit in a block.
-    forward(h, delta, ctx, cache, state) -> Tensor   returns the new pending delta
+    forward(h, delta, ctx, cache, state) -> Tensor   returns the new pending delta (None if
+                                              it is already in the stream); an arrangement
+                                              with `first_norm()` also takes `next_norm=`
 """
 
 from __future__ import annotations

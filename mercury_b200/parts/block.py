@@ -21,18 +21,23 @@ class PreNormBlock:
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
-    def forward(self, h, delta, ctx, cache, state):
+    def first_norm(self):
+        """The norm that opens this block (what the block before may compute ahead)."""
+        return self.mixer_norm
+
+    def forward(self, h, delta, ctx, cache, state, next_norm=None):
         mixer, ff = self.mixer, self.feed_forward
         x = self.mixer_norm.add_norm(h, delta, ctx,
                                      defer=getattr(mixer, "accepts_pending_norm", False))
         if getattr(mixer, "adds_to_residual", False):
-            mixed = mixer.forward(x, ctx, cache, state, residual=h)
+            mixed = mixer.forward(x, ctx, cache, state, residual=h,
+                                  then_norm=self.feed_forward_norm)
         else:
             mixed = mixer.forward(x, ctx, cache, state)
         x = self.feed_forward_norm.add_norm(h, mixed, ctx,
                                             defer=getattr(ff, "accepts_pending_norm", False))
         if getattr(ff, "adds_to_residual", False):
-            return ff.forward(x, ctx, residual=h)
+            return ff.forward(x, ctx, residual=h, then_norm=next_norm)
         return ff.forward(x, ctx)
 
 

@@ -39,12 +39,13 @@ class GatedFeedForward(FeedForward):
         self.gate_up_weight = torch.cat([gate.to(widest), up.to(widest)], dim=0).contiguous()
         self.down_weight = setup.place(tensors[p + "down_proj.weight"])
 
-    def forward(self, x, ctx, residual=None):
+    def forward(self, x, ctx, residual=None, then_norm=None):
         tokens = x.shape[0]
         act = ctx.buffer("ff_act", tokens, self.intermediate_size)
         ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx)
         if residual is not None:
-            return ctx.ops.linear_residual(act, self.down_weight, None, residual, ctx, "ff_out")
+            return ctx.ops.linear_residual(act, self.down_weight, None, residual, ctx, "ff_out",
+                                           then_norm=then_norm)
         out = ctx.buffer("ff_out", tokens, self.hidden_size)
         ctx.ops.linear(act, self.down_weight, None, out)
         return out

@@ -49,6 +49,11 @@ class RMSNorm(Norm):
     def add_norm(self, h, delta, ctx, rows=None, defer=False):
         """`defer=True` says that the consumer takes a `PendingNorm`; one is returned when
         nothing has to be added first and the kernels can fuse the norm for this many rows."""
+        pre = getattr(ctx, "prenormed", None)
+        if pre is not None:
+            ctx.prenormed = None
+            if pre[0] is self and delta is None and rows is None:
+                return pre[1]      # the product before this norm already left its output
         count = h.shape[0] if rows is None else rows.shape[0]
         if (defer and delta is None
                 and getattr(ctx.ops, "can_fuse_norm", lambda *a: False)(count, self.size, self.weight)):

@@ -46,7 +46,7 @@ class TorchOps:
     def _x(x):
         return x.materialize() if hasattr(x, "materialize") else x
 
-    def linear_residual(self, x, weight, bias, h, ctx, name):
+    def linear_residual(self, x, weight, bias, h, ctx, name, then_norm=None):
         y = self._x(x).to(self.acc) @ weight.to(self.acc).T
         if bias is not None:
             y = y + bias.to(self.acc)

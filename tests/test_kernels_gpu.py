@@ -190,12 +190,40 @@ def test_linear_residual(ops, twin, m, n, k):
     assert float((result - want).abs().max() / want.abs().max()) <= tol
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 896, 896), (8, 896, 4864), (16, 1536, 320), (3, 64, 128)])
+def test_linear_residual_leaves_the_next_norm(ops, twin, m, n, k):
+    """The last block of the product also normalises the updated stream; twice in a row, as
+    the ticket must come back to zero."""
+    from mercury_b200.kernels.ops import CudaOps
+
+    ops = CudaOps("cuda")
+    ops.fuse_next_norm = True
+    norm = SimpleNamespace(weight=rand((n,), torch.bfloat16, 61, 0.1) + 1, eps=1e-6, size=n)
+    for seed in (35, 36):
+        x = rand((m, k), torch.bfloat16, seed)
+        w = rand((n, k), torch.bfloat16, seed + 10, 0.1)
+        h = rand((m, n), torch.float32, seed + 20)
+        h_want = (h.double() + x.double() @ w.double().T).float()
+        ctx = fake_ctx(ops)
+        ctx.prenormed = None
+        assert ops.linear_residual(x, w, None, h, ctx, "tmp", then_norm=norm) is None
+        assert ctx.prenormed is not None and ctx.prenormed[0] is norm
+        want = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        twin.add_rmsnorm(h_want.clone(), None, norm.weight, norm.eps, want)
+        got = ctx.prenormed[1]
+        assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 2.0 ** -7
+        assert float((h.double() - h_want.double()).abs().max() / h_want.abs().max()) <= 2 * k ** 0.5 * 2.0 ** -24
+
+
 @pytest.mark.parametrize("m,hidden", [(1, 896), (8, 896), (13, 1536), (16, 320)])
 def test_products_that_normalise_their_own_input(ops, twin, m, hidden):
     """linear, linear_swiglu and qkv_rope_store given a PendingNorm against the same ops given
     the norm's output."""
+    from mercury_b200.kernels.ops import CudaOps
     from mercury_b200.parts.norm import PendingNorm
 
+    ops = CudaOps("cuda")
+    ops.fuse_norm = True
     h = rand((m + 3, hidden), torch.float32, 41)
     norm_w = rand((hidden,), torch.bfloat16, 42, 0.1) + 1
     ctx = fake_ctx(ops)
