@@ -31,6 +31,13 @@ WIDTHS = {
 }
 LENGTHS = (150, 70, 97, 40, 130)
 MAX_TOKENS = 384
+# bfloat16 at these widths: the plain PyTorch twin of the kernels (float32 arithmetic,
+# bfloat16 storage between kernels, run on the CPU through the same step function) is
+# itself off from the float64 oracle by up to 1.3e-2 (0.5B widths) and 2.3e-2 (1.5B widths)
+# of the largest logit on these requests: rounding to 8 bits grows with the width and the
+# maximum is taken over a vocabulary of 151936. The engine is held to 1.75 times the twin's
+# worst figure; the tiny models keep 2e-2.
+BF16_TOLERANCE = 4e-2
 
 
 @lru_cache(maxsize=None)
@@ -67,4 +74,5 @@ def test_real_widths(name, dtype, monkeypatch):
         runner = ModelRunner(config=config, tensors=tensors, dtype=dtype, device="cuda", page_size=16,
                              num_pages=MAX_TOKENS // 16, max_seqs=4, max_step_tokens=MAX_TOKENS,
                              max_model_len=MAX_TOKENS)
-        replay_check.run_and_check(runner, name, LENGTHS, steps, rows, dtype)
+        replay_check.run_and_check(runner, name, LENGTHS, steps, rows, dtype,
+                                   BF16_TOLERANCE if dtype == torch.bfloat16 else None)
