@@ -329,9 +329,38 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         int* __restrict__ counters, int n_q, int n_kv, int page_size, float scale,
                         int window, int num_splits) {
-    grid_dependency_sync();
     constexpr int CH = D / 8;
     constexpr int STAGES = 3;
+    // Before waiting for the kernel in front (which stores this step's keys): ask L2 for the
+    // keys and values of this block's tiles. Lengths and block tables were copied to the
+    // device before the step began, and all but the newest key are from earlier steps.
+    {
+        const int seq_ = blockIdx.x, kvh_ = blockIdx.y;
+        const int q_len_ = q_start[seq_ + 1] - q_start[seq_];
+        if (q_len_ > 0 && (threadIdx.x & 1) == 0) {
+            const int kv_len_ = kv_len_of[seq_];
+            int lo = 0;
+            if (window > 0 && kv_len_ - q_len_ - window + 1 > 0) lo = (kv_len_ - q_len_ - window + 1) / MMA_BN;
+            int hi = (kv_len_ - 1) / MMA_BN + 1;
+            if (num_splits > 1) {
+                const int per = (hi - lo + num_splits - 1) / num_splits;
+                lo = lo + (int)blockIdx.z * per;
+                if (lo + per < hi) hi = lo + per;
+            }
+            for (int kt = lo; kt < hi; ++kt) {
+                const int key = kt * MMA_BN + (threadIdx.x >> 1);
+                if (key >= kv_len_) continue;
+                const int page = table[(int64_t)seq_ * max_pages + key / page_size];
+                if (page < 0) continue;
+                const int64_t at = (((int64_t)page * n_kv + kvh_) * page_size + (key % page_size)) * D;
+                for (int b = 0; b < D * 2; b += 128) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(k_pages + at) + b));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(v_pages + at) + b));
+                }
+            }
+        }
+    }
+    grid_dependency_sync();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][D]
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]

@@ -135,6 +135,22 @@ __device__ __forceinline__ void skinny_mainloop(const SkinnyInput& in, const flo
     }
 }
 
+// Ask L2 for this warp's share of the weight rows. Issued before the kernel waits for its
+// predecessor (weights do not depend on it), so that with programmatic dependent launch the
+// weight stream overlaps the tail of the kernel before.
+__device__ __forceinline__ void skinny_prefetch_weights(const __nv_bfloat16* __restrict__ w, int n0,
+                                                        int K, int c_begin, int c_end) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    // one 128-byte line holds two chunks of a row: lanes with t4 == 0 cover the even chunks
+    if (t4 != 0) return;
+    const __nv_bfloat16* wa = w + (int64_t)(n0 + g) * K;
+    const __nv_bfloat16* wb = w + (int64_t)(n0 + g + 8) * K;
+    for (int c = c_begin; c < c_end; c += 2) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + c * 32));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + c * 32));
+    }
+}
+
 // Every warp leaves its 16 x (8 NT) partial tile in shared memory: red[warp][row][token].
 template <int NT>
 __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT][4]) {
@@ -162,15 +178,10 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
                                    const __nv_bfloat16* __restrict__ next_norm_w, float next_eps,
                                    __nv_bfloat16* __restrict__ next_normed,
                                    int* __restrict__ ticket) {
-    grid_dependency_sync();
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
     __shared__ float rstd_s[TOK];
     __shared__ int is_last;
-    if (NORM) {
-        skinny_row_rstd(in, T, K, rstd_s);
-        __syncthreads();
-    }
     const int warp = threadIdx.x >> 5;
     const int rt = warp / ksplit, ks = warp - rt * ksplit;
     int n0;  // first weight row of this warp's tile
@@ -181,6 +192,16 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
         n0 = (blockIdx.x * rowt + rt) * 16;
     }
     const int limit = EPI == 2 ? ((rt & 1) + 1) * half_n : N;
+    if (n0 < limit) {
+        const int chunks = K / 32;
+        const int per = (chunks + ksplit - 1) / ksplit;
+        skinny_prefetch_weights(w, n0, K, ks * per, ks * per + per < chunks ? ks * per + per : chunks);
+    }
+    grid_dependency_sync();
+    if (NORM) {
+        skinny_row_rstd(in, T, K, rstd_s);
+        __syncthreads();
+    }
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
@@ -283,8 +304,15 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
                                        __nv_bfloat16* __restrict__ k_pages,
                                        __nv_bfloat16* __restrict__ v_pages, int T, int K, int n_q,
                                        int n_kv, int page_size, int store, int ksplit) {
-    grid_dependency_sync();
     constexpr int ROWT = D / 16;
+    {
+        const int w_ = threadIdx.x >> 5;
+        const int rt_ = w_ / ksplit, ks_ = w_ - rt_ * ksplit;
+        const int chunks_ = K / 32, per_ = (chunks_ + ksplit - 1) / ksplit;
+        skinny_prefetch_weights(w, blockIdx.x * D + rt_ * 16, K, ks_ * per_,
+                                ks_ * per_ + per_ < chunks_ ? ks_ * per_ + per_ : chunks_);
+    }
+    grid_dependency_sync();
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];          // [ROWT * ksplit][16][TOK]
     float* val = red + ROWT * ksplit * 16 * TOK;  // [TOK][D]

@@ -235,8 +235,20 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = self.launch_count(replayed=False)
-            with torch.cuda.graph(graph):
-                logits = self.run(batch)
+            # Inside a captured decode step every kernel may be scheduled while the one in
+            # front drains (programmatic dependent launch): the kernels prefetch weights and
+            # cached keys before they wait. Prompt steps run without it: their grids are
+            # larger than the device and early blocks would only take room (the same holds
+            # for decode batches beyond 16, whose products are the library's).
+            dependent = getattr(self.ops, "set_dependent_launch", None) if bucket <= 16 else None
+            if dependent is not None:
+                dependent(True)
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.run(batch)
+            finally:
+                if dependent is not None:
+                    dependent(False)
             kernels = self.launch_count(replayed=False) - before
             held = self._graphs[bucket] = (graph, logits, kernels)
         graph, logits, kernels = held

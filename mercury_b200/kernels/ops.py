@@ -62,6 +62,7 @@ class CudaOps:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}x")
         self.lib = library.load()
         # let each kernel be scheduled while its predecessor drains (see csrc/common.cuh)
+        self.dependent_launch = bool(dependent_launch)     # True: on every launch, not only in graphs
         self.lib.mb_set_dependent_launch(int(dependent_launch))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_splits = decode_splits
@@ -82,6 +83,11 @@ class CudaOps:
         if self._pinned_stream is not None:
             return self._pinned_stream
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def set_dependent_launch(self, enabled: bool) -> None:
+        """Launch the kernels that follow with (or without) the programmatic-serialization
+        attribute; see csrc/common.cuh."""
+        self.lib.mb_set_dependent_launch(int(bool(enabled) or self.dependent_launch))
 
     def pin_stream(self) -> None:
         """Look the current stream up once for the many launches of a step."""
