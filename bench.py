@@ -123,13 +123,15 @@ def model_numbers(cfg: dict) -> dict:
             "attn_flops": lambda t: 2 * t * t * n_q * d * layers, "head_flops_per_row": 2 * head}
 
 
-def make_runner(torch, config, tensors, batch, page_tokens, graphs=True):
+def make_runner(torch, config, tensors, batch, page_tokens, graphs=True, gemm=None):
     from mercury_b200.engine.runner import ModelRunner
+    from mercury_b200.kernels.ops import CudaOps
 
+    ops = CudaOps("cuda", gemm=gemm) if gemm else None
     return ModelRunner(config=config, tensors=tensors, dtype=torch.bfloat16, device="cuda",
                        page_size=BLOCK, num_pages=page_tokens // BLOCK, max_seqs=batch,
                        max_step_tokens=max(PREFILL_TOKENS, batch), max_model_len=MODEL_LEN,
-                       cuda_graphs=graphs)
+                       cuda_graphs=graphs, ops=ops)
 
 
 def timed(torch, fn, reps: int) -> float:
@@ -319,7 +321,7 @@ def run_part(args) -> dict:
     tensors = random_tensors(config, SEED, torch.bfloat16)
     batch = args.batch
     runner = make_runner(torch, config, tensors, max(batch, 2), max(batch, 2) * (CONTEXT + 256),
-                         graphs=not args.no_graphs)
+                         graphs=not args.no_graphs, gemm=args.gemm)
     if args.only == "prefill":
         return {"prefill_ms": round(prefill_rate(torch, runner, vocab, reps=args.steps), 3)}
     rate, ms, launches = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps, args.warmup)
@@ -393,6 +395,8 @@ def main() -> int:
                    help="run one part only (for profilers); prints its own small JSON")
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")
     p.add_argument("--no-graphs", action="store_true", help="launch kernels one by one")
+    p.add_argument("--gemm", default=None, choices=("library", "tcgen05", "auto"),
+                   help="many-token product of --only prefill/decode (default: the engine's)")
     args = p.parse_args()
     if args.gpus != 1:
         print("bench.py measures a single-GPU engine; --gpus must be 1", flush=True)

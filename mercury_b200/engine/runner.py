@@ -130,6 +130,9 @@ class ModelRunner:
         self._graphs: dict[int, tuple] = {}
         self.graph_replays = 0
         self.graph_launches = 0      # kernels run by replayed graphs
+        self._shape_graphs: dict[tuple, tuple] = {}   # other steps, by the shape of the batch
+        self._shape_seen: dict[tuple, int] = {}
+        self.max_shape_graphs = 16
 
     # ------------------------------------------------------------------ sizes
 
@@ -262,6 +265,40 @@ class ModelRunner:
             return logits[:len(entries)]
         return logits[torch.tensor(wanted, device=self.device)]
 
+    def _step_with_shape_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
+        """Steps other than pure decoding are captured per batch shape: the launch sequence
+        of a step depends only on (tokens, sequences, longest portion, wanted rows), and a
+        server cutting prompts into portions of one size sees the same shapes again and
+        again. A shape is captured the second time it is seen; at most `max_shape_graphs`
+        are kept. Without this a 2048-token step is bound by the Python launch loop."""
+        tokens, seqs, _max_q, rows = key
+        batch = self.prepare(entries, token_capacity=tokens, seq_capacity=seqs,
+                             page_capacity=self.max_pages)
+        batch.attention_splits = self._graph_splits(seqs)
+        held = self._shape_graphs.get(key)
+        if held is None:
+            if len(self._shape_graphs) >= self.max_shape_graphs:
+                self._shape_graphs.pop(next(iter(self._shape_graphs)))
+            self.run(batch)                       # warm-up outside the capture
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = self.launch_count(replayed=False)
+            with torch.cuda.graph(graph):
+                logits = self.run(batch)
+            kernels = self.launch_count(replayed=False) - before
+            held = self._shape_graphs[key] = (graph, logits, kernels)
+        graph, logits, kernels = held
+        graph.replay()
+        self.graph_replays += 1
+        self.graph_launches += kernels
+        if getattr(self.ops, "gemm", "library") != "library":
+            self.ops._tc_pending = True            # the graph may hold tcgen05 products
+        check = getattr(self.ops, "check_errors", None)
+        if check is not None:
+            check()
+        self.finish(entries)
+        return logits if rows else None
+
     @torch.inference_mode()
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run exactly the tokens given, as one batch, from the cache that earlier steps
@@ -271,6 +308,14 @@ class ModelRunner:
         if (self.use_graphs and len(entries) <= self.max_seqs
                 and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries)):
             return self._decode_with_graph(entries)
+        if self.use_graphs:
+            key = (sum(len(e.tokens) for e in entries), len(entries),
+                   max(len(e.tokens) for e in entries), sum(len(e.want) for e in entries))
+            if key in self._shape_graphs or self._shape_seen.get(key, 0) >= 1:
+                return self._step_with_shape_graph(entries, key)
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            self._shape_seen[key] = 1
         batch = self.prepare(entries)
         logits = self.run(batch)
         check = getattr(self.ops, "check_errors", None)

@@ -28,14 +28,14 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 class CudaOps:
-    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "library",
+    def __init__(self, device="cuda", decode_splits: int | None = None, gemm: str = "auto",
                  dependent_launch: bool = False):
         """`gemm` picks the bfloat16 product on many tokens: "tcgen05" (this package's
         TMA + tensor-memory kernel wherever it takes the shape), "library" (cuBLAS through
-        torch.mm, where the reference calls F.linear; the default, because inside a whole
-        prompt step it is still ahead of this package's first tcgen05 kernel), "auto"
-        (tcgen05 for the narrow products, where it wins when timed alone, the library for
-        the wide ones) or "simt" (the CUDA-core kernel). Few tokens always take the weight-streaming
+        torch.mm, where the reference calls F.linear), "auto" (the default: the gated gate/up
+        product with its SiLU epilogue on the persistent tcgen05 kernel, where fusing beats
+        library product plus gate kernel, and the plain products on the library, which is
+        still ahead there) or "simt" (the CUDA-core kernel). Few tokens always take the weight-streaming
         kernels. The float32 engine always runs the CUDA-core kernel: a library product
         would need its reduced-precision mode switched off process-wide to be a true 32-bit
         product."""
@@ -126,10 +126,16 @@ class CudaOps:
                                       _flag(out.dtype), self._stream()), "add_rmsnorm")
         self.launches += 1
 
+    def _error_word(self) -> torch.Tensor:
+        if self._tc_error is None:
+            self._tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._tc_error
+
     def check_errors(self) -> None:
         """Raise if a bounded wait inside a tcgen05 kernel ran out since the last check
         (reads one word from the device, so it synchronises)."""
-        if not self._tc_pending:
+        if not self._tc_pending or self._tc_error is None:
+            self._tc_pending = False
             return
         self._tc_pending = False
         code = int(self._tc_error.item())
@@ -210,14 +216,14 @@ class CudaOps:
             x = pending.materialize()
         self._rows(x)
         if all_bf16 and self.gemm in ("tcgen05", "auto") and self.lib.mb_gemm_tcgen05_supports(m, n, k):
-            # measured on B200: ahead of the library for M >= 256 with N, K up to about 2048
-            narrow = m >= 256 and n <= 2048 and k <= 2048
-            if self.gemm == "tcgen05" or narrow:
-                if self._tc_error is None:
-                    self._tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)
+            # Measured inside a 2048-token step on B200 (weights cold in L2) the library is
+            # ahead on the plain products (q/k/v 8.5 us, o 7.3 us, down 17 us against 12, 12
+            # and 33 us), so "auto" leaves them to it; the gated product is where this
+            # package's kernel wins (see linear_swiglu).
+            if self.gemm == "tcgen05":
                 check(self.lib.mb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out),
                                                int(out.dtype == torch.float32), m, n, k,
-                                               _ptr(self._tc_error), 0, self._stream()),
+                                               _ptr(self._error_word()), 0, self._stream()),
                       "linear (tcgen05)")
                 self.launches += 1
                 self._tc_pending = True
@@ -258,6 +264,15 @@ class CudaOps:
             return
         if self._pending(x) is not None:
             x = x.materialize()
+        if (self.gemm in ("tcgen05", "auto") and x.dtype == torch.bfloat16
+                and weight.dtype == torch.bfloat16 and m >= 256 and width % 8 == 0
+                and self.lib.mb_gemm_tcgen05_supports(m, width, k)):
+            check(self.lib.mb_gemm_tcgen05_persistent(_ptr(x), _ptr(weight), None, _ptr(out), 2, m,
+                                                      width, k, _ptr(self._error_word()),
+                                                      self._stream()), "linear_swiglu (tcgen05)")
+            self.launches += 1
+            self._tc_pending = True
+            return
         gate_up = ctx.buffer("gate_up", m, 2 * width)
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
