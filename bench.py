@@ -42,6 +42,14 @@ QWEN25_05B = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "use_sliding_window": False,
     "max_position_embeddings": 32768,
 }
+SIZES = {
+    "0.5b": QWEN25_05B,
+    "1.5b": {**QWEN25_05B, "num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12,
+             "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 8960},
+    "7b": {**QWEN25_05B, "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28,
+           "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 18944,
+           "vocab_size": 152064, "tie_word_embeddings": False},
+}
 BATCH = 8
 CONTEXT = 2048        # tokens each request holds when decoding starts
 MODEL_LEN = 4096      # benchmark context length: the most a request may reach
@@ -298,8 +306,11 @@ def run_part(args) -> dict:
     from mercury_b200.config import config_from_dict
     from mercury_b200.weights import random_tensors
 
-    _entry, config = config_from_dict(QWEN25_05B)
-    vocab = QWEN25_05B["vocab_size"]
+    if args.only == "mixed":
+        return run_mixed(args)
+    raw = SIZES[args.size]
+    _entry, config = config_from_dict(raw)
+    vocab = raw["vocab_size"]
     if args.only == "products":
         from mercury_b200.kernels.ops import CudaOps
 
@@ -327,6 +338,51 @@ def run_part(args) -> dict:
     rate, ms, launches = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps, args.warmup)
     return {"decode_tokens_per_s": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch,
             "launches_per_step": launches, "graphs": not args.no_graphs}
+
+
+def run_mixed(args) -> dict:
+    """`--only mixed`: 32 requests through Engine.generate, prompt lengths uniform in
+    [64, 2048], half of them sharing one 512-token prefix, 128 greedy tokens each (the
+    benchmark description's serving workload, by default at Qwen2.5-1.5B sizes)."""
+    import torch
+
+    from mercury_b200 import Engine, EngineConfig, SamplingParams
+    from mercury_b200.config import config_from_dict
+    from mercury_b200.engine.runner import ModelRunner
+    from mercury_b200.weights import random_tensors
+
+    raw = SIZES[args.size]
+    _entry, config = config_from_dict(raw)
+    tensors = random_tensors(config, SEED, torch.bfloat16)
+    gen = torch.Generator().manual_seed(SEED + 5)
+    shared = torch.randint(0, raw["vocab_size"], (512,), generator=gen).tolist()
+    prompts = []
+    for i in range(32):
+        n = int(torch.randint(64, 2049, (1,), generator=gen))
+        body = torch.randint(0, raw["vocab_size"], (n,), generator=gen).tolist()
+        prompts.append((shared + body[512:]) if (i % 2 == 0 and n > 512) else body)
+    pool_tokens = 32 * (2048 + 128 + BLOCK)
+    runner = ModelRunner(config=config, tensors=tensors, dtype=torch.bfloat16, device="cuda",
+                         page_size=BLOCK, num_pages=pool_tokens // BLOCK, max_seqs=32,
+                         max_step_tokens=4096, max_model_len=MODEL_LEN)
+    cfg = EngineConfig(model="(in memory)", dtype="bfloat16", block_size=BLOCK,
+                       num_blocks=pool_tokens // BLOCK, max_running=32, max_batched_tokens=4096,
+                       prefill_chunk=2048, max_model_len=MODEL_LEN, policy=args.policy, seed=SEED)
+    engine = Engine(cfg, runner=runner)
+    engine.generate([prompts[0][:64]], SamplingParams(ignore_eos=True), 4)      # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, SamplingParams(ignore_eos=True), 128)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    produced = sum(len(o) for o in outs)
+    snap = engine.snapshot()
+    return {"workload": "mixed: 32 requests, prompts 64..2048, 16 share a 512-token prefix, 128 tokens each",
+            "size": args.size, "policy": args.policy, "output_tokens": produced,
+            "prompt_tokens": sum(len(p) for p in prompts), "seconds": round(seconds, 3),
+            "output_tokens_per_s": round(produced / seconds, 1),
+            "prefix_hit_tokens": snap["cache"]["hit_tokens"], "steps": snap["engine"]["steps"],
+            "preemptions": snap["scheduler"]["preemptions"], "leaked_pages": engine.leaked_pages()}
 
 
 def run_reference(args) -> dict:
@@ -391,8 +447,11 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=64)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="mercury_b200", choices=("mercury_b200", "reference"))
-    p.add_argument("--only", default="all", choices=("all", "decode", "prefill", "products"),
-                   help="run one part only (for profilers); prints its own small JSON")
+    p.add_argument("--only", default="all", choices=("all", "decode", "prefill", "products", "mixed"),
+                   help="run one part only (for profilers and side workloads); prints its own JSON")
+    p.add_argument("--size", default=None, choices=tuple(SIZES),
+                   help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")
+    p.add_argument("--policy", default="lpm", choices=("fcfs", "lpm", "lpm_aging"))
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")
     p.add_argument("--no-graphs", action="store_true", help="launch kernels one by one")
     p.add_argument("--gemm", default=None, choices=("library", "tcgen05", "auto"),
@@ -401,6 +460,8 @@ def main() -> int:
     if args.gpus != 1:
         print("bench.py measures a single-GPU engine; --gpus must be 1", flush=True)
         return 2
+    if args.size is None:
+        args.size = "1.5b" if args.only == "mixed" else "0.5b"
     if args.only != "all":
         print(json.dumps(run_part(args)), flush=True)
         return 0

@@ -216,8 +216,9 @@ __global__ void add_rmsnorm_bf16_regs_kernel(float* __restrict__ h,
     }
 }
 
-// bfloat16, the whole head rotated, head size a multiple of 8: two pairs per thread
-// through 4-byte accesses, values copied in 16-byte pieces.
+// bfloat16, the whole head rotated, head size a multiple of 16: one warp per (token, head),
+// eight features per lane through 16-byte accesses (a lane holds features [8j, 8j+8) of the
+// first half and the matching eight of the second half, i.e. four pairs twice).
 __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
                                        const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t,
@@ -225,50 +226,61 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
                                        const int* __restrict__ seq_of_token,
                                        const int* __restrict__ table, int max_pages,
                                        __nv_bfloat16* __restrict__ k_pages,
-                                       __nv_bfloat16* __restrict__ v_pages, int n_q, int n_kv, int d,
-                                       int page_size, int store) {
+                                       __nv_bfloat16* __restrict__ v_pages, int tokens, int n_q,
+                                       int n_kv, int d, int page_size, int store) {
     grid_dependency_sync();
-    const int t = blockIdx.x;
+    const int heads = n_q + 2 * n_kv;
+    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp_global >= tokens * heads) return;
+    const int t = warp_global / heads, head = warp_global - t * heads;
     const int seq = seq_of_token[t];
     if (seq < 0) return;
     const int pos = positions[t];
-    const int half = d / 2, pairs2 = half / 2;
-    const int64_t row = (int64_t)t * (n_q + 2 * n_kv) * d;
-    int64_t slot = -1;
-    if (store) {
+    const int half = d / 2;
+    __nv_bfloat16* x = qkv + (int64_t)t * heads * d + (int64_t)head * d;
+    __nv_bfloat16* dst = nullptr;
+    if (head >= n_q && store) {
         const int page = table[(int64_t)seq * max_pages + pos / page_size];
-        if (page >= 0) slot = (int64_t)page * n_kv * page_size + pos % page_size;
+        if (page >= 0) {
+            const bool is_k = head < n_q + n_kv;
+            const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+            dst = (is_k ? k_pages : v_pages) +
+                  (((int64_t)page * n_kv + kvh) * page_size + pos % page_size) * d;
+        }
     }
-    for (int w = threadIdx.x; w < (n_q + n_kv) * pairs2; w += blockDim.x) {
-        const int head = w / pairs2;
-        const int i = (w - head * pairs2) * 2;
-        __nv_bfloat16* x = qkv + row + (int64_t)head * d;
-        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i));
-        float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + i + half));
+    if (head >= n_q + n_kv) {                    // a value head: copy
+        if (dst)
+            for (int c = lane * 8; c < d; c += 256)
+                *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(x + c);
+        return;
+    }
+    for (int i = lane * 8; i < half; i += 256) {
+        uint4 aq = *reinterpret_cast<const uint4*>(x + i);
+        uint4 bq = *reinterpret_cast<const uint4*>(x + i + half);
         if (cos_t) {
-            const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)pos * half + i);
-            const float2 sn = *reinterpret_cast<const float2*>(sin_t + (int64_t)pos * half + i);
-            const float2 ra = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
-            const float2 rb = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
-            a = ra;
-            b = rb;
+            __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&aq);
+            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&bq);
+            const float* cp = cos_t + (int64_t)pos * half + i;
+            const float* sp = sin_t + (int64_t)pos * half + i;
+            const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(a2[e]), b = __bfloat1622float2(b2[e]);
+                a2[e] = __floats2bfloat162_rn(a.x * cs[2 * e] - b.x * sn[2 * e],
+                                              a.y * cs[2 * e + 1] - b.y * sn[2 * e + 1]);
+                b2[e] = __floats2bfloat162_rn(b.x * cs[2 * e] + a.x * sn[2 * e],
+                                              b.y * cs[2 * e + 1] + a.y * sn[2 * e + 1]);
+            }
         }
-        const __nv_bfloat162 ta = __floats2bfloat162_rn(a.x, a.y), tb = __floats2bfloat162_rn(b.x, b.y);
-        *reinterpret_cast<__nv_bfloat162*>(x + i) = ta;
-        *reinterpret_cast<__nv_bfloat162*>(x + i + half) = tb;
-        if (head >= n_q && slot >= 0) {
-            __nv_bfloat16* dst = k_pages + (slot + (int64_t)(head - n_q) * page_size) * d;
-            *reinterpret_cast<__nv_bfloat162*>(dst + i) = ta;
-            *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = tb;
-        }
-    }
-    if (slot >= 0) {
-        const __nv_bfloat16* v = qkv + row + (int64_t)(n_q + n_kv) * d;
-        const int chunks = d / 8;
-        for (int w = threadIdx.x; w < n_kv * chunks; w += blockDim.x) {
-            const int head = w / chunks, c = (w - head * chunks) * 8;
-            *reinterpret_cast<uint4*>(v_pages + (slot + (int64_t)head * page_size) * d + c) =
-                *reinterpret_cast<const uint4*>(v + head * d + c);
+        *reinterpret_cast<uint4*>(x + i) = aq;
+        *reinterpret_cast<uint4*>(x + i + half) = bq;
+        if (dst) {
+            *reinterpret_cast<uint4*>(dst + i) = aq;
+            *reinterpret_cast<uint4*>(dst + i + half) = bq;
         }
     }
 }
@@ -361,11 +373,14 @@ MB_EXPORT int mb_rope_store(void* qkv, const float* cos_t, const float* sin_t, i
         MB_LAUNCH((rope_store_kernel<float>), tokens, 256, 0, s, 
             (float*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (float*)k_pages, (float*)v_pages, n_q, n_kv, d, page_size, store);
-    else if (dtype == MB_BF16 && d % 8 == 0 && (rot == d || rot == 0))
-        MB_LAUNCH((rope_store_bf16_kernel), tokens, 256, 0, s, 
-            (__nv_bfloat16*)qkv, rot ? cos_t : nullptr, sin_t, positions, seq_of_token, table,
-            max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_q, n_kv, d, page_size,
-            store);
+    else if (dtype == MB_BF16 && d % 16 == 0 && (rot == d || rot == 0)) {
+        const long long warps = (long long)tokens * (n_q + 2 * n_kv);
+        const int blocks = (int)((warps + 7) / 8);
+        MB_LAUNCH((rope_store_bf16_kernel), blocks, 256, 0, s, (__nv_bfloat16*)qkv,
+                  rot ? cos_t : nullptr, sin_t, positions, seq_of_token, table, max_pages,
+                  (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, tokens, n_q, n_kv, d, page_size,
+                  store);
+    }
     else if (dtype == MB_BF16)
         MB_LAUNCH((rope_store_kernel<__nv_bfloat16>), tokens, 256, 0, s, 
             (__nv_bfloat16*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
