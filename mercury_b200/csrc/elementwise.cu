@@ -216,9 +216,9 @@ __global__ void add_rmsnorm_bf16_regs_kernel(float* __restrict__ h,
     }
 }
 
-// bfloat16, the whole head rotated, head size a multiple of 16: one warp per (token, head),
-// eight features per lane through 16-byte accesses (a lane holds features [8j, 8j+8) of the
-// first half and the matching eight of the second half, i.e. four pairs twice).
+// bfloat16, the whole head rotated, head size a multiple of 16: one thread per (token, head,
+// run of eight pairs), through 16-byte accesses (a thread holds features [8j, 8j+8) of the
+// first half and the matching eight of the second half).
 __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
                                        const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t,
@@ -230,14 +230,16 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
                                        int n_kv, int d, int page_size, int store) {
     grid_dependency_sync();
     const int heads = n_q + 2 * n_kv;
-    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp_global >= tokens * heads) return;
-    const int t = warp_global / heads, head = warp_global - t * heads;
+    const int half = d / 2, runs = half / 8;
+    const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (int64_t)tokens * heads * runs) return;
+    const int run = (int)(item % runs);
+    const int head = (int)((item / runs) % heads);
+    const int t = (int)(item / ((int64_t)runs * heads));
     const int seq = seq_of_token[t];
     if (seq < 0) return;
     const int pos = positions[t];
-    const int half = d / 2;
+    const int i = run * 8;
     __nv_bfloat16* x = qkv + (int64_t)t * heads * d + (int64_t)head * d;
     __nv_bfloat16* dst = nullptr;
     if (head >= n_q && store) {
@@ -250,12 +252,13 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
         }
     }
     if (head >= n_q + n_kv) {                    // a value head: copy
-        if (dst)
-            for (int c = lane * 8; c < d; c += 256)
-                *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(x + c);
+        if (dst) {
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(x + i);
+            *reinterpret_cast<uint4*>(dst + i + half) = *reinterpret_cast<const uint4*>(x + i + half);
+        }
         return;
     }
-    for (int i = lane * 8; i < half; i += 256) {
+    {
         uint4 aq = *reinterpret_cast<const uint4*>(x + i);
         uint4 bq = *reinterpret_cast<const uint4*>(x + i + half);
         if (cos_t) {
@@ -374,8 +377,8 @@ MB_EXPORT int mb_rope_store(void* qkv, const float* cos_t, const float* sin_t, i
             (float*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (float*)k_pages, (float*)v_pages, n_q, n_kv, d, page_size, store);
     else if (dtype == MB_BF16 && d % 16 == 0 && (rot == d || rot == 0)) {
-        const long long warps = (long long)tokens * (n_q + 2 * n_kv);
-        const int blocks = (int)((warps + 7) / 8);
+        const long long items = (long long)tokens * (n_q + 2 * n_kv) * (d / 16);
+        const int blocks = (int)((items + 255) / 256);
         MB_LAUNCH((rope_store_bf16_kernel), blocks, 256, 0, s, (__nv_bfloat16*)qkv,
                   rot ? cos_t : nullptr, sin_t, positions, seq_of_token, table, max_pages,
                   (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, tokens, n_q, n_kv, d, page_size,

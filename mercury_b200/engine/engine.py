@@ -50,7 +50,8 @@ class Engine:
             runner = ModelRunner(
                 cfg.model, dtype=cfg.torch_dtype, device=cfg.device, page_size=cfg.block_size,
                 num_pages=cfg.num_blocks, max_seqs=cfg.max_running,
-                max_step_tokens=cfg.max_batched_tokens, max_model_len=cfg.max_model_len, ops=ops)
+                max_step_tokens=cfg.max_batched_tokens, max_model_len=cfg.max_model_len, ops=ops,
+                cuda_graphs=cfg.cuda_graphs)
         self.runner = runner
         cfg.validate_against(runner.spec.max_positions)
         self.cache = runner.cache

@@ -27,18 +27,27 @@ class Workspace:
     """Activation buffers by name, allocated once for the largest step and handed out as
     row slices, so that addresses stay the same from step to step."""
 
+    # buffers whose row count follows what a step asks for (logits of the wanted rows), not
+    # the step's token count: they start small and grow
+    ROW_SIZED = ("logits", "normed_rows")
+
     def __init__(self, device, dtype, max_rows: int):
         self.device = device
         self.dtype = dtype
         self.max_rows = max_rows
         self._buffers: dict[tuple, torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []   # outgrown buffers: captured graphs still use them
 
     def get(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
         dt = self.dtype if dtype is None else (torch.float32 if dtype == "float32" else dtype)
         key = (name, cols, dt)
         buf = self._buffers.get(key)
         if buf is None or buf.shape[0] < rows:
-            capacity = max(rows, self.max_rows if buf is None else 2 * buf.shape[0])
+            if buf is not None:
+                self._retired.append(buf)
+                capacity = max(rows, 2 * buf.shape[0])
+            else:
+                capacity = max(rows, 64) if name in self.ROW_SIZED else max(rows, self.max_rows)
             buf = torch.empty((capacity, cols), dtype=dt, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]
