@@ -58,6 +58,9 @@ _SIGNATURES = {
                         c_int, c_void_p],
     "mb_gemm_tcgen05_persistent": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p],
+    "mb_paged_attention_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
@@ -85,6 +88,8 @@ def load():
     lib.mb_gemm_skinny_supports.restype = c_int
     lib.mb_gemm_skinny_qkv_supports.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_gemm_skinny_qkv_supports.restype = c_int
+    lib.mb_attention_tcgen05_supports.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.mb_attention_tcgen05_supports.restype = c_int
     lib.mb_attention_mma_supports.argtypes = [c_int]
     lib.mb_attention_mma_supports.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]

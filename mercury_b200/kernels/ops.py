@@ -43,6 +43,7 @@ class CudaOps:
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
+        self.attention = "auto"   # "auto": tensor-memory kernel for prompt portions; "mma": never
         # Normalising inside the consuming product saves a launch but makes every block
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
         # the Qwen2 shapes, so the fusion is off unless asked for.
@@ -343,6 +344,23 @@ class CudaOps:
         tensor-core kernel takes runs there, everything else on the CUDA cores."""
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
+        tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
+            head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
+        if kernel == "tcgen05" and not tc_ok:
+            raise KernelError("the tensor-memory attention takes bfloat16, head size 64 and pages "
+                              "of 8 to 128 tokens")
+        # prompt portions (at least one full tile of rows) go to the tensor-memory kernel
+        if tc_ok and (kernel == "tcgen05" or (kernel is None and self.attention == "auto"
+                                              and batch.max_q_len * group >= 128)):
+            check(self.lib.mb_paged_attention_tcgen05(
+                _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), cache.k.shape[0],
+                _ptr(cache.table), cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
+                _ptr(out), tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads,
+                head_dim, cache.page_size, float(scale), int(window), _ptr(self._error_word()),
+                self._stream()), "paged_attention (tcgen05)")
+            self.launches += 1
+            self._tc_pending = True
+            return
         use_mma = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_mma_supports(head_dim)
                    and kernel != "simt")
         if kernel == "mma" and not use_mma:

@@ -374,9 +374,9 @@ ATTENTION_CASES = [
 
 
 def attention_close(got, want, dtype, kernel):
-    """The tensor-core kernel rounds the probabilities to bfloat16 before P.V and the result
+    """The tensor-core kernels round the probabilities to bfloat16 before P.V and the result
     once more: two roundings of 2^-8, against one for the CUDA-core kernel."""
-    if kernel == "mma":
+    if kernel in ("mma", "tcgen05"):
         err = float((got.double() - want.double()).abs().max()) / float(want.abs().max())
         assert err <= 2 * 2.0 ** -8, f"attention (mma): relative error {err:.3e}"
     else:
@@ -384,7 +384,8 @@ def attention_close(got, want, dtype, kernel):
 
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
-                                          ("mma", torch.bfloat16)], ids=["f32", "bf16", "bf16-mma"])
+                                          ("mma", torch.bfloat16), ("tcgen05", torch.bfloat16)],
+                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05"])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("case", range(len(ATTENTION_CASES)), ids=lambda i: f"case{i}")
 def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
@@ -394,6 +395,9 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     n_q, n_kv, d, page, q_lens, kv_lens, window = ATTENTION_CASES[case]
     if kernel == "mma" and not ops.lib.mb_attention_mma_supports(d):
         pytest.skip("head size left to the CUDA-core kernel")
+    if kernel == "tcgen05" and (splits != 1 or not ops.lib.mb_attention_tcgen05_supports(
+            d, page, n_q, n_kv, (n_q + 2 * n_kv) * d)):
+        pytest.skip("left to the other attention kernels")
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 5
     drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
     batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=3, seed=1,
@@ -419,6 +423,7 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     want = torch.zeros_like(got)
     ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got, kernel=kernel)
     twin.paged_attention(qkv_twin, n_q, n_kv, d, batch, cache_twin, d ** -0.5, window, want)
+    ops.check_errors()
     assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
     attention_close(got[live], want[live], dtype, kernel)
 
