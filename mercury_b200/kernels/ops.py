@@ -43,7 +43,10 @@ class CudaOps:
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
-        self.attention = "auto"   # "auto": tensor-memory kernel for prompt portions; "mma": never
+        # "mma": the mma.sync kernels (the default: faster today); "auto": the tensor-memory
+        # kernel for prompt portions of head size 64
+        self.attention = "mma"
+        self.prompt_splits: int | None = None   # override of the key split of prompt portions
         # Normalising inside the consuming product saves a launch but makes every block
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
         # the Qwen2 shapes, so the fusion is off unless asked for.
@@ -338,6 +341,16 @@ class CudaOps:
             return 1
         return max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
 
+    def _prompt_splits(self, batch, num_kv_heads, group) -> int:
+        """Key ranges per row tile of a prompt portion. Cutting the keys (and merging the
+        ranges afterwards) shortens the chain of the last, heaviest row tile, but on B200 a
+        2048-token portion got slower with every cut (3.87 ms whole, 4.09 ms in two, 4.43 ms
+        in eight: the float32 partial results cost more than the tail), so prompts are not
+        cut unless `prompt_splits` says so."""
+        if self.prompt_splits is not None:
+            return max(1, self.prompt_splits)
+        return 1
+
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
                         window, out, kernel: str | None = None):
         """`kernel` forces "mma" or "simt"; by default bfloat16 with a head size the
@@ -368,7 +381,10 @@ class CudaOps:
                               f"128, not {qkv.dtype} with {head_dim}")
         if use_mma:
             small = batch.max_q_len * group <= 16
-            splits = self._splits(batch, num_kv_heads, group, 16, 64) if small else 1
+            if small:
+                splits = self._splits(batch, num_kv_heads, group, 16, 64)
+            else:
+                splits = self._prompt_splits(batch, num_kv_heads, group)
         else:
             splits = self._splits(batch, num_kv_heads, group, 16, 32)
         floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
