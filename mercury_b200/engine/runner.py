@@ -225,9 +225,18 @@ class ModelRunner:
         """How many ways the keys of each sequence are split in a captured decode step: the
         grid is fixed at capture, so it is sized to fill the device for this many sequences
         whatever their lengths turn out to be."""
+        forced = getattr(self.ops, "decode_splits", None)
+        if forced:
+            return max(1, int(forced))
         kv_heads = max((l.need.num_kv_heads for l in self.model.cache_layers.values()), default=1)
         sms = getattr(self.ops, "sm_count", 148)
-        return max(1, min(32, -(-2 * sms // max(1, bucket * kv_heads))))
+        # measured on B200 at 2048-token contexts: about one block per SM for small batches
+        # (at most a dozen ranges per sequence: a range then holds three or more 64-key
+        # tiles), about two per SM once the batch alone brings 32 or more blocks
+        rows = max(1, bucket * kv_heads)
+        if rows <= 16:
+            return max(1, min(12, sms // rows))
+        return max(1, -(-2 * sms // rows))
 
     def _decode_with_graph(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Decode-only steps (one token per entry) replay a CUDA graph captured once per
