@@ -43,7 +43,27 @@ struct SkinnyInput {
     const __nv_bfloat16* norm_w;
     const int* rows;
     float eps;
+    // deferred RMSNorm scale: x holds stream * norm weight (not yet divided by the rms), and
+    // ss_part[tok * ss_tiles + j] the sums of squares of the stream's 16-column tiles, left
+    // by the product that updated the stream; 1/rms multiplies this product's result rows
+    const float* ss_part;
+    int ss_tiles;
+    float ss_eps;
+    int ss_k;
 };
+
+// 1/rms of each row from the partial sums of squares, into scale_s[T] (ones without them).
+__device__ __forceinline__ void skinny_row_scale(const SkinnyInput& in, int T, float* scale_s) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int tok = warp; tok < T; tok += warps) {
+        float ss = 0.f;
+        if (in.ss_part) {
+            for (int j = lane; j < in.ss_tiles; j += 32) ss += in.ss_part[(int64_t)tok * in.ss_tiles + j];
+            ss = warp_sum(ss);
+        }
+        if (lane == 0) scale_s[tok] = in.ss_part ? rsqrtf(ss / (float)in.ss_k + in.ss_eps) : 1.f;
+    }
+}
 
 // 1/rms of each of the T rows of the stream, by the whole block, into rstd_s[T].
 __device__ __forceinline__ void skinny_row_rstd(const SkinnyInput& in, int T, int K, float* rstd_s) {
@@ -175,13 +195,13 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ bias, void* __restrict__ out,
                                    int T, int N, int K, int half_n, int rowt, int ksplit,
-                                   const __nv_bfloat16* __restrict__ next_norm_w, float next_eps,
-                                   __nv_bfloat16* __restrict__ next_normed,
-                                   int* __restrict__ ticket) {
+                                   const __nv_bfloat16* __restrict__ next_norm_w,
+                                   __nv_bfloat16* __restrict__ next_x,
+                                   float* __restrict__ next_ss) {
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
     __shared__ float rstd_s[TOK];
-    __shared__ int is_last;
+    __shared__ float scale_s[TOK];
     const int warp = threadIdx.x >> 5;
     const int rt = warp / ksplit, ks = warp - rt * ksplit;
     int n0;  // first weight row of this warp's tile
@@ -198,6 +218,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
         skinny_prefetch_weights(w, n0, K, ks * per, ks * per + per < chunks ? ks * per + per : chunks);
     }
     grid_dependency_sync();
+    skinny_row_scale(in, T, scale_s);     // read after the barrier that follows the product
     if (NORM) {
         skinny_row_rstd(in, T, K, rstd_s);
         __syncthreads();
@@ -227,60 +248,47 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
                 up += red[((2 * p + 1) * ksplit + k) * 16 * TOK + r * TOK + tok];
             }
             // the separate kernels round gate and up to bfloat16 between product and gate
-            gate = __bfloat162float(__float2bfloat16_rn(gate));
-            up = __bfloat162float(__float2bfloat16_rn(up));
+            gate = __bfloat162float(__float2bfloat16_rn(gate * scale_s[tok]));
+            up = __bfloat162float(__float2bfloat16_rn(up * scale_s[tok]));
             reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * half_n + n] =
                 __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
         }
     } else {
+        // (the loop bound and the block size are multiples of 32: whole warps run it, and
+        // the 16 rows of one (tile, token) sit in one half-warp)
         for (int idx = threadIdx.x; idx < rowt * 16 * TOK; idx += blockDim.x) {
             const int r = idx % 16, tok = (idx / 16) % TOK, tile = idx / (16 * TOK);
-            const int n = (blockIdx.x * rowt + tile) * 16 + r;
-            if (tok >= T || n >= N) continue;
+            const int tile_global = blockIdx.x * rowt + tile;
+            const int n = tile_global * 16 + r;
+            const bool live = tok < T && n < N;
             float v = 0.f;
             for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
-            if (bias) v += __bfloat162float(bias[n]);
-            if (EPI == 0)
-                reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
-            else if (EPI == 3)
-                reinterpret_cast<float*>(out)[(int64_t)tok * N + n] += v;
-            else
-                reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
-        }
-    }
-    if (EPI == 3 && next_norm_w != nullptr) {
-        // The block that finishes last sees the whole updated stream and normalises its T
-        // rows for the product that follows, which saves the norm's own launch.
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const int t = atomicAdd(ticket, 1);
-            is_last = t == (int)gridDim.x - 1;
-            if (is_last) *ticket = 0;
-        }
-        __syncthreads();
-        if (!is_last) return;
-        __threadfence();
-        const float* h = reinterpret_cast<const float*>(out);
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-        for (int tok = warp; tok < T; tok += warps) {
-            const float* row = h + (int64_t)tok * N;
-            float ss = 0.f;
-            for (int k = lane * 4; k < N; k += 128) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            v *= scale_s[tok < T ? tok : 0];
+            if (bias && live) v += __bfloat162float(bias[n]);
+            float sq = 0.f;
+            if (live) {
+                if (EPI == 0) {
+                    reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+                } else if (EPI == 3) {
+                    float* at = reinterpret_cast<float*>(out) + (int64_t)tok * N + n;
+                    const float updated = *at + v;
+                    *at = updated;
+                    if (next_norm_w) {
+                        // for the product after the next norm: the stream times that norm's
+                        // weight, and this tile's share of the row's sum of squares
+                        next_x[(int64_t)tok * N + n] =
+                            __float2bfloat16_rn(updated * __bfloat162float(next_norm_w[n]));
+                        sq = updated * updated;
+                    }
+                } else {
+                    reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+                }
             }
-            ss = warp_sum(ss);
-            const float rstd = rsqrtf(ss / (float)N + next_eps);
-            for (int k = lane * 4; k < N; k += 128) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
-                const uint2 wq = *reinterpret_cast<const uint2*>(next_norm_w + k);
-                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.x));
-                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.y));
-                uint2 oq;
-                oq.x = pack2(v.x * rstd * w0.x, v.y * rstd * w0.y);
-                oq.y = pack2(v.z * rstd * w1.x, v.w * rstd * w1.y);
-                *reinterpret_cast<uint2*>(next_normed + (int64_t)tok * N + k) = oq;
+            if (EPI == 3 && next_norm_w) {
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (r == 0 && tok < T && tile_global * 16 < N)
+                    next_ss[(int64_t)tok * (N / 16) + tile_global] = sq;
             }
         }
     }
@@ -319,6 +327,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
     __shared__ int tok_pos[TOK];
     __shared__ int tok_page[TOK];           // -2: padding token, -1: no page
     __shared__ float rstd_s[TOK];
+    __shared__ float scale_s[TOK];
     const int head = blockIdx.x;  // 0..n_q-1 q heads, then k heads, then v heads
     if (threadIdx.x < TOK) {
         const int tok = threadIdx.x;
@@ -333,6 +342,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         tok_pos[tok] = pos;
         tok_page[tok] = page;
     }
+    skinny_row_scale(in, T, scale_s);
     if (NORM) {
         skinny_row_rstd(in, T, K, rstd_s);
         __syncthreads();
@@ -355,6 +365,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         const int tile = r / 16, rr = r % 16;
         float v = 0.f;
         for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + rr * TOK + tok];
+        v *= scale_s[tok < T ? tok : 0];
         if (bias) v += __bfloat162float(bias[head * D + r]);
         // the separate kernels round the projection to bfloat16 before rotating it
         val[tok * D + r] = __bfloat162float(__float2bfloat16_rn(v));
@@ -427,13 +438,18 @@ MB_EXPORT int mb_gemm_skinny_supports(int T, int N, int K) {
     else { constexpr int NT = 2; __VA_ARGS__ }
 
 static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_w, const int* rows,
-                                float eps) {
+                                float eps, const float* ss_part, int ss_tiles, float ss_eps,
+                                int ss_k) {
     SkinnyInput in;
     in.x = (const __nv_bfloat16*)x;
     in.h = h;
     in.norm_w = (const __nv_bfloat16*)norm_w;
     in.rows = rows;
     in.eps = eps;
+    in.ss_part = ss_part;
+    in.ss_tiles = ss_tiles;
+    in.ss_eps = ss_eps;
+    in.ss_k = ss_k;
     return in;
 }
 
@@ -444,32 +460,34 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, true>), blocks, threads, smem, s, in,    \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
-                          (const bf*)next_w, next_eps, (bf*)next_out, ticket);                   \
+                          (const bf*)next_w, (bf*)next_x, next_ss);                              \
         } else {                                                                                 \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, false>), blocks, threads, smem, s, in,   \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
-                          (const bf*)next_w, next_eps, (bf*)next_out, ticket);                   \
+                          (const bf*)next_w, (bf*)next_x, next_ss);                              \
         }                                                                                        \
     } while (0)
 
 // The activations are either `x` (bfloat16 [T, K]) or, when `norm_w` is given, the float32
 // stream `h` [*, K] normalised with `norm_w` and `eps`, rows picked by `rows` if not null.
 // mode: 0 = bfloat16 out, 1 = float32 out, 3 = add into the float32 rows of `out`.
-// bias may be null. With mode 3 and `next_w` given, the last block to finish also writes
-// RMSNorm(out rows) * next_w as bfloat16 into `next_out` [T, N]; `ticket` is one zeroed
-// int on the device (left zeroed); N must then be a multiple of 4.
+// bias may be null. A third form of input: `ss_part` given means x is a stream already
+// multiplied by a norm weight and ss_part [T, ss_tiles] holds its sums of squares per
+// 16-column tile; the result rows are multiplied by rsqrt(sum / ss_k + ss_eps).
+// With mode 3 and `next_w` given the product leaves exactly that for the product after the
+// next norm: next_x [T, N] = bfloat16(updated stream * next_w) and next_ss [T, N / 16].
 MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, const int* rows,
-                             float eps, const void* w, const void* bias, void* out, int mode, int T,
-                             int N, int K, const void* next_w, float next_eps, void* next_out,
-                             int* ticket, void* stream) {
-    if (next_w && (mode != 3 || !next_out || !ticket || N % 4)) return MB_ERR_UNSUPPORTED_SIZE;
+                             float eps, const float* ss_part, int ss_tiles, float ss_eps, int ss_k,
+                             const void* w, const void* bias, void* out, int mode, int T, int N,
+                             int K, const void* next_w, void* next_x, float* next_ss, void* stream) {
+    if (next_w && (mode != 3 || !next_x || !next_ss)) return MB_ERR_UNSUPPORTED_SIZE;
     if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
     if (mode != 0 && mode != 1 && mode != 3) return MB_ERR_BAD_DTYPE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
-    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps);
+    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
     const int nt = (T + 7) / 8;
     const int tiles = N / 16;
     const int ksplit = pick_ksplit(tiles, K / 32, norm_w ? 16 : 32);
@@ -489,12 +507,13 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
 
 // w: [2 * width, K] with the gate rows first; out: [T, width] bfloat16. Input as above.
 MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* norm_w,
-                                    const int* rows, float eps, const void* w, void* out, int T,
+                                    const int* rows, float eps, const float* ss_part, int ss_tiles,
+                                    float ss_eps, int ss_k, const void* w, void* out, int T,
                                     int width, int K, void* stream) {
     if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
-    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps);
+    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
     const int nt = (T + 7) / 8;
     const int pairs = width / 16;
     const int ksplit = pick_ksplit(2 * pairs, K / 32, norm_w ? 8 : 16);
@@ -505,9 +524,8 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     const int N = 2 * width, half_n = width;
     const void* bias = nullptr;
     const void* next_w = nullptr;
-    void* next_out = nullptr;
-    int* ticket = nullptr;
-    const float next_eps = 0.f;
+    void* next_x = nullptr;
+    float* next_ss = nullptr;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
@@ -533,6 +551,7 @@ MB_EXPORT int mb_gemm_skinny_qkv_supports(int T, int K, int d, int rot) {
 // The packed q/k/v projection of a few tokens with bias, rotation and cache store fused.
 // Input as for mb_gemm_skinny (rows is not used here).
 MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const float* h, const void* norm_w, float eps,
+                                      const float* ss_part, int ss_tiles, float ss_eps, int ss_k,
                                       const void* w, const void* bias, void* qkv,
                                       const float* cos_t, const float* sin_t, int rot,
                                       const int* positions, const int* seq_of_token,
@@ -542,7 +561,7 @@ MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const float* h, const void*
     if (!mb_gemm_skinny_qkv_supports(T, K, d, rot)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
-    const SkinnyInput in = skinny_input(x, h, norm_w, nullptr, eps);
+    const SkinnyInput in = skinny_input(x, h, norm_w, nullptr, eps, ss_part, ss_tiles, ss_eps, ss_k);
     const int nt = (T + 7) / 8;
     const int heads = n_q + 2 * n_kv;
     const int rowt = d / 16;

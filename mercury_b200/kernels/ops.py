@@ -51,12 +51,10 @@ class CudaOps:
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
         # the Qwen2 shapes, so the fusion is off unless asked for.
         self.fuse_norm = False
-        # The product that adds into the stream can let its last block compute the norm
-        # that follows (one launch less per norm). Measured on B200 inside a captured decode
-        # step this is slower than the separate norm kernel (one block works alone at the
-        # end of every product), so it is off unless asked for.
-        self.fuse_next_norm = False
-        self._norm_ticket: torch.Tensor | None = None
+        # The product that adds into the stream also leaves the stream times the next norm's
+        # weight and the rows' sums of squares; the product after that norm multiplies its
+        # result rows by 1/rms. The norm's own launch disappears.
+        self.fuse_next_norm = True
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: the engine's kernels are CUDA only and there is "
                               "no CPU path")
@@ -161,19 +159,25 @@ class CudaOps:
         return x if hasattr(x, "materialize") else None
 
     def _skinny_input(self, x):
-        """(x, h, norm weight, rows, eps) pointers/values of the C interface."""
+        """The nine input arguments of the few-token products: (x, h, norm weight, rows, eps)
+        and (partial sums of squares, their tiles per row, eps, row length)."""
         pending = self._pending(x)
         if pending is None:
-            return _ptr(x), None, None, None, 0.0
-        return None, _ptr(pending.h), _ptr(pending.weight), _ptr(pending.rows), float(pending.eps)
+            return _ptr(x), None, None, None, 0.0, None, 0, 0.0, 0
+        scaled = getattr(pending, "ss_part", None)
+        if scaled is not None:
+            return (_ptr(pending.x), None, None, None, 0.0, _ptr(scaled), scaled.shape[1],
+                    float(pending.eps), pending.size)
+        return (None, _ptr(pending.h), _ptr(pending.weight), _ptr(pending.rows), float(pending.eps),
+                None, 0, 0.0, 0)
 
     def linear_residual(self, x, weight, bias, h, ctx, name, then_norm=None):
         """h += x . weight^T (+ bias) in the float32 stream when the few-token kernel takes
         the shape (returns None); otherwise the product lands in the buffer `name` and is
         returned for the next norm to add. `then_norm` names the norm part that follows
-        (it has `weight`, `eps`, `size`): the kernel's last block then also leaves that
-        norm's output in `ctx.prenormed`, where the norm part picks it up instead of
-        launching."""
+        (it has `weight`, `eps`, `size`): the kernel then also leaves that norm's output, up
+        to the division by the row's rms, in `ctx.prenormed` (a `PendingScaled`), where the
+        norm part picks it up instead of launching."""
         m, k = x.shape
         n = weight.shape[0]
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
@@ -184,16 +188,17 @@ class CudaOps:
                     and getattr(then_norm, "weight", None) is not None
                     and then_norm.weight.dtype == torch.bfloat16)
             normed = ctx.buffer("normed", m, n) if fuse else None
-            if fuse and self._norm_ticket is None:
-                self._norm_ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
+            sums = ctx.buffer("norm_sums", m, n // 16, dtype="float32") if fuse else None
             check(self.lib.mb_gemm_skinny(
-                _ptr(x), None, None, None, 0.0, _ptr(weight), _ptr(bias), _ptr(h), 3, m, n, k,
-                _ptr(then_norm.weight) if fuse else None, float(then_norm.eps) if fuse else 0.0,
-                _ptr(normed), _ptr(self._norm_ticket) if fuse else None, self._stream()),
-                "linear_residual (skinny)")
+                *self._skinny_input(x), _ptr(weight), _ptr(bias), _ptr(h), 3, m, n, k,
+                _ptr(then_norm.weight) if fuse else None, _ptr(normed), _ptr(sums),
+                self._stream()), "linear_residual (skinny)")
             self.launches += 1
             if fuse:
-                ctx.prenormed = (then_norm, normed)
+                from ..parts.norm import PendingScaled
+
+                ctx.prenormed = (then_norm, PendingScaled(normed, sums, h, then_norm.weight,
+                                                          then_norm.eps, ctx, n))
             return None
         out = ctx.buffer(name, m, n)
         self.linear(x, weight, bias, out)
@@ -212,7 +217,7 @@ class CudaOps:
         if all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k):
             check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
                                           _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
-                                          None, 0.0, None, None, self._stream()),
+                                          None, None, None, self._stream()),
                   "linear (skinny)")
             self.launches += 1
             return
@@ -292,9 +297,9 @@ class CudaOps:
                 and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
                 and cache.k.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_qkv_supports(m, k, head_dim, rot)):
-            xp, hp, wp, _rows, eps = self._skinny_input(x)
+            xp, hp, wp, _rows, eps, ssp, sst, sse, ssk = self._skinny_input(x)
             check(self.lib.mb_gemm_skinny_qkv_rope(
-                xp, hp, wp, eps, _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
+                xp, hp, wp, eps, ssp, sst, sse, ssk, _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
                 _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table),
                 cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), m, k, num_heads, num_kv_heads,
                 head_dim, cache.page_size, int(cache.write), self._stream()),

@@ -30,6 +30,19 @@ class PendingNorm:
         return out
 
 
+class PendingScaled(PendingNorm):
+    """A norm whose output exists up to the division by the row's rms: `x` holds the stream
+    times the norm weight (bfloat16) and `ss_part` [rows, tiles] the stream's sums of
+    squares per 16-column tile, both left by the product that updated the stream. A product
+    that takes this multiplies its result rows by 1/rms (a row scale commutes with the
+    product); any other consumer calls `materialize()`, which runs the norm from the
+    stream."""
+
+    def __init__(self, x, ss_part, h, weight, eps, ctx, size):
+        super().__init__(h, weight, eps, None, ctx, size)
+        self.x, self.ss_part = x, ss_part
+
+
 class RMSNorm(Norm):
     capturable = True
 
@@ -53,7 +66,8 @@ class RMSNorm(Norm):
         if pre is not None:
             ctx.prenormed = None
             if pre[0] is self and delta is None and rows is None:
-                return pre[1]      # the product before this norm already left its output
+                # the product before this norm already left its output (up to the row scale)
+                return pre[1] if defer else pre[1].materialize()
         count = h.shape[0] if rows is None else rows.shape[0]
         if (defer and delta is None
                 and getattr(ctx.ops, "can_fuse_norm", lambda *a: False)(count, self.size, self.weight)):

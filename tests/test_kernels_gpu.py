@@ -169,8 +169,11 @@ def test_linear_swiglu(ops, twin, m, width, k):
 
 
 def fake_ctx(ops):
-    return SimpleNamespace(ops=ops, dtype=torch.bfloat16, buffer=lambda name, rows, cols, dtype=None:
-                           torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda"))
+    def buffer(name, rows, cols, dtype=None):
+        kind = torch.float32 if dtype == "float32" else (dtype or torch.bfloat16)
+        return torch.empty((rows, cols), dtype=kind, device="cuda")
+
+    return SimpleNamespace(ops=ops, dtype=torch.bfloat16, buffer=buffer)
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 896, 896), (8, 896, 4864), (16, 1536, 320), (40, 896, 896),
@@ -192,27 +195,55 @@ def test_linear_residual(ops, twin, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(1, 896, 896), (8, 896, 4864), (16, 1536, 320), (3, 64, 128)])
 def test_linear_residual_leaves_the_next_norm(ops, twin, m, n, k):
-    """The last block of the product also normalises the updated stream; twice in a row, as
-    the ticket must come back to zero."""
+    """The product that updates the stream also leaves the stream times the next norm's
+    weight and the rows' sums of squares; the products after it scale their rows by 1/rms.
+    Checked through all three consumers against the norm's output computed separately."""
     from mercury_b200.kernels.ops import CudaOps
 
     ops = CudaOps("cuda")
     ops.fuse_next_norm = True
     norm = SimpleNamespace(weight=rand((n,), torch.bfloat16, 61, 0.1) + 1, eps=1e-6, size=n)
-    for seed in (35, 36):
-        x = rand((m, k), torch.bfloat16, seed)
-        w = rand((n, k), torch.bfloat16, seed + 10, 0.1)
-        h = rand((m, n), torch.float32, seed + 20)
-        h_want = (h.double() + x.double() @ w.double().T).float()
-        ctx = fake_ctx(ops)
-        ctx.prenormed = None
-        assert ops.linear_residual(x, w, None, h, ctx, "tmp", then_norm=norm) is None
-        assert ctx.prenormed is not None and ctx.prenormed[0] is norm
-        want = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-        twin.add_rmsnorm(h_want.clone(), None, norm.weight, norm.eps, want)
-        got = ctx.prenormed[1]
-        assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 2.0 ** -7
-        assert float((h.double() - h_want.double()).abs().max() / h_want.abs().max()) <= 2 * k ** 0.5 * 2.0 ** -24
+    x = rand((m, k), torch.bfloat16, 35)
+    w = rand((n, k), torch.bfloat16, 45, 0.1)
+    h = rand((m, n), torch.float32, 55)
+    h_want = (h.double() + x.double() @ w.double().T).float()
+    ctx = fake_ctx(ops)
+    ctx.prenormed = None
+    assert ops.linear_residual(x, w, None, h, ctx, "tmp", then_norm=norm) is None
+    assert ctx.prenormed is not None and ctx.prenormed[0] is norm
+    pending = ctx.prenormed[1]
+    assert float((h.double() - h_want.double()).abs().max() / h_want.abs().max()) <= 2 * k ** 0.5 * 2.0 ** -24
+    normed = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    twin.add_rmsnorm(h_want.clone(), None, norm.weight, norm.eps, normed)
+    # materialised: the plain norm of the updated stream
+    got = pending.materialize()
+    assert float((got.double() - normed.double()).abs().max() / normed.double().abs().max()) <= 2.0 ** -7
+    # a plain product, the gated product and the q/k/v product fed with the pending input
+    w1 = rand((256, n), torch.bfloat16, 62, 0.1)
+    out, want = (torch.empty((m, 256), dtype=torch.float32, device="cuda") for _ in range(2))
+    ops.linear(pending, w1, None, out)
+    twin.linear(normed, w1, None, want)
+    assert float((out - want).abs().max() / want.abs().max()) <= 2.0 ** -6
+    w2 = rand((2 * 96, n), torch.bfloat16, 63, 0.1)
+    out, want = (torch.empty((m, 96), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    ops.linear_swiglu(pending, w2, out, ctx)
+    twin.linear_swiglu(normed, w2, want)
+    assert float((out.double() - want.double()).abs().max() / want.double().abs().max()) <= 2.0 ** -5
+    n_q, n_kv, d, page = 3, 1, 64, 16
+    kv_lens = tuple(range(20, 20 + m))
+    batch, table = make_batch((1,) * m, kv_lens, page, 64, seed=7)
+    kc, vc = fill_cache(batch, table, kv_lens, (1,) * m, n_kv, d, page, 64, torch.bfloat16, 8, False)
+    kc2, vc2 = kc.clone(), vc.clone()
+    w3 = rand(((n_q + 2 * n_kv) * d, n), torch.bfloat16, 64, 0.1)
+    b3 = rand(((n_q + 2 * n_kv) * d,), torch.bfloat16, 65)
+    angles = torch.rand((64, d // 2), generator=torch.Generator().manual_seed(9)) * 6
+    tables = (angles.cos().cuda(), angles.sin().cuda())
+    qkv = torch.zeros((m, (n_q + 2 * n_kv) * d), dtype=torch.bfloat16, device="cuda")
+    qkv2 = qkv.clone()
+    ops.qkv_rope_store(pending, w3, b3, qkv, n_q, n_kv, d, tables, batch, LayerCache(kc, vc, page, table, True))
+    twin.qkv_rope_store(normed, w3, b3, qkv2, n_q, n_kv, d, tables, batch, LayerCache(kc2, vc2, page, table, True))
+    for got, want in ((qkv[:, :n_q * d], qkv2[:, :n_q * d]), (kc, kc2), (vc, vc2)):
+        assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 2.0 ** -5
 
 
 @pytest.mark.parametrize("m,hidden", [(1, 896), (8, 896), (13, 1536), (16, 320)])
