@@ -13,7 +13,7 @@ from replay_check import requests_for, run_and_check, sharpened_model
 from tiny import PAGE_SIZE, RAW
 
 LENGTHS = {"A": (37, 70, 129, 45), "B": (33, 64, 150, 41), "C": (50, 131, 65, 90),
-           "D": (35, 120, 64, 47)}
+           "D": (35, 120, 64, 47), "E": (70, 33, 100, 51)}
 
 
 def make_runner(name, num_tokens=320):
@@ -26,7 +26,7 @@ def make_runner(name, num_tokens=320):
                        max_step_tokens=num_tokens, max_model_len=num_tokens, ops=TorchOps())
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_replay_logic(name, mode):
     lengths = LENGTHS[name]

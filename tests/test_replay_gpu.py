@@ -23,7 +23,8 @@ from tiny import PAGE_SIZE, RAW
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": (37, 70, 129, 200, 45, 96, 161), "B": (33, 64, 150, 41, 97, 208, 80),
-           "C": (50, 131, 65, 190, 77, 40, 100), "D": (35, 120, 64, 201, 90, 47, 133)}
+           "C": (50, 131, 65, 190, 77, 40, 100), "D": (35, 120, 64, 201, 90, 47, 133),
+           "E": (70, 33, 140, 90, 51)}
 MAX_TOKENS = 512   # 8 pages of 64: the seven requests need far more, so pages come back
 
 
@@ -38,7 +39,7 @@ def make_runner(name, dtype, num_tokens=MAX_TOKENS):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_replay_matches_plain(name, dtype, mode):
     lengths = LENGTHS[name]
@@ -74,6 +75,27 @@ def test_first_tokens(name, dtype):
     steps, rows = replay_cases.decode_tail(requests, tail=64)
     runner = make_runner(name, dtype)
     run_and_check(runner, name, lengths, steps, rows, dtype)
+
+
+def test_weights_stored_in_32_bit_stay_so_in_the_bfloat16_engine():
+    """A checkpoint stored in float32, run by the bfloat16 engine: the weights stay 32-bit,
+    the products fall to the kernels that take such weights, and the result is at least as
+    close to the oracle as with bfloat16 weights."""
+    from mercury_b200.engine.runner import ModelRunner
+
+    name, lengths = "B", LENGTHS["B"][:4]
+    _raw, config, tensors = sharpened_model(name)
+    wide = {k: v.float() for k, v in tensors.items()}
+    requests = requests_for(name, lengths)
+    steps, rows = replay_cases.mixed(requests, 512, seed=2)
+    page = PAGE_SIZE[name]
+    runner = ModelRunner(config=config, tensors=wide, dtype=torch.bfloat16, device="cuda",
+                         page_size=page, num_pages=512 // page, max_seqs=4, max_step_tokens=512,
+                         max_model_len=512)
+    mixer = runner.model.blocks[0].mixer
+    assert mixer.qkv_weight.dtype == torch.float32 and runner.model.embedding.table.dtype == torch.float32
+    assert next(iter(runner.kv_layers.values()))[0].dtype == torch.bfloat16
+    run_and_check(runner, name, lengths, steps, rows, torch.bfloat16)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

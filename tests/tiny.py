@@ -37,9 +37,15 @@ TINY_D = {
     "intermediate_size": 176, "vocab_size": 515, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
     "tie_word_embeddings": True, "use_sliding_window": False, "max_position_embeddings": 2048,
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32}
-SEED = {"A": 0, "B": 1, "C": 2, "D": 3}
-RAW = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+TINY_E = {   # one KV head under 32 query heads, head size 80 (no tensor-core attention), pages of 64
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 160,
+    "num_attention_heads": 32, "num_key_value_heads": 1, "head_dim": 80,
+    "intermediate_size": 272, "vocab_size": 1000, "rope_theta": 100000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "use_sliding_window": False, "max_position_embeddings": 2048,
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32, "E": 64}
+SEED = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+RAW = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def tiny_model(name: str, std: float | None = None):
