@@ -61,8 +61,16 @@ class BatchBuffers:
     """The pinned host buffer, its device twin, and the code that fills them."""
 
     def __init__(self, device, max_tokens: int, max_seqs: int, max_pages: int, num_groups: int,
-                 pin: bool):
+                 pin: bool, append_only: list[bool] | None = None):
+        """`append_only[g]` says that a block table of group g only ever grows at its end
+        (no window gives pages back), so a row that the same sequence filled in the last
+        step of the same layout needs only its new pages written."""
         self.device = torch.device(device)
+        self.append_only = list(append_only) if append_only is not None else [False] * num_groups
+        self._last_layout: tuple | None = None
+        self._row_owner: list[list] = []
+        self._row_written: list[list[int]] = []
+        self._arange = np.arange(max(max_tokens, max_seqs) + 1, dtype=np.int32)
         self.max_tokens = max_tokens
         self.max_seqs = max_seqs
         self.max_pages = max_pages
@@ -128,32 +136,67 @@ class BatchBuffers:
         seq_of[:] = -1
         token_ids[num_tokens:] = 0
         positions[num_tokens:] = 0
-        tables[:] = -1
         logit_rows[:] = 0
+        if self._last_layout != (tc, sc, pc, rc):
+            # another layout wrote over this region: every row starts from nothing
+            self._last_layout = (tc, sc, pc, rc)
+            tables[:] = -1
+            self._row_owner = [[None] * sc for _ in range(self.num_groups)]
+            self._row_written = [[0] * sc for _ in range(self.num_groups)]
+        decode_only = all(len(e.tokens) == 1 for e in entries)
         cursor = row = 0
         max_q = max_kv = 0
+        if decode_only and num_seqs:
+            starts = [e.seq.num_computed for e in entries]
+            count = self._arange[:num_seqs]
+            token_ids[:num_seqs] = [e.tokens[0] for e in entries]
+            positions[:num_seqs] = starts
+            seq_of[:num_seqs] = count
+            q_start[:num_seqs] = count
+            kv_len[:num_seqs] = positions[:num_seqs] + 1
+            slots[:num_seqs] = [e.seq.slot for e in entries]
+            cursor, max_q, max_kv = num_seqs, 1, max(starts) + 1
         for index, e in enumerate(entries):
+            for group, table in enumerate(e.seq.tables):
+                held = len(table)
+                if self._row_owner[group][index] is e.seq and self.append_only[group]:
+                    written = self._row_written[group][index]
+                    if held > written:
+                        tables[group, index, written:held] = table[written:]
+                else:
+                    if self._row_owner[group][index] is not None:
+                        tables[group, index, :] = -1
+                    tables[group, index, :held] = table
+                    self._row_owner[group][index] = e.seq
+                self._row_written[group][index] = held
             n = len(e.tokens)
+            base = index if decode_only else cursor
+            for w in (e.want if row_capacity is None else ()):
+                if not 0 <= w < n:
+                    raise ValueError(f"{e.seq.seq_id}: wanted place {w} is outside its {n} tokens")
+                logit_rows[row] = base + w
+                row += 1
+            if decode_only:
+                continue
             start = e.seq.num_computed
             token_ids[cursor:cursor + n] = e.tokens
-            positions[cursor:cursor + n] = np.arange(start, start + n, dtype=np.int32)
+            positions[cursor:cursor + n] = self._arange[:n] + start
             seq_of[cursor:cursor + n] = index
             q_start[index] = cursor
             kv_len[index] = start + n
             slots[index] = e.seq.slot
-            for group, table in enumerate(e.seq.tables):
-                tables[group, index, :len(table)] = table
-            for w in (e.want if row_capacity is None else ()):
-                if not 0 <= w < n:
-                    raise ValueError(f"{e.seq.seq_id}: wanted place {w} is outside its {n} tokens")
-                logit_rows[row] = cursor + w
-                row += 1
             cursor += n
             max_q = max(max_q, n)
             max_kv = max(max_kv, start + n)
+        for group in range(self.num_groups):
+            owners = self._row_owner[group]
+            for index in range(num_seqs, sc):
+                if owners[index] is not None:
+                    tables[group, index, :] = -1
+                    owners[index] = None
         if row_capacity is not None:
             rows = rc
-            logit_rows[:rc] = np.arange(rc, dtype=np.int32)
+            logit_rows[:rc] = self._arange[:rc]
         q_start[num_seqs:sc + 1] = cursor
         kv_len[num_seqs:] = 0
         slots[num_seqs:] = 0
@@ -174,5 +217,5 @@ class BatchBuffers:
             slots=dview("slots"),
             logit_rows=dview("logit_rows")[:rows if row_capacity is None else rc],
             tables=[t for t in dview("tables").view(self.num_groups, sc, pc)],
-            decode_only=all(len(e.tokens) == 1 for e in entries),
+            decode_only=decode_only,
         )

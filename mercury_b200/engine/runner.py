@@ -130,7 +130,8 @@ class ModelRunner:
         max_pages = -(-self.max_model_len // page_size)
         self.buffers = BatchBuffers(self.device, max_step_tokens, max_seqs, max_pages,
                                     max(1, len(self.model.group_windows)),
-                                    pin=self.device.type == "cuda")
+                                    pin=self.device.type == "cuda",
+                                    append_only=[w == 0 for w in self.model.group_windows] or None)
         self.workspace = Workspace(self.device, dtype, max_step_tokens)
         self.ctx = StepContext(ops, self.workspace, page_size, dtype)
         self.steps = 0
