@@ -1,36 +1,56 @@
 // Paged attention of prompt portions on the fifth-generation tensor cores (bfloat16, head
 // size 64): scores and the probability-weighted values are tcgen05.mma products with their
-// accumulators in tensor memory; queries, keys and values arrive by TMA, keys and values one
-// cache page per copy straight from the pages the block table names.
+// accumulators in tensor memory; queries, keys and values arrive by TMA, keys and values
+// straight from the pages the block table names.
 //
 // Same contract as the other attention kernels (ragged batch, causal by absolute position,
 // optional window; mercury/model/attention.py:77-101 is the reference's gather-and-SDPA
 // version). A CTA takes floor(128 / group) query tokens of one sequence and one KV head: the
 // (token, head of the group) pairs are the 128 rows of the MMA, one row per accumulator
-// lane and per softmax thread. Per tile of 128 keys:
-//   producer (warp 4)  TMA of up to 128/page_size key pages and value pages
-//   MMA      (warp 5)  S = Q K^T (128 x 128 x 64) into tensor memory
-//   softmax  (warps 0-3, one thread per row)  tcgen05.ld of the row, mask, running maximum,
+// lane and per softmax thread. Keys are walked in tiles of 64 and the three roles run a
+// tile or more apart:
+//   producer (warp 8)  TMA of the tile's key and value pages into a three-stage ring
+//   MMA      (warp 9)  S(i+1) = Q K(i+1)^T is issued before P(i) V(i), so the tensor cores
+//                      work on the next scores while the softmax of tile i runs; the scores
+//                      are double-buffered in tensor memory, and O += P(i) V(i) accumulates
+//                      in tensor memory over all tiles (2 x 64 + 64 columns)
+//   softmax  (warps 0-7, two threads per row: warps w and w + 4 share the rows of tensor-
+//            memory lane quarter w, 32 keys and 32 output columns each)  one tcgen05.ld of
+//            the scores, mask, running maximum (the two halves meet through shared memory),
 //            2^x, probabilities rounded to bfloat16 into a swizzled shared-memory tile
-//   MMA                O_tile = P V (128 x 64 x 128), V used as stored (MN-major operand)
-//   softmax            O = O * correction + O_tile in registers (float32)
-// Two CTAs fit on an SM (80 KB of shared memory, 256 tensor-memory columns each), so one
-// CTA's MMAs run under the other's softmax. Every mbarrier wait is bounded; a wait that
-// runs out sets the error word and the CTA winds down (frees its tensor memory, returns).
+//            (double-buffered). The maximum that the probabilities and the output are
+//            relative to is only raised when a tile exceeds it by more than 2^8 (the warp
+//            then rescales its rows of O in tensor memory); short of that a stale maximum
+//            changes nothing but the scale of intermediate values, and the per-tile pass
+//            over the output disappears
+// The walk over the key tiles of the last row tile is the critical path of a causal prompt
+// (every CTA is resident from the start). Launched as thread-block clusters of 2 or 4 CTAs,
+// the CTAs of a cluster share one row tile and split its key tiles between them; each
+// leaves its (maximum, sum, unnormalised output) in its own shared memory and the first CTA
+// of the cluster merges them through distributed shared memory, so the partial results
+// never touch global memory.
+// Two CTAs fit on an SM (97 KB of shared memory, 256 tensor-memory columns each). Every
+// mbarrier wait is bounded; a wait that runs out sets the error word and the CTA winds down
+// (frees its tensor memory, returns).
 #include "tcgen05.cuh"
 
 namespace mb {
 
 constexpr int TA_D = 64;             // head size
 constexpr int TA_ROWS = 128;         // MMA M: query rows per CTA
-constexpr int TA_KEYS = 128;         // keys per tile
-constexpr int TA_THREADS = 192;
+constexpr int TA_KEYS = 64;          // keys per tile
+constexpr int TA_STAGES = 3;         // key/value tiles in flight
+constexpr int TA_THREADS = 320;          // 8 softmax warps, producer, MMA issuer
+constexpr int TA_HALF = TA_KEYS / 2;     // keys (and output columns) per softmax thread
+constexpr int TA_TILE_BYTES = TA_KEYS * 128;   // one key (or value) tile in shared memory
 
 __device__ __forceinline__ float ta_exp2(float x) {
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+
+constexpr float TA_RAISE = 8.f;      // log2 of how far a tile may exceed the maximum in use
 
 // MN-major B operand (values as stored: [key][d], d contiguous, 128-byte swizzle).
 __device__ __forceinline__ uint64_t umma_desc_mn(const void* tile) {
@@ -43,7 +63,7 @@ __device__ __forceinline__ uint64_t umma_desc_mn(const void* tile) {
     return d;
 }
 
-__global__ void __launch_bounds__(TA_THREADS)
+__global__ void __launch_bounds__(TA_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const int* __restrict__ table,
@@ -55,13 +75,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base =
         reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;                       // 128 rows x 128 B
-    unsigned char* k_s = q_s + TA_ROWS * 128;        // 128 keys x 128 B
-    unsigned char* v_s = k_s + TA_KEYS * 128;        // 128 keys x 128 B
-    unsigned char* p_s = v_s + TA_KEYS * 128;        // 2 x (128 rows x 128 B): keys 0-63, 64-127
-    __shared__ uint64_t q_full, kv_full, s_ready, p_ready, o_ready;
+    unsigned char* q_s = base;                              // 128 rows x 128 B
+    unsigned char* kv_s = q_s + TA_ROWS * 128;              // [stage][K tile, V tile]
+    unsigned char* p_s = kv_s + TA_STAGES * 2 * TA_TILE_BYTES;   // 2 x (128 rows x 128 B)
+    __shared__ uint64_t q_full, kv_full[TA_STAGES], kv_free[TA_STAGES], s_ready[2], p_ready[2],
+        o_ready[2], pair_met[4];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int page_ok[TA_KEYS];                 // per key of the tile: 1 if its page was copied
+    __shared__ int page_ok[TA_STAGES][TA_KEYS];      // per key of a tile: 1 if its page was copied
+    __shared__ float row_xch[2][2][TA_ROWS];         // [tile parity][half][row]: maxima, then sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = n_q / n_kv;
@@ -80,14 +101,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     const int p_min = first_pos + tok0, p_max = first_pos + tok_max;
     int t_lo = 0;
     if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / TA_KEYS;
-    const int t_hi = p_max / TA_KEYS + 1;
+    // the key tiles of this row tile, cut evenly over the CTAs of the cluster
+    uint32_t cl_rank, cl_size;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cl_size));
+    const int tiles_all = p_max / TA_KEYS + 1 - t_lo;
+    const int tiles_per_cta = (tiles_all + (int)cl_size - 1) / (int)cl_size;
+    const int t_first = t_lo + (int)cl_rank * tiles_per_cta;
+    int n_tiles = t_lo + tiles_all - t_first;
+    if (n_tiles > tiles_per_cta) n_tiles = tiles_per_cta;
+    if (n_tiles < 0) n_tiles = 0;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        mbar_init(&kv_full, 1);
-        mbar_init(&s_ready, 1);
-        mbar_init(&p_ready, 4);
-        mbar_init(&o_ready, 1);
+        for (int i = 0; i < TA_STAGES; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_free[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_met[i], 2);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_ready[i], 1);
+            mbar_init(&p_ready[i], 8);
+        }
+        // P V of tile i commits to o_ready[i & 1]: a wait for tile i finds that barrier either
+        // in the phase of tile i or just past it (tile i - 2 is known to be complete when the
+        // scores of tile i have arrived, tile i + 2 cannot start before P(i + 2) exists), so
+        // the parity of the wait is never ambiguous although most phases are never waited for
+        mbar_init(&o_ready[0], 1);
+        mbar_init(&o_ready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -101,193 +142,336 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = tmem_base_slot;            // 128 columns of scores
-    const uint32_t tmem_o = tmem_base_slot + TA_KEYS;  // 64 columns of P.V
+    const uint32_t tmem_s = tmem_base_slot;                 // 2 x 64 columns of scores
+    const uint32_t tmem_o = tmem_base_slot + 2 * TA_KEYS;   // 64 columns of output
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- producer
-        // page ids of a tile are looked up by the whole warp, copies issued by lane 0
-        if (lane == 0) {
+        if (lane == 0 && n_tiles > 0) {
             mbar_expect_tx(&q_full, (uint32_t)(group * tok_per_tile * 128));
             tma_load_4d(q_s, &map_q, 0, 0, kvh, q_begin + tok0, &q_full);
         }
-        const int pages_per_tile = TA_KEYS / page_size;
+        // a copy brings `box` keys: a whole page, or 64 keys of a larger one
+        const int box = page_size < TA_KEYS ? page_size : TA_KEYS;
+        const int copies = TA_KEYS / box;
         bool ok = true;
-        for (int kt = t_lo; kt < t_hi && ok; ++kt) {
-            const int i = kt - t_lo;
-            if (i > 0) ok = mbar_wait(&o_ready, (uint32_t)((i - 1) & 1), error, 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            // lanes 0 .. pages_per_tile-1 each look one page up
-            int page = -1;
-            if (lane < pages_per_tile) {
-                const int key0 = kt * TA_KEYS + lane * page_size;
-                if (key0 < kv_len) page = table[(int64_t)seq * max_pages + key0 / page_size];
+        for (int i = 0; i < n_tiles; ++i) {
+            const int st = i % TA_STAGES, kt = t_first + i;
+            if (i >= TA_STAGES) {
+                ok = mbar_wait(&kv_free[st], (uint32_t)((i / TA_STAGES - 1) & 1), error, 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            // lanes 0 .. copies-1 each look one page up
+            int page = -1, row = 0;
+            if (lane < copies) {
+                const int key0 = kt * TA_KEYS + lane * box;
+                if (key0 < kv_len) {
+                    page = table[(int64_t)seq * max_pages + key0 / page_size];
+                    row = (page * n_kv + kvh) * page_size + key0 % page_size;
+                }
             }
             for (int k = lane; k < TA_KEYS; k += 32) {
-                const int pg = __shfl_sync(0xffffffffu, page, k / page_size);
-                page_ok[k] = pg >= 0 && kt * TA_KEYS + k < kv_len;
+                const int pg = __shfl_sync(0xffffffffu, page, k / box);
+                page_ok[st][k] = pg >= 0 && kt * TA_KEYS + k < kv_len;
             }
             const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
             __syncwarp();
-            if (lane == 0) {
-                const int copies = __popc(valid);
-                mbar_expect_tx(&kv_full, (uint32_t)(copies * 2 * page_size * 128));
-            }
+            if (lane == 0) mbar_expect_tx(&kv_full[st], (uint32_t)(__popc(valid) * 2 * box * 128));
             __syncwarp();
             if (page >= 0) {
-                const int row = (page * n_kv + kvh) * page_size;
-                tma_load_2d(k_s + lane * page_size * 128, &map_k, 0, row, &kv_full);
-                tma_load_2d(v_s + lane * page_size * 128, &map_v, 0, row, &kv_full);
+                unsigned char* k_dst = kv_s + st * 2 * TA_TILE_BYTES + lane * box * 128;
+                tma_load_2d(k_dst, &map_k, 0, row, &kv_full[st]);
+                tma_load_2d(k_dst + TA_TILE_BYTES, &map_v, 0, row, &kv_full[st]);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(TA_ROWS, TA_KEYS);
             const uint32_t idesc_o = umma_idesc(TA_ROWS, TA_D) | (1u << 16);   // B is MN-major
-            bool ok = mbar_wait(&q_full, 0, error, 2);
-            for (int kt = t_lo; kt < t_hi && ok; ++kt) {
-                const uint32_t parity = (uint32_t)((kt - t_lo) & 1);
-                ok = mbar_wait(&kv_full, parity, error, 2);
-                if (!ok) break;
+            const uint64_t qd = umma_desc(q_s);
+            bool ok = n_tiles > 0 && mbar_wait(&q_full, 0, error, 2);
+            // S(i) = Q K(i)^T into score buffer i & 1
+            auto issue_scores = [&](int i) -> bool {
+                const int st = i % TA_STAGES;
+                if (!mbar_wait(&kv_full[st], (uint32_t)((i / TA_STAGES) & 1), error, 2)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t qd = umma_desc(q_s), kd = umma_desc(k_s);
+                const uint64_t kd = umma_desc(kv_s + st * 2 * TA_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < TA_D / 16; ++k)
-                    umma_bf16(tmem_s, qd + (uint64_t)(2 * k), kd + (uint64_t)(2 * k), idesc_s, k > 0);
-                umma_commit(&s_ready);
-                ok = mbar_wait(&p_ready, parity, error, 5);
+                    umma_bf16(tmem_s + (uint32_t)((i & 1) * TA_KEYS), qd + (uint64_t)(2 * k),
+                              kd + (uint64_t)(2 * k), idesc_s, k > 0);
+                umma_commit(&s_ready[i & 1]);
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                // the scores of the next tile first: their buffer was read by the softmax of
+                // tile i - 1, which handed P(i - 1) over before this point
+                if (i + 1 < n_tiles) ok = issue_scores(i + 1);
+                if (!ok) break;
+                ok = mbar_wait(&p_ready[i & 1], (uint32_t)((i >> 1) & 1), error, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t vd = umma_desc_mn(v_s);
+                const int st = i % TA_STAGES;
+                const uint64_t vd = umma_desc_mn(kv_s + st * 2 * TA_TILE_BYTES + TA_TILE_BYTES);
+                const uint64_t pd = umma_desc(p_s + (i & 1) * (TA_ROWS * 128));
 #pragma unroll
-                for (int k = 0; k < TA_KEYS / 16; ++k) {
-                    const uint64_t pd = umma_desc(p_s + (k / 4) * (TA_ROWS * 128)) + (uint64_t)(2 * (k % 4));
-                    umma_bf16(tmem_o, pd, vd + (uint64_t)(k * (2048 >> 4)), idesc_o, k > 0);
-                }
-                umma_commit(&o_ready);
+                for (int k = 0; k < TA_KEYS / 16; ++k)
+                    umma_bf16(tmem_o, pd + (uint64_t)(2 * k), vd + (uint64_t)(k * (2048 >> 4)),
+                              idesc_o, i > 0 || k > 0);
+                umma_commit(&o_ready[i & 1]);       // O holds tiles 0 .. i
+                umma_commit(&kv_free[st]);
             }
         }
     } else {
-        // ---------------------------------------------------------------- softmax: row = thread
-        const int r = warp * 32 + lane;
+        // ------------------------------------------------------- softmax: two threads per row
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;
         const int tok = tok0 + r / group;
         const int hg = r % group;
         const bool row_ok = r < group * tok_per_tile && tok < q_len;
         const int pos = first_pos + tok;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t col0 = (uint32_t)(half * TA_HALF);
         const float scale2 = scale * 1.4426950408889634f;
-        float o[TA_D];
-#pragma unroll
-        for (int c = 0; c < TA_D; ++c) o[c] = 0.f;
+        // the two warps of a lane quarter meet on an mbarrier of their own (a bounded wait,
+        // like every other wait of this kernel); `meetings` counts them for the parity
+        int meetings = 0;
+        auto pair_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&pair_met[quarter])) : "memory");
+            bool met = mbar_wait(&pair_met[quarter], (uint32_t)(meetings & 1), error, 6);
+            ++meetings;
+            return __all_sync(0xffffffffu, met);
+        };
+        // m: the maximum that O and l are relative to (log2 units); l: this thread's keys only
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int kt = t_lo; kt < t_hi; ++kt) {
-            const uint32_t parity = (uint32_t)((kt - t_lo) & 1);
-            ok = mbar_wait(&s_ready, parity, error, 3);
+        const uint32_t my_o = tmem_o + lane_addr + col0;
+        for (int i = 0; i < n_tiles; ++i) {
+            const int st = i % TA_STAGES, kt = t_first + i;
+            ok = mbar_wait(&s_ready[i & 1], (uint32_t)((i >> 1) & 1), error, 3);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sv[TA_HALF];
+            tmem_load_32(tmem_s + lane_addr + (uint32_t)((i & 1) * TA_KEYS) + col0, sv);
             const int key0 = kt * TA_KEYS;
             // does every key of the tile count for this row, and is every key real?
             const bool plain = row_ok && key0 + TA_KEYS - 1 <= pos && key0 + TA_KEYS <= kv_len &&
                                (window <= 0 || key0 > pos - window);
-            // pass 1: the row's maximum over the tile
-            float m_new = m;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TA_KEYS; c0 += 32) {
-                uint32_t sv[32];
-                tmem_load_32(tmem_s + lane_addr + (uint32_t)c0, sv);
+            if (!plain) {
+                // a key that does not count becomes -inf in place
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = key0 + c0 + j;
-                    bool seen = plain;
-                    if (!plain) {
-                        seen = row_ok && key <= pos && key < kv_len && page_ok[c0 + j];
-                        if (window > 0) seen = seen && key > pos - window;
-                    }
-                    if (seen) m_new = fmaxf(m_new, __uint_as_float(sv[j]) * scale2);
+                for (int j = 0; j < TA_HALF; ++j) {
+                    const int key = key0 + (int)col0 + j;
+                    bool seen = row_ok && key <= pos && key < kv_len && page_ok[st][col0 + j];
+                    if (window > 0) seen = seen && key > pos - window;
+                    sv[j] = seen ? sv[j] : 0xff800000u;
                 }
             }
-            const float corr = m_new > -INFINITY ? ta_exp2(m - m_new) : 1.f;
-            m = m_new;
-            l *= corr;
-            // pass 2: probabilities, rounded to bfloat16, into the swizzled P tile
-#pragma unroll 1
-            for (int c0 = 0; c0 < TA_KEYS; c0 += 32) {
-                uint32_t sv[32];
-                tmem_load_32(tmem_s + lane_addr + (uint32_t)c0, sv);
-                unsigned char* prow = p_s + (c0 / 64) * (TA_ROWS * 128) + r * 128;
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 packed;
-                    uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+            for (int j = 0; j < TA_HALF; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(sv[j]));
+            const float part = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+            row_xch[i & 1][half][r] = part;
+            ok = pair_sync();
+            if (!ok) break;
+            const float m_tile = fmaxf(part, row_xch[i & 1][half ^ 1][r]);
+            if (i == 0) {
+                m = m_tile;
+            } else if (__any_sync(0xffffffffu, m_tile > m + TA_RAISE)) {
+                // some row of this warp outgrew its maximum: every row moves to its exact
+                // maximum and the warp rescales its rows of O, once P(i-1) V(i-1) is in
+                const float m_new = fmaxf(m, m_tile);
+                const float factor = m > -INFINITY ? ta_exp2(m - m_new) : 1.f;
+                m = m_new;
+                l *= factor;
+                ok = mbar_wait(&o_ready[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), error, 4);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t ov[TA_HALF];
+                tmem_load_32(my_o, ov);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float p2[2];
-#pragma unroll
-                        for (int z = 0; z < 2; ++z) {
-                            const int j = q4 * 8 + e * 2 + z;
-                            const int key = key0 + c0 + j;
-                            bool seen = plain;
-                            if (!plain) {
-                                seen = row_ok && key <= pos && key < kv_len && page_ok[c0 + j];
-                                if (window > 0) seen = seen && key > pos - window;
-                            }
-                            const float p = (seen && m > -INFINITY)
-                                                ? ta_exp2(__uint_as_float(sv[j]) * scale2 - m)
-                                                : 0.f;
-                            l += p;
-                            p2[z] = p;
-                        }
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p2[0], p2[1]);
-                        pw[e] = *reinterpret_cast<uint32_t*>(&h2);
-                    }
-                    const int chunk = (c0 % 64) / 8 + q4;          // 16-byte chunk inside the 128-byte row
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) * 16)) = packed;
-                }
+                for (int c = 0; c < TA_HALF; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+                tmem_store_32(my_o, ov);
+                tmem_wait_st();
             }
+            // probabilities, rounded to bfloat16, into the swizzled P tile; a row that has
+            // seen no key yet (m = -inf) gets zeros: (-inf) * scale2 - 0 = -inf, 2^-inf = 0
+            const float shift = m > -INFINITY ? m : 0.f;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            unsigned char* prow = p_s + (i & 1) * (TA_ROWS * 128) + r * 128;
+#pragma unroll
+            for (int c = 0; c < TA_HALF / 8; ++c) {
+                uint4 packed;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = ta_exp2(__uint_as_float(sv[c * 8 + 2 * e]) * scale2 - shift);
+                    const float p1 = ta_exp2(__uint_as_float(sv[c * 8 + 2 * e + 1]) * scale2 - shift);
+                    sum[e] += p0 + p1;
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                    pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                const int chunk = half * (TA_HALF / 8) + c;
+                *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) * 16)) = packed;
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             // a value row that was not copied, or lies beyond the sequence, must not reach the
-            // MMA as it is (0 * NaN): thread r clears key r of the tile
-            if (!page_ok[r]) {
-                uint4 zero = make_uint4(0, 0, 0, 0);
+            // MMA as it is (0 * NaN): the first 64 threads each clear one key of the tile
+            if (half == 0 && r < TA_KEYS && !page_ok[st][r]) {
+                unsigned char* v_row = kv_s + st * 2 * TA_TILE_BYTES + TA_TILE_BYTES + r * 128;
+                const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(v_s + r * 128 + c * 16) = zero;
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(v_row + c * 16) = zero;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0)
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready)) : "memory");
-            ok = mbar_wait(&o_ready, parity, error, 4);
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[i & 1])) : "memory");
+        }
+        // the output: all tiles are in once the last P V has been committed
+        float o[TA_HALF];
+#pragma unroll
+        for (int c = 0; c < TA_HALF; ++c) o[c] = 0.f;
+        if (ok && n_tiles > 0) {
+            ok = mbar_wait(&o_ready[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), error, 4);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t ov[TA_HALF];
+                tmem_load_32(my_o, ov);
 #pragma unroll
-            for (int c0 = 0; c0 < TA_D; c0 += 32) {
-                uint32_t ov[32];
-                tmem_load_32(tmem_o + lane_addr + (uint32_t)c0, ov);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * corr + __uint_as_float(ov[j]);
-            }
-            // the next tile's P.V may overwrite tmem_o only after this read: ordered by the
-            // p_ready arrival of the next tile, which comes after it in program order
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        }
-        if (ok && row_ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * TA_D;
-#pragma unroll
-            for (int c = 0; c < TA_D; c += 8) {
-                uint4 q;
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    h2[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
-                *reinterpret_cast<uint4*>(dst + c) = q;
+                for (int c = 0; c < TA_HALF; ++c) o[c] = __uint_as_float(ov[c]);
             }
         }
+        // the row's sum: both halves
+        if (ok) {
+            row_xch[n_tiles & 1][half][r] = l;
+            ok = pair_sync();
+            l += row_xch[n_tiles & 1][half ^ 1][r];
+        }
+        if (cl_size == 1) {
+            if (ok && row_ok) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                __nv_bfloat16* dst =
+                    out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * TA_D + col0;
+#pragma unroll
+                for (int c = 0; c < TA_HALF; c += 8) {
+                    uint4 q;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        h2[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
+                    *reinterpret_cast<uint4*>(dst + c) = q;
+                }
+            }
+        } else {
+            // this CTA's share of the keys, for the merge below: the key/value ring is free
+            // (every tile loaded was consumed); four columns of a row lie together and the
+            // rows of a column group follow each other, so that a warp writes whole lines
+            float4* merge_o = reinterpret_cast<float4*>(kv_s);              // [16 groups][128 rows]
+            float* merge_ml = reinterpret_cast<float*>(merge_o + (TA_D / 4) * TA_ROWS);   // [m, l][128]
+#pragma unroll
+            for (int c = 0; c < TA_HALF; c += 4)
+                merge_o[(((int)col0 + c) / 4) * TA_ROWS + r] = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+            if (half == 0) {
+                merge_ml[r] = m;
+                merge_ml[TA_ROWS + r] = l;
+            }
+        }
+    }
+    if (cl_size > 1) {
+        // Every thread of every CTA of the cluster comes here (a CTA without key tiles too).
+        __syncthreads();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (cl_rank == 0 && warp < 8) {
+            const int quarter = warp & 3, half = warp >> 2;
+            const int r = quarter * 32 + lane;
+            const int tok = tok0 + r / group, hg = r % group;
+            const bool row_ok = r < group * tok_per_tile && tok < q_len;
+            const int col0 = half * TA_HALF;
+            const uint32_t local_o = smem_u32(kv_s);
+            const uint32_t local_ml = local_o + TA_D * TA_ROWS * 4;
+            uint32_t remote_o[4];
+            float weight[4], l_of[4];
+            float m_all = -INFINITY, l_all = 0.f;
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                weight[k] = -INFINITY;
+                l_of[k] = 0.f;
+                remote_o[k] = local_o;
+                if (k < cl_size) {
+                    uint32_t remote_ml;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_o[k]) : "r"(local_o), "r"(k));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_ml) : "r"(local_ml), "r"(k));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(weight[k]) : "r"(remote_ml + 4 * r) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l_of[k]) : "r"(remote_ml + 4 * (TA_ROWS + r)) : "memory");
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m_all = fmaxf(m_all, weight[k]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                weight[k] = weight[k] > -INFINITY ? ta_exp2(weight[k] - m_all) : 0.f;
+                l_all += l_of[k] * weight[k];
+            }
+            if (row_ok) {
+                const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+                __nv_bfloat16* dst =
+                    out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * TA_D + col0;
+#pragma unroll
+                for (int c = 0; c < TA_HALF; c += 8) {
+                    // all loads of these eight columns first, then the sums
+                    float4 part[4][2];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                        for (int g4 = 0; g4 < 2; ++g4) {
+                            part[k][g4] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (weight[k] != 0.f) {    // a CTA without keys for this row is skipped
+                                const uint32_t at =
+                                    remote_o[k] + 16u * (uint32_t)(((col0 + c) / 4 + g4) * TA_ROWS + r);
+                                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(part[k][g4].x), "=f"(part[k][g4].y),
+                                               "=f"(part[k][g4].z), "=f"(part[k][g4].w)
+                                             : "r"(at)
+                                             : "memory");
+                            }
+                        }
+                    }
+                    float acc[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                        for (int g4 = 0; g4 < 2; ++g4) {
+                            acc[4 * g4 + 0] += part[k][g4].x * weight[k];
+                            acc[4 * g4 + 1] += part[k][g4].y * weight[k];
+                            acc[4 * g4 + 2] += part[k][g4].z * weight[k];
+                            acc[4 * g4 + 3] += part[k][g4].w * weight[k];
+                        }
+                    }
+                    uint4 q;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        h2[e] = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+                    *reinterpret_cast<uint4*>(dst + c) = q;
+                }
+            }
+        }
+        // nobody leaves (and gives its shared memory up) before the merge has read it
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -308,19 +492,20 @@ MB_EXPORT int mb_attention_tcgen05_supports(int d, int page_size, int n_q, int n
     if (d != TA_D || n_kv <= 0 || n_q % n_kv) return 0;
     const int group = n_q / n_kv;
     if (group > TA_ROWS) return 0;
-    if (page_size < 8 || page_size > TA_KEYS || (page_size & (page_size - 1))) return 0;
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return 0;
     return q_row_stride % 8 == 0;
 }
 
 // qkv: [tokens, q_row_stride] bfloat16 with the rotated queries first; k_pages / v_pages:
 // [num_pages, n_kv, page_size, 64]; out: [tokens, n_q * 64]. `error` as for mb_gemm_tcgen05
-// (codes 1 producer, 2 and 5 MMA issuer, 3 and 4 softmax).
+// (codes 1 producer, 2 and 5 MMA issuer, 3, 4 and 6 softmax). `cluster` (1, 2 or 4) is the
+// number of CTAs that share a row tile and split its keys.
 MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, const void* k_pages,
                                          const void* v_pages, int num_pages, const int* table,
                                          int max_pages, const int* q_start, const int* kv_len,
                                          void* out, int tokens, int num_seqs, int max_q_len, int n_q,
                                          int n_kv, int d, int page_size, float scale, int window,
-                                         int* error, void* stream) {
+                                         int cluster, int* error, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_tcgen05_supports(d, page_size, n_q, n_kv, q_row_stride)) return MB_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) return MB_ERR_ALIGNMENT;
@@ -338,12 +523,12 @@ MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, cons
         const cuuint64_t rows = (cuuint64_t)num_pages * n_kv * page_size;
         cuuint64_t dims[2] = {(cuuint64_t)TA_D, rows};
         cuuint64_t strides[1] = {(cuuint64_t)TA_D * 2};
-        cuuint32_t box[2] = {(cuuint32_t)TA_D, (cuuint32_t)page_size};
+        cuuint32_t box[2] = {(cuuint32_t)TA_D, (cuuint32_t)(page_size < TA_KEYS ? page_size : TA_KEYS)};
         if (!make_map_nd(&map_k, k_pages, 2, dims, strides, box) ||
             !make_map_nd(&map_v, v_pages, 2, dims, strides, box))
             return MB_ERR_LAUNCH;
     }
-    const size_t smem = (size_t)(TA_ROWS + 2 * TA_KEYS + 2 * TA_ROWS) * 128 + 1024;
+    const size_t smem = (size_t)(TA_ROWS + TA_STAGES * 2 * TA_KEYS + 2 * TA_ROWS) * 128 + 1024;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -352,10 +537,24 @@ MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, cons
         raised = true;
     }
     const int tiles_per_seq = (max_q_len + tok_per_tile - 1) / tok_per_tile;
-    dim3 grid(num_seqs * tiles_per_seq, n_kv);
-    if (n_kv > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    MB_LAUNCH((attention_tcgen05_kernel), grid, TA_THREADS, smem, (cudaStream_t)stream, map_q, map_k, map_v,
-              table, max_pages, q_start, kv_len, (__nv_bfloat16*)out, n_q, n_kv, page_size, scale, window,
-              tiles_per_seq, error);
+    if (n_kv > 65535 || (cluster != 1 && cluster != 2 && cluster != 4)) return MB_ERR_UNSUPPORTED_SIZE;
+    // the CTAs of a cluster lie along z and share (row tile, KV head)
+    dim3 grid(num_seqs * tiles_per_seq, n_kv, cluster);
+    cudaLaunchConfig_t config = launch_config(grid, TA_THREADS, smem, (cudaStream_t)stream);
+    cudaLaunchAttribute attrs[2];
+    int num_attrs = 0;
+    if (config.numAttrs) attrs[num_attrs++] = config.attrs[0];
+    if (cluster > 1) {
+        attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[num_attrs].val.clusterDim.x = 1;
+        attrs[num_attrs].val.clusterDim.y = 1;
+        attrs[num_attrs].val.clusterDim.z = (unsigned)cluster;
+        ++num_attrs;
+    }
+    config.attrs = attrs;
+    config.numAttrs = num_attrs;
+    cudaLaunchKernelEx(&config, attention_tcgen05_kernel, map_q, map_k, map_v, table, max_pages, q_start,
+                       kv_len, (__nv_bfloat16*)out, n_q, n_kv, page_size, scale, window, tiles_per_seq,
+                       error);
     return launch_status();
 }

@@ -43,9 +43,10 @@ class CudaOps:
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
-        # "mma": the mma.sync kernels (the default: faster today); "auto": the tensor-memory
-        # kernel for prompt portions of head size 64
-        self.attention = "mma"
+        # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head size 64, the
+        # mma.sync kernels for everything else; "mma": the mma.sync kernels only
+        self.attention = "auto"
+        self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         self.prompt_splits: int | None = None   # override of the key split of prompt portions
         # Normalising inside the consuming product saves a launch but makes every block
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
@@ -346,6 +347,21 @@ class CudaOps:
             return 1
         return max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
 
+    def _prompt_cluster(self, batch, num_kv_heads, group) -> int:
+        """CTAs per row tile of the tensor-memory attention. Every CTA of a causal prompt is
+        resident from the start, so the walk over the keys of the last row tile sets the
+        kernel's time; as long as the device has room, 2 or 4 CTAs share a row tile and
+        split its keys (merged through distributed shared memory)."""
+        if self.prompt_cluster is not None:
+            return self.prompt_cluster
+        tokens_per_tile = max(1, 128 // group)
+        ctas = batch.num_seqs * -(-batch.max_q_len // tokens_per_tile) * num_kv_heads
+        key_tiles = -(-batch.max_kv_len // 64)
+        cluster = 1
+        while cluster < 4 and key_tiles >= 8 * cluster and ctas * cluster < 4 * self.sm_count:
+            cluster *= 2
+        return cluster
+
     def _prompt_splits(self, batch, num_kv_heads, group) -> int:
         """Key ranges per row tile of a prompt portion. Cutting the keys (and merging the
         ranges afterwards) shortens the chain of the last, heaviest row tile, but on B200 a
@@ -374,7 +390,8 @@ class CudaOps:
                 _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), cache.k.shape[0],
                 _ptr(cache.table), cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
                 _ptr(out), tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads,
-                head_dim, cache.page_size, float(scale), int(window), _ptr(self._error_word()),
+                head_dim, cache.page_size, float(scale), int(window),
+                self._prompt_cluster(batch, num_kv_heads, group), _ptr(self._error_word()),
                 self._stream()), "paged_attention (tcgen05)")
             self.launches += 1
             self._tc_pending = True

@@ -401,6 +401,9 @@ ATTENTION_CASES = [
     (14, 2, 64, 16, (130, 1, 9), (130, 515, 300), 0),
     (6, 3, 128, 32, (70, 2), (200, 66), 50),
     (8, 1, 64, 8, (1, 1, 1), (64, 65, 1000), 0),
+    (14, 2, 64, 64, (200, 3), (500, 131), 0),
+    (7, 7, 64, 128, (150,), (400,), 0),
+    (4, 2, 64, 16, (300, 1, 70), (600, 200, 70), 100),
 ]
 
 
@@ -426,9 +429,11 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     n_q, n_kv, d, page, q_lens, kv_lens, window = ATTENTION_CASES[case]
     if kernel == "mma" and not ops.lib.mb_attention_mma_supports(d):
         pytest.skip("head size left to the CUDA-core kernel")
-    if kernel == "tcgen05" and (splits != 1 or not ops.lib.mb_attention_tcgen05_supports(
-            d, page, n_q, n_kv, (n_q + 2 * n_kv) * d)):
+    if kernel == "tcgen05" and not ops.lib.mb_attention_tcgen05_supports(
+            d, page, n_q, n_kv, (n_q + 2 * n_kv) * d):
         pytest.skip("left to the other attention kernels")
+    # for the tensor-memory kernel the split is the number of CTAs that share a row tile
+    clusters = (None,) if kernel != "tcgen05" else ((1,) if splits == 1 else (2, 4))
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 5
     drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
     batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=3, seed=1,
@@ -450,13 +455,15 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     close(torch.nan_to_num(k), torch.nan_to_num(k_twin), dtype, "stored keys")
     close(torch.nan_to_num(v), torch.nan_to_num(v_twin), dtype, "stored values")
 
-    got = torch.zeros((tokens, n_q * d), dtype=dtype, device="cuda")
-    want = torch.zeros_like(got)
-    ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got, kernel=kernel)
+    want = torch.zeros((tokens, n_q * d), dtype=dtype, device="cuda")
     twin.paged_attention(qkv_twin, n_q, n_kv, d, batch, cache_twin, d ** -0.5, window, want)
-    ops.check_errors()
-    assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
-    attention_close(got[live], want[live], dtype, kernel)
+    for cluster in clusters:
+        ops.prompt_cluster = cluster
+        got = torch.zeros_like(want)
+        ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got, kernel=kernel)
+        ops.check_errors()
+        assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
+        attention_close(got[live], want[live], dtype, kernel)
 
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
