@@ -30,7 +30,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 
 // Bounded wait for the phase with the given parity; false (and the error word set) if it
 // never came. try_wait itself suspends the thread for a while when the phase is not there
-// yet; the clock is read only now and then, so that a waiting warp takes few issue slots.
+// yet (a suspend-time hint changed nothing measurable); the clock is read only now and then.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error, int code) {
     const uint32_t addr = smem_u32(bar);
     long long start = 0;
