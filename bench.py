@@ -236,8 +236,6 @@ def prefill_rate(torch, runner, vocab, reps=5):
 def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
     """Decode tokens/s through Engine.step(): host tokens in, host tokens out."""
     from mercury_b200 import Engine, EngineConfig, SamplingParams
-    from mercury_b200.engine.request import RequestState
-
     runner = make_runner(torch, config, tensors, batch, batch * (context + 256))
     cfg = EngineConfig(model="(in memory)", dtype="bfloat16", block_size=BLOCK,
                        num_blocks=runner.cache.pools[0].num_pages, max_running=batch,
@@ -246,12 +244,17 @@ def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
     engine = Engine(cfg, runner=runner)
     gen = torch.Generator().manual_seed(SEED + 4)
     produced = []
+    started = set()
+
+    def sink(event):
+        produced.append(event.kind)
+        started.add(event.rid)
+
     for b in range(batch):
         prompt = torch.randint(0, vocab, (context,), generator=gen).tolist()
-        engine.submit(f"e2e-{b}", prompt, steps + warmup + batch + 8, lambda ev: produced.append(ev.kind),
+        engine.submit(f"e2e-{b}", prompt, steps + warmup + batch + 8, sink,
                       SamplingParams(ignore_eos=True))
-    while any(r.seq_len - r.num_computed != 1 or r.state is not RequestState.RUNNING
-              for r in engine.sched.running + engine.sched.waiting) or not engine.sched.running:
+    while len(started) < batch:          # prompts first: until every request decodes
         engine.step()
     for _ in range(warmup):
         engine.step()

@@ -57,6 +57,7 @@ class EngineConfig:
     prefix_caching: bool = True
     cryptographic_hashes: bool = False
     cuda_graphs: bool = True
+    lookahead: bool = True
     seed: int = 0
     debug_invariants: bool = False
     max_step_records: int = 500_000

@@ -21,6 +21,16 @@ __global__ void embed_kernel(const int* __restrict__ ids, const void* __restrict
         out[(int64_t)t * hidden + c] = ok ? load_as_float(table, base + c, table_dtype) : 0.f;
 }
 
+// Token ids that were not known on the host when the step was put together (the step was
+// launched while the step before was still running): ids[t] = sampled[from[t]] where
+// from[t] >= 0, taken from the tokens the step before has sampled on the device.
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ from,
+                                    const int* __restrict__ sampled, int tokens) {
+    grid_dependency_sync();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < tokens && from[t] >= 0) ids[t] = sampled[from[t]];
+}
+
 // ---------------------------------------------------------------------------- norm
 // One block per row. x = h + delta (float32); when `rows` is null the sum is stored back
 // as the new residual (mercury/model/qwen2.py:27-28); y = x * rsqrt(mean(x^2) + eps) * w
@@ -312,6 +322,13 @@ MB_EXPORT int mb_embed(const int* ids, const void* table, int table_dtype, float
     if (tokens <= 0) return MB_OK;
     MB_LAUNCH((embed_kernel), tokens, 256, 0, (cudaStream_t)stream, ids, table, table_dtype, out, hidden,
                                                             vocab);
+    return launch_status();
+}
+
+MB_EXPORT int mb_patch_tokens(int* ids, const int* from, const int* sampled, int tokens, void* stream) {
+    if (tokens <= 0) return MB_OK;
+    MB_LAUNCH((patch_tokens_kernel), (tokens + 127) / 128, 128, 0, (cudaStream_t)stream, ids, from, sampled,
+              tokens);
     return launch_status();
 }
 

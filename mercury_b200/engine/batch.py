@@ -10,10 +10,12 @@ goes to the device in one copy.
 Layout of the buffer for capacities (tokens Tc, sequences Sc, pages per sequence Pc,
 logit rows Rc, groups G):
 
-    token_ids[Tc] positions[Tc] seq_of_token[Tc] q_start[Sc+1] kv_len[Sc] slots[Sc]
-    logit_rows[Rc] tables[G][Sc][Pc]
+    token_ids[Tc] positions[Tc] seq_of_token[Tc] token_from[Tc] q_start[Sc+1] kv_len[Sc]
+    slots[Sc] logit_rows[Rc] tables[G][Sc][Pc]
 
 Unused token rows carry sequence -1 (kernels skip them), unused sequences have q_len 0.
+`token_from[t]` is -1, or the row of the previous step's sampled tokens that token t is to
+be taken from on the device (the host did not know it yet when the batch was built).
 """
 
 from __future__ import annotations
@@ -30,12 +32,15 @@ from ..cache.manager import Sequence
 class StepEntry:
     """`tokens` are the next tokens of `seq` (positions seq.num_computed ...); `want` lists
     the indices among them whose logits are asked for; `hashes` are the chain hashes of the
-    sequence's full pages, if its pages are to become shareable."""
+    sequence's full pages, if its pages are to become shareable. `late` = (index among
+    `tokens`, row of the previous step's samples) names a token whose id is still on the
+    device: the step was put together before the step in front had been read back."""
 
     seq: Sequence
     tokens: list[int]
     want: list[int]
     hashes: list[int] | None = None
+    late: tuple[int, int] | None = None
 
 
 @dataclass
@@ -48,6 +53,7 @@ class StepBatch:
     token_ids: torch.Tensor
     positions: torch.Tensor
     seq_of_token: torch.Tensor
+    token_from: torch.Tensor
     q_start: torch.Tensor
     kv_len: torch.Tensor
     slots: torch.Tensor
@@ -55,6 +61,7 @@ class StepBatch:
     tables: list[torch.Tensor]
     decode_only: bool = False
     attention_splits: int | None = None   # fixed split of the keys, when a graph needs one
+    late_tokens: bool = False             # whether any token id still has to come from the device
 
 
 class BatchBuffers:
@@ -83,7 +90,8 @@ class BatchBuffers:
         self._in_flight = False
 
     def _layout(self, tc: int, sc: int, pc: int, rc: int) -> dict:
-        names = [("token_ids", tc), ("positions", tc), ("seq_of_token", tc), ("q_start", sc + 1),
+        names = [("token_ids", tc), ("positions", tc), ("seq_of_token", tc), ("token_from", tc),
+                 ("q_start", sc + 1),
                  ("kv_len", sc), ("slots", sc), ("logit_rows", rc),
                  ("tables", self.num_groups * sc * pc)]
         out, offset = {}, 0
@@ -130,6 +138,9 @@ class BatchBuffers:
             return buf[start:start + count]
 
         token_ids, positions, seq_of = view("token_ids"), view("positions"), view("seq_of_token")
+        token_from = view("token_from")
+        token_from[:] = -1
+        late_tokens = False
         q_start, kv_len, slots = view("q_start"), view("kv_len"), view("slots")
         logit_rows = view("logit_rows")
         tables = view("tables").reshape(self.num_groups, sc, pc)
@@ -171,6 +182,9 @@ class BatchBuffers:
                 self._row_written[group][index] = held
             n = len(e.tokens)
             base = index if decode_only else cursor
+            if e.late is not None:
+                token_from[base + e.late[0]] = e.late[1]
+                late_tokens = True
             for w in (e.want if row_capacity is None else ()):
                 if not 0 <= w < n:
                     raise ValueError(f"{e.seq.seq_id}: wanted place {w} is outside its {n} tokens")
@@ -213,9 +227,10 @@ class BatchBuffers:
         return StepBatch(
             num_tokens=tc, num_seqs=sc, max_q_len=max_q, max_kv_len=max_kv, num_logit_rows=rows,
             token_ids=dview("token_ids"), positions=dview("positions"),
-            seq_of_token=dview("seq_of_token"), q_start=dview("q_start"), kv_len=dview("kv_len"),
+            seq_of_token=dview("seq_of_token"), token_from=dview("token_from"),
+            q_start=dview("q_start"), kv_len=dview("kv_len"),
             slots=dview("slots"),
             logit_rows=dview("logit_rows")[:rows if row_capacity is None else rc],
             tables=[t for t in dview("tables").view(self.num_groups, sc, pc)],
-            decode_only=decode_only,
+            decode_only=decode_only, late_tokens=late_tokens,
         )

@@ -5,12 +5,20 @@
 (tests/test_runner.py:65-77 of the reference): submit every prompt, step until nothing is
 left, return the tokens by request. The loop runs on the caller's thread; there is no
 server around it.
+
+A step is launched and read back in two halves, and `step()` puts the launch of the next
+step between them whenever the next plan cannot depend on what the tokens turn out to be:
+the requests that go on get a stand-in for the token that is still on the device, the
+scheduler plans with it, the next step takes the real ids from the device, and only then
+does the host wait for the tokens of the step in front. The GPU so never waits for the
+host's bookkeeping. A request that ends on a token read this way (end of sequence) has
+one surplus token computed, which is dropped.
 """
 
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Callable
 
 from ..cache.hashing import extend_hashes
@@ -39,6 +47,19 @@ class StreamEvent:
 
 
 Sink = Callable[[StreamEvent], None]
+
+STAND_IN = -1     # in a request's output: a token sampled on the device and not read back yet
+
+
+@dataclass
+class _Flight:
+    """A step that has been launched: its plan, whose row of sampled tokens is whose, and
+    the sampler's handle to read them back with."""
+
+    plan: Plan
+    sampling: list[Request] = field(default_factory=list)
+    handle: tuple[int, int] | None = None
+    t_start: float = 0.0
 
 
 class Engine:
@@ -69,6 +90,8 @@ class Engine:
         self._commands: list[tuple[str, object]] = []
         self._sinks: dict[str, Sink] = {}
         self._submitted = 0
+        self._flight: _Flight | None = None
+        self.lookahead = cfg.lookahead
 
     # ------------------------------------------------------------------ client side
 
@@ -130,7 +153,7 @@ class Engine:
 
     def run_until_idle(self) -> None:
         self._drain_commands()
-        while self.sched.has_work() or self._commands:
+        while self.sched.has_work() or self._commands or self._flight is not None:
             if self.step() is None and not self._commands and self.sched.has_work():
                 raise RuntimeError("the scheduler has work but planned nothing: the pool is too "
                                    "small for the waiting request")
@@ -138,40 +161,104 @@ class Engine:
     # ------------------------------------------------------------------ the loop
 
     def step(self) -> StepRecord | None:
+        """Read back one step (launching it first if none is under way) and, where that is
+        safe, launch the step after it before waiting for the tokens."""
         t_start = time.perf_counter()
         self._drain_commands()
+        flight = self._flight
+        self._flight = None
+        if flight is None:
+            flight = self._launch(None, t_start)
+            if flight is None:
+                self.metrics.counters["idle_steps"] += 1
+                return None
+        ahead = None
+        if self.lookahead and self._can_look_ahead(flight):
+            for r in flight.sampling:
+                if len(r.out) + 1 < r.max_tokens:      # it goes on unless this token ends it
+                    r.out.append(STAND_IN)
+                    r.unread = 1
+            ahead = self._launch(flight, time.perf_counter())
+            if ahead is not None:
+                self.metrics.counters["steps_launched_ahead"] += 1
+        record = self._complete(flight)
+        self._flight = ahead
+        return record
+
+    def _can_look_ahead(self, flight: _Flight) -> bool:
+        """Whether the plan of the next step is the same whatever the tokens of this one
+        are: nobody new could be admitted, nobody has to be preempted for pages, and no
+        command is waiting. (A request that ends on its token is found out one step late;
+        that costs one surplus token, not a different plan for the others.)"""
+        if self._commands:
+            return False
+        sched = self.sched
+        ending = any(len(r.out) + 1 >= r.max_tokens for r in flight.sampling)
+        if sched.waiting and (ending or (len(sched.running) < sched.max_running
+                                         and self.cache.has_slot())):
+            return False
+        short = [0] * len(self.cache.pools)
+        sampled = {id(r) for r in flight.sampling}
+        for r in sched.running:
+            if r.seq is None:
+                continue
+            length = r.seq_len + (1 if id(r) in sampled else 0)
+            target = min(length, r.num_computed + sched.prefill_chunk)
+            for group, pages in enumerate(self.cache.pages_short(r.seq, target)):
+                short[group] += pages
+        return all(n <= free for n, free in zip(short, self.cache.num_available()))
+
+    def _launch(self, before: _Flight | None, t_start: float) -> _Flight | None:
+        """Plan a step and put it on the device. `before` is the step in front if its tokens
+        have not been read yet: stand-ins among this step's inputs are taken from there."""
         plan: Plan = self.sched.schedule(self.clock())
         for r in plan.preempted:
             self._emit(r, StreamEvent(rid=r.rid, kind="preempted", t=self.clock()))
         if not plan:
-            self.metrics.counters["idle_steps"] += 1
             return None
-
+        row_of = {id(r): row for row, r in enumerate(before.sampling)} if before else {}
         entries, sampling = [], []
         page = self.cache.page_size
         for e in plan.entries:
             r = e.request
             hashes = None
             if self.sched.prefix_caching:
-                if r.seq_len // page > len(r.hashes):
-                    extend_hashes(r.hashes, r.tokens, page, self.cfg.cryptographic_hashes)
+                # pages are hashed (and shared) only once all their tokens are known
+                if r.known_len // page > len(r.hashes):
+                    extend_hashes(r.hashes, r.tokens[:r.known_len], page,
+                                  self.cfg.cryptographic_hashes)
                 hashes = r.hashes
+            late = None
+            if r.unread and e.start + e.count == r.seq_len:
+                late = (e.count - 1, row_of[id(r)])
             entries.append(StepEntry(r.seq, r.token_slice(e.start, e.count),
-                                     [e.count - 1] if e.samples else [], hashes))
+                                     [e.count - 1] if e.samples else [], hashes, late))
             if e.samples:
                 sampling.append(r)
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, [(r.params, r.seed, len(r.out)) for r in sampling]) \
-            if sampling else []
+        sampled = self.sampler.on_device(before.handle) if before and before.handle else None
+        logits = self.runner.step(entries, sampled)
+        handle = None
+        if sampling:
+            handle = self.sampler.begin(logits, [(r.params, r.seed, len(r.out)) for r in sampling])
+        return _Flight(plan, sampling, handle, t_start)
+
+    def _complete(self, flight: _Flight) -> StepRecord:
+        """Wait for the step's tokens and route them."""
+        tokens = self.sampler.finish(flight.handle) if flight.handle is not None else []
         now = self.clock()
-        for r, token in zip(sampling, tokens):
+        for r, token in zip(flight.sampling, tokens):
+            if r.done:
+                r.unread = 0
+                self.metrics.counters["surplus_tokens"] += 1
+                continue       # ended or aborted while this step ran: a surplus token
             self._accept(r, token, now)
         if self.cfg.debug_invariants:
             self.cache.check_invariants()
+        plan = flight.plan
         record = StepRecord(
             t=now, num_entries=len(plan.entries), num_decode=plan.num_decode,
             num_tokens=plan.num_tokens, sched_s=plan.sched_seconds,
-            step_s=time.perf_counter() - t_start, waiting=len(self.sched.waiting),
+            step_s=time.perf_counter() - flight.t_start, waiting=len(self.sched.waiting),
             running=len(self.sched.running), free_pages=min(self.cache.num_available()),
             preempted=len(plan.preempted))
         self.metrics.add_step(record)
@@ -184,6 +271,9 @@ class Engine:
                 self.sched.add(payload)
             elif kind == "abort":
                 r = self.sched.abort(payload)
+                if r is not None and r.unread:
+                    r.out.pop()            # the stand-in of a token that will not be read
+                    r.unread = 0
                 if r is not None:
                     self.metrics.counters["aborted_requests"] += 1
                     r.finished_at = self.clock()
@@ -194,8 +284,13 @@ class Engine:
                     self._sinks.pop(payload, None)
 
     def _accept(self, r: Request, token: int, now: float) -> None:
-        index = len(r.out)
-        r.out.append(int(token))
+        if r.unread:
+            index = len(r.out) - 1          # the stand-in becomes the token
+            r.out[index] = int(token)
+            r.unread = 0
+        else:
+            index = len(r.out)
+            r.out.append(int(token))
         if r.first_token_at is None:
             r.first_token_at = now
         self._emit(r, StreamEvent(rid=r.rid, kind="token", token=int(token), index=index, t=now))

@@ -36,7 +36,7 @@ class EngineMetrics:
         self.finished: deque[dict] = deque(maxlen=200_000)
         self.counters = {"steps": 0, "idle_steps": 0, "step_tokens": 0, "decode_tokens": 0,
                          "finished_requests": 0, "aborted_requests": 0, "rejected_requests": 0,
-                         "preemptions": 0}
+                         "preemptions": 0, "steps_launched_ahead": 0, "surplus_tokens": 0}
 
     def add_step(self, record: StepRecord) -> None:
         self.steps.append(record)

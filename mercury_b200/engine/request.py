@@ -38,6 +38,9 @@ class Request:
     preemptions: int = 0
     recomputed_tokens: int = 0
     finish_reason: str | None = None
+    # 1 while the last entry of `out` stands for a token that has been sampled on the
+    # device and not yet read back (the engine launched the next step ahead of reading it)
+    unread: int = 0
 
     @property
     def tokens(self) -> list[int]:
@@ -55,6 +58,11 @@ class Request:
     @property
     def seq_len(self) -> int:
         return len(self.prompt) + len(self.out)
+
+    @property
+    def known_len(self) -> int:
+        """Tokens whose ids the host knows."""
+        return len(self.prompt) + len(self.out) - self.unread
 
     @property
     def num_computed(self) -> int:

@@ -174,8 +174,11 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
 
-    def prepare(self, entries: list[StepEntry], **capacities) -> StepBatch:
-        """Provide pages for the entries' tokens and put the batch on the device."""
+    def prepare(self, entries: list[StepEntry], sampled: torch.Tensor | None = None,
+                **capacities) -> StepBatch:
+        """Provide pages for the entries' tokens and put the batch on the device. Token ids
+        that an entry marks as `late` are taken on the device from `sampled`, the tokens the
+        step before has sampled (and the host may not have read yet)."""
         for e in entries:
             if not e.tokens:
                 raise ValueError(f"{e.seq.seq_id}: an entry needs at least one token")
@@ -188,7 +191,13 @@ class ModelRunner:
                     f"{e.seq.seq_id}: no pages left for tokens up to {end} "
                     f"(available per group: {self.cache.num_available()})")
         self._reset_fresh_state()
-        return self.buffers.build(entries, self.page_size, **capacities)
+        batch = self.buffers.build(entries, self.page_size, **capacities)
+        if batch.late_tokens:
+            if sampled is None:
+                raise ValueError("an entry's token is to come from the step before, but its "
+                                 "sampled tokens were not given")
+            self.ops.patch_tokens(batch.token_ids, batch.token_from, sampled)
+        return batch
 
     def run(self, batch: StepBatch) -> torch.Tensor | None:
         """The model pass over a prepared batch; float32 logits `[wanted, vocab]` or None."""
@@ -239,7 +248,7 @@ class ModelRunner:
             return max(1, min(12, sms // rows))
         return max(1, -(-2 * sms // rows))
 
-    def _decode_with_graph(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def _decode_with_graph(self, entries: list[StepEntry], sampled=None) -> torch.Tensor | None:
         """Decode-only steps (one token per entry) replay a CUDA graph captured once per
         batch-size bucket: the launch sequence is fixed and everything that varies (tokens,
         positions, block tables, lengths) is read by the kernels from the step's device
@@ -249,7 +258,7 @@ class ModelRunner:
         capacities = dict(token_capacity=bucket, seq_capacity=bucket, page_capacity=self.max_pages,
                           row_capacity=bucket)
         # every row of the bucket gets logits; rows nobody asked for are dropped below
-        batch = self.prepare(entries, **capacities)
+        batch = self.prepare(entries, sampled, **capacities)
         batch.attention_splits = self._graph_splits(bucket)
         held = self._graphs.get(bucket)
         if held is None:
@@ -284,14 +293,15 @@ class ModelRunner:
             return logits[:len(entries)]
         return logits[torch.tensor(wanted, device=self.device)]
 
-    def _step_with_shape_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
+    def _step_with_shape_graph(self, entries: list[StepEntry], key: tuple,
+                               sampled=None) -> torch.Tensor | None:
         """Steps other than pure decoding are captured per batch shape: the launch sequence
         of a step depends only on (tokens, sequences, longest portion, wanted rows), and a
         server cutting prompts into portions of one size sees the same shapes again and
         again. A shape is captured the second time it is seen; at most `max_shape_graphs`
         are kept. Without this a 2048-token step is bound by the Python launch loop."""
         tokens, seqs, _max_q, rows = key
-        batch = self.prepare(entries, token_capacity=tokens, seq_capacity=seqs,
+        batch = self.prepare(entries, sampled, token_capacity=tokens, seq_capacity=seqs,
                              page_capacity=self.max_pages)
         batch.attention_splits = self._graph_splits(seqs)
         held = self._shape_graphs.get(key)
@@ -319,23 +329,25 @@ class ModelRunner:
         return logits if rows else None
 
     @torch.inference_mode()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], sampled: torch.Tensor | None = None
+             ) -> torch.Tensor | None:
         """Run exactly the tokens given, as one batch, from the cache that earlier steps
         left; returns the logits at the wanted places in the order of the entries and of
         each entry's `want` (None if nothing is wanted). The tensor returned is a view of a
-        buffer that the next step overwrites."""
+        buffer that the next step overwrites. `sampled` (device int32) supplies the token
+        ids of entries marked `late`."""
         if (self.use_graphs and len(entries) <= self.max_seqs
                 and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries)):
-            return self._decode_with_graph(entries)
+            return self._decode_with_graph(entries, sampled)
         if self.use_graphs:
             key = (sum(len(e.tokens) for e in entries), len(entries),
                    max(len(e.tokens) for e in entries), sum(len(e.want) for e in entries))
             if key in self._shape_graphs or self._shape_seen.get(key, 0) >= 1:
-                return self._step_with_shape_graph(entries, key)
+                return self._step_with_shape_graph(entries, key, sampled)
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
             self._shape_seen[key] = 1
-        batch = self.prepare(entries)
+        batch = self.prepare(entries, sampled)
         logits = self.run(batch)
         check = getattr(self.ops, "check_errors", None)
         if check is not None:

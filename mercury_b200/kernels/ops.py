@@ -43,6 +43,10 @@ class CudaOps:
             raise KernelError(f"unknown gemm choice {gemm!r}")
         self.gemm = gemm
         self.skinny = True     # few-token products go to the weight-streaming kernels
+        # ... up to this many weight elements: a larger matrix (the LM head) is bound by HBM
+        # alone, and there the library's kernel streams faster (measured on B200 with 8
+        # tokens, weights cold: 151936 x 896 in 52 us against 76 us, 5.3 against 3.6 TB/s)
+        self.skinny_max_elements = 96 * 1024 * 1024
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head size 64, the
         # mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
@@ -118,6 +122,13 @@ class CudaOps:
         check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
                                 out.shape[0], out.shape[1], table.shape[0], self._stream()),
               "embed")
+        self.launches += 1
+
+    def patch_tokens(self, token_ids, token_from, sampled):
+        """token_ids[t] = sampled[token_from[t]] wherever token_from[t] >= 0: ids that the
+        step before has sampled on the device and the host has not read yet."""
+        check(self.lib.mb_patch_tokens(_ptr(token_ids), _ptr(token_from), _ptr(sampled),
+                                       token_ids.shape[0], self._stream()), "patch_tokens")
         self.launches += 1
 
     def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
@@ -215,7 +226,8 @@ class CudaOps:
         self._rows(weight), self._rows(out)
         all_bf16 = (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                     and (bias is None or bias.dtype == torch.bfloat16))
-        if all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k):
+        if (all_bf16 and self.skinny and self.lib.mb_gemm_skinny_supports(m, n, k)
+                and (n * k <= self.skinny_max_elements or self.gemm == "simt")):
             check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
                                           _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
                                           None, None, None, self._stream()),
@@ -266,7 +278,8 @@ class CudaOps:
         m, k = x.shape
         width = out.shape[1]
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-                and self.lib.mb_gemm_skinny_supports(m, width, k)):
+                and self.lib.mb_gemm_skinny_supports(m, width, k)
+                and 2 * width * k <= self.skinny_max_elements):
             check(self.lib.mb_gemm_skinny_swiglu(*self._skinny_input(x), _ptr(weight), _ptr(out),
                                                  m, width, k, self._stream()),
                   "linear_swiglu (skinny)")

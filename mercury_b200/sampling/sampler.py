@@ -38,32 +38,61 @@ def request_seed(params: SamplingParams, engine_seed: int, rid: str) -> int:
 
 
 class Sampler:
+    """`begin` launches the kernels of one batch and the copy of its tokens to the host;
+    `finish` waits for that copy. Two sets of buffers alternate, so that the tokens of one
+    batch stay on the device (where the next step may take its inputs from them) and on
+    their way to the host while the next batch is being sampled."""
+
     def __init__(self, ops, device, max_rows: int):
         self.ops = ops
         self.device = torch.device(device)
         pin = self.device.type == "cuda"
-        self.host = torch.zeros((3, max_rows), dtype=torch.float32, pin_memory=pin)
-        self.dev = torch.zeros((3, max_rows), dtype=torch.float32, device=self.device)
-        self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self.tokens_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self.host = torch.zeros((2, 3, max_rows), dtype=torch.float32, pin_memory=pin)
+        self.dev = torch.zeros((2, 3, max_rows), dtype=torch.float32, device=self.device)
+        self.tokens = torch.zeros((2, max_rows), dtype=torch.int32, device=self.device)
+        self.tokens_host = torch.zeros((2, max_rows), dtype=torch.int32, pin_memory=pin)
+        self._copied = [torch.cuda.Event(), torch.cuda.Event()] if pin else None
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, rows: list[tuple[SamplingParams, int, int]]) -> list[int]:
+    def begin(self, logits: torch.Tensor, rows: list[tuple[SamplingParams, int, int]]
+              ) -> tuple[int, int]:
         """`rows[i]` = (params, seed, output index) of the request that logits row i belongs
-        to. Returns one token id per row, on the host."""
+        to. Returns a handle for `finish` and `on_device`."""
         count = len(rows)
+        turn = self._turn
+        self._turn ^= 1
         if count == 0:
-            return []
-        out = self.tokens[:count]
+            return turn, 0
+        out = self.tokens[turn, :count]
         if all(p.greedy for p, _s, _i in rows):
             self.ops.argmax(logits, out)
         else:
-            host = self.host[:, :count]
+            host = self.host[turn, :, :count]
             for i, (p, seed, index) in enumerate(rows):
                 host[0, i] = p.temperature
                 host[1, i] = p.top_p
                 host[2, i] = 0.0 if p.greedy else draw_uniform(seed, index)
-            self.dev[:, :count].copy_(host, non_blocking=True)
-            self.ops.sample(logits, self.dev[0, :count], self.dev[1, :count], self.dev[2, :count],
-                            out)
-        self.tokens_host[:count].copy_(out, non_blocking=False)
-        return self.tokens_host[:count].tolist()
+            dev = self.dev[turn, :, :count]
+            dev.copy_(host, non_blocking=True)
+            self.ops.sample(logits, dev[0], dev[1], dev[2], out)
+        self.tokens_host[turn, :count].copy_(out, non_blocking=True)
+        if self._copied is not None:
+            self._copied[turn].record()
+        return turn, count
+
+    def on_device(self, handle: tuple[int, int]) -> torch.Tensor:
+        """The sampled tokens of a batch as they lie on the device (int32)."""
+        turn, count = handle
+        return self.tokens[turn, :count]
+
+    def finish(self, handle: tuple[int, int]) -> list[int]:
+        """One token id per row, on the host."""
+        turn, count = handle
+        if count == 0:
+            return []
+        if self._copied is not None:
+            self._copied[turn].synchronize()
+        return self.tokens_host[turn, :count].tolist()
+
+    def sample(self, logits: torch.Tensor, rows: list[tuple[SamplingParams, int, int]]) -> list[int]:
+        return self.finish(self.begin(logits, rows))

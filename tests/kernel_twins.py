@@ -22,6 +22,10 @@ class TorchOps:
     def embed(self, token_ids, table, out):
         out.copy_(table[token_ids.long()].to(out.dtype))
 
+    def patch_tokens(self, token_ids, token_from, sampled):
+        late = token_from >= 0
+        token_ids[late] = sampled[token_from[late].long()]
+
     def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
         if rows is None:
             if delta is not None:
