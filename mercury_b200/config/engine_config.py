@@ -7,6 +7,7 @@ Kept with their meaning: `model`, `device`, `dtype`, `block_size`, `num_blocks`,
 does not: `max_batched_tokens` (tokens of one step, decode tokens included) and
 `prefill_chunk` (most tokens of one prompt in one step). `cuda_graphs` replays decode-only
 steps from captured graphs. `prefix_caching` switches the hash lookup at admission.
+`lookahead` lets the engine launch a step before it has read the tokens of the step in front.
 """
 
 from __future__ import annotations

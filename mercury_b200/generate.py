@@ -52,6 +52,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--scan-limit", type=int, default=128)
     p.add_argument("--no-prefix-caching", action="store_true")
     p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--no-lookahead", action="store_true",
+                   help="read every step's tokens before the next step is launched")
     p.add_argument("--cryptographic-hashes", action="store_true")
     p.add_argument("--debug-invariants", action="store_true")
     p.add_argument("--seed", type=int, default=0)
@@ -86,7 +88,7 @@ def main(argv: list[str] | None = None) -> int:
         prefill_chunk=args.prefill_chunk, max_model_len=args.max_model_len, policy=args.policy,
         aging_tokens_per_s=args.aging_tokens_per_s, max_wait_s=args.max_wait_s,
         scan_limit=args.scan_limit, prefix_caching=not args.no_prefix_caching,
-        cuda_graphs=not args.no_cuda_graphs, cryptographic_hashes=args.cryptographic_hashes,
+        cuda_graphs=not args.no_cuda_graphs, lookahead=not args.no_lookahead, cryptographic_hashes=args.cryptographic_hashes,
         debug_invariants=args.debug_invariants, seed=args.seed)
     if args.num_blocks < 0:
         from .engine.runner import kv_bytes_per_token_of
