@@ -639,6 +639,354 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
             __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
 }
 
+// The decode kernel once more, for up to eight key ranges per (sequence, KV head): the
+// blocks of one (sequence, KV head) form a thread-block cluster. Two things take the keys
+// off the critical path of a captured decode step. (1) Everything a block needs of the
+// cache except the tile with the newest key is copied into shared memory BEFORE the block
+// waits for the kernel in front (which writes only the newest key and the queries), so that
+// after the wait only the queries, and in one block of the cluster one tile, are fetched.
+// (2) The ranges are merged through distributed shared memory: every block leaves its
+// (maximum, sum, output) in its own shared memory and, after a cluster barrier, each block
+// finishes a share of the rows from all the others' memories; nothing goes through global
+// memory, and there is no ticket to take.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+                                const __nv_bfloat16* __restrict__ k_pages,
+                                const __nv_bfloat16* __restrict__ v_pages,
+                                const int* __restrict__ table, int max_pages,
+                                const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
+                                __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size,
+                                float scale, int window) {
+    constexpr int CH = D / 8;
+    constexpr int STAGES = D == 64 ? 5 : 3;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][D]
+    __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
+    __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
+    float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][D], after the loop
+    float* o_part = o_red + 4 * 16 * D;                                   // [16][D], this block's result
+    __shared__ float ml_red[4][16][2];
+    __shared__ float ml_part[16][2];                                      // row maximum (log2 units), sum
+
+    uint32_t split, num_splits;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(num_splits));
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int group = n_q / n_kv;
+    // lengths and block tables were copied to the device before the step began
+    const int q_begin = q_start[seq];
+    const int q_len = q_start[seq + 1] - q_begin;
+    if (q_len <= 0) return;                  // the same for every block of the cluster
+    const int rows = q_len * group;          // <= 16
+    const int kv_len = kv_len_of[seq];
+    const int first_pos = kv_len - q_len;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int p_min = first_pos, p_max = kv_len - 1;
+    int t_lo = 0;
+    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / MMA_BN;
+    int t_hi = p_max / MMA_BN + 1;
+    // tiles that hold a key of this step: written by the kernel in front
+    const int t_new = first_pos / MMA_BN;
+    {
+        const int per = (t_hi - t_lo + (int)num_splits - 1) / (int)num_splits;
+        t_lo = t_lo + (int)split * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+    const int n_tiles = t_hi > t_lo ? t_hi - t_lo : 0;
+
+    // each thread copies half a key row of K and of V: one table lookup per tile
+    const int lj = tid >> 1, lc0 = (tid & 1) * (CH / 2);
+    auto load_tile = [&](int stage, int kt) {
+        const int key = kt * MMA_BN + lj;
+        int page = -1;
+        if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+        const bool valid = page >= 0;
+        const int64_t at =
+            valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
+        __nv_bfloat16* kd = k_s + (stage * MMA_BN + lj) * D;
+        __nv_bfloat16* vd = v_s + (stage * MMA_BN + lj) * D;
+#pragma unroll
+        for (int c = 0; c < CH / 2; ++c) {
+            const int sw = ((lc0 + c) ^ (lj & 7)) * 8;
+            cp_async_16(kd + sw, k_pages + at + (lc0 + c) * 8, valid);
+            cp_async_16(vd + sw, v_pages + at + (lc0 + c) * 8, valid);
+        }
+    };
+
+    // ---- before the wait: the first STAGES tiles, one copy group each (an empty group for a
+    // tile that is not there or holds keys of this step)
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+        const int kt = t_lo + st;
+        if (kt < t_hi && kt < t_new) load_tile(st, kt);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    grid_dependency_sync();
+
+    // ---- after it: the queries, and the tiles of the first STAGES that had to wait
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int tok = r / group, hg = r - tok * group;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r < rows)
+            val = *reinterpret_cast<const uint4*>(qkv + (int64_t)(q_begin + tok) * q_row_stride +
+                                                  (kvh * group + hg) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
+    }
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+        const int kt = t_lo + st;
+        if (kt < t_hi && kt >= t_new) load_tile(st, kt);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+
+    int pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        row_ok[h] = r < rows;
+        pos[h] = first_pos + r / group;
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float scale2 = scale * 1.4426950408889634f;
+
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(qf[ks], q_s + r * D + ((c ^ (r & 7)) * 8));
+    }
+
+    // Copy groups in the order they were committed: tiles 0 .. STAGES-1, the late group, then
+    // one refill per iteration from the second on. A tile of this step's keys may sit in the
+    // late group: it waits for everything; any other tile is older than the newest
+    // STAGES - 2 groups when its turn comes.
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = t_lo + it;
+        const int stage = it % STAGES;
+        if (kt >= t_new) {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+        }
+        __syncthreads();   // tile `it` has landed for everyone; the stage of tile it-1 is free
+        if (it >= 1) {
+            const int next = it - 1 + STAGES;
+            if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
+            asm volatile("cp.async.commit_group;\n" ::);
+        }
+        const __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
+        const __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
+
+        // this warp's 16 keys of the tile
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t b[4];
+            const int j = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+            const int c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, kt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        float m_new[2] = {m[0], m[1]};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int key = kt * MMA_BN + warp * 16 + nt * 8 + 2 * t4 + (e & 1);
+                bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                if (window > 0) seen = seen && key > pos[h] - window;
+                s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
+                m_new[h] = fmaxf(m_new[h], s[nt][e]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
+            m[h] = m_new[h];
+            l[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const float p = m[h] > -INFINITY ? fast_exp2(s[nt][e] - m[h]) : 0.f;
+                s[nt][e] = p;
+                l[h] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+        uint32_t a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2) {
+            uint32_t b[4];
+            const int j = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int c = d2 * 2 + (lane >> 4);
+            ldmatrix_x4_trans(b, vt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(o[2 * d2], a, b[0], b[1]);
+            mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();   // every warp is done with the key tiles: their memory becomes o_red
+
+    // ---- merge the four warps (each saw a quarter of the keys)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        if (t4 == 0) {
+            ml_red[warp][g + h * 8][0] = m[h];
+            ml_red[warp][g + h * 8][1] = l[h];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
+        const float mine = m[h] > -INFINITY ? fast_exp2(m[h] - big) : 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            float2 v = make_float2(o[i][2 * h] * mine, o[i][2 * h + 1] * mine);
+            *reinterpret_cast<float2*>(o_red + (warp * 16 + r) * D + i * 8 + 2 * t4) = v;
+        }
+    }
+    __syncthreads();
+    // 128 threads: thread -> (row = tid / 8, 8 threads across D)
+    {
+        const int r = tid >> 3;
+        const int tok = r / group, hg = r - tok * group;
+        float big = -INFINITY, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (ml_red[w][r][0] > -INFINITY) sum += ml_red[w][r][1] * fast_exp2(ml_red[w][r][0] - big);
+        for (int c = (tid & 7); c < D; c += 8) {
+            const float v = o_red[(0 * 16 + r) * D + c] + o_red[(1 * 16 + r) * D + c] +
+                            o_red[(2 * 16 + r) * D + c] + o_red[(3 * 16 + r) * D + c];
+            if (num_splits == 1) {
+                if (r < rows)
+                    out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
+                        __float2bfloat16_rn(sum > 0.f ? v / sum : 0.f);
+            } else {
+                o_part[r * D + c] = v;
+            }
+        }
+        if ((tid & 7) == 0) {
+            ml_part[r][0] = big;
+            ml_part[r][1] = sum;
+        }
+    }
+    if (num_splits == 1) return;
+
+    // ---- the ranges meet: every block finishes its share of the rows from all the blocks
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    {
+        const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
+        const int r_first = (int)split * per_block;
+        const uint32_t local_o = (uint32_t)__cvta_generic_to_shared(o_part);
+        const uint32_t local_ml = (uint32_t)__cvta_generic_to_shared(&ml_part[0][0]);
+        for (int e = tid; e < per_block * D; e += 128) {
+            const int r = r_first + e / D, c = e % D;
+            if (r >= rows) continue;
+            float mz[8], vz[8], lz[8];
+            float big = -INFINITY;
+#pragma unroll
+            for (uint32_t z = 0; z < 8; ++z) {
+                mz[z] = -INFINITY;
+                vz[z] = lz[z] = 0.f;
+                if (z < num_splits) {
+                    uint32_t remote_o, remote_ml;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_o) : "r"(local_o), "r"(z));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_ml) : "r"(local_ml), "r"(z));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mz[z]) : "r"(remote_ml + 8 * r) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lz[z]) : "r"(remote_ml + 8 * r + 4) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(vz[z]) : "r"(remote_o + 4 * (r * D + c)) : "memory");
+                }
+            }
+#pragma unroll
+            for (int z = 0; z < 8; ++z) big = fmaxf(big, mz[z]);
+            float acc = 0.f, denom = 0.f;
+#pragma unroll
+            for (int z = 0; z < 8; ++z) {
+                const float w = mz[z] > -INFINITY ? fast_exp2(mz[z] - big) : 0.f;
+                acc += w * vz[z];
+                denom += w * lz[z];
+            }
+            const int tok = r / group, hg = r - tok * group;
+            out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
+                __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+        }
+    }
+    // nobody leaves (and gives its shared memory up) while another block may still read it
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int D>
+int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
+                                    const void* v_pages, const int* table, int max_pages,
+                                    const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
+                                    int page_size, float scale, int window, int num_seqs, int cluster,
+                                    cudaStream_t s) {
+    constexpr int STAGES = D == 64 ? 5 : 3;
+    const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = true;
+    }
+    typedef __nv_bfloat16 bf;
+    cudaLaunchConfig_t config = launch_config(dim3(num_seqs, n_kv, cluster), 128, smem, s);
+    cudaLaunchAttribute attrs[2];
+    int num_attrs = 0;
+    if (config.numAttrs) attrs[num_attrs++] = config.attrs[0];
+    if (cluster > 1) {
+        attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[num_attrs].val.clusterDim.x = 1;
+        attrs[num_attrs].val.clusterDim.y = 1;
+        attrs[num_attrs].val.clusterDim.z = (unsigned)cluster;
+        ++num_attrs;
+    }
+    config.attrs = attrs;
+    config.numAttrs = num_attrs;
+    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D>, (const bf*)qkv, q_row_stride,
+                       (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start, kv_len, (bf*)out,
+                       n_q, n_kv, page_size, scale, window);
+    return launch_status();
+}
+
 template <int D>
 int launch_attention_decode(const void* qkv, int q_row_stride, const void* k_pages,
                             const void* v_pages, const int* table, int max_pages, const int* q_start,
@@ -697,6 +1045,31 @@ using namespace mb;
 // 1 if this kernel takes the head size (bfloat16 only), else 0: the caller then uses the
 // CUDA-core kernel.
 MB_EXPORT int mb_attention_mma_supports(int d) { return d == 64 || d == 128; }
+
+// Decode-like batches (at most 16 rows per sequence and KV head) with the key ranges of a
+// (sequence, KV head) as one cluster of `cluster` blocks (1, 2, 4 or 8): no scratch, no
+// counters, one launch. bfloat16, head sizes 64 and 128.
+MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
+                                                const void* v_pages, const int* table, int max_pages,
+                                                const int* q_start, const int* kv_len, void* out,
+                                                int tokens, int num_seqs, int max_q_len, int n_q,
+                                                int n_kv, int d, int page_size, float scale, int window,
+                                                int cluster, void* stream) {
+    if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
+    if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
+    if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
+    if (q_row_stride % 8) return MB_ERR_ALIGNMENT;
+    if (max_q_len * (n_q / n_kv) > 16 || n_kv > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return MB_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64)
+        return launch_attention_decode_cluster<64>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                                   q_start, kv_len, out, n_q, n_kv, page_size, scale,
+                                                   window, num_seqs, cluster, s);
+    return launch_attention_decode_cluster<128>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                                q_start, kv_len, out, n_q, n_kv, page_size, scale, window,
+                                                num_seqs, cluster, s);
+}
 
 // Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.
 MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,

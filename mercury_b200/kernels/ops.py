@@ -51,6 +51,10 @@ class CudaOps:
         # mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
+        # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
+        # 8 blocks, merged through distributed shared memory, while fewer than 16 ranges are
+        # wanted; beyond that the ranges go through global memory as before
+        self.decode_clusters = True
         self.prompt_splits: int | None = None   # override of the key split of prompt portions
         # Normalising inside the consuming product saves a launch but makes every block
         # redo the row statistics; measured on B200 the separate norm kernel is faster for
@@ -418,6 +422,18 @@ class CudaOps:
             small = batch.max_q_len * group <= 16
             if small:
                 splits = self._splits(batch, num_kv_heads, group, 16, 64)
+                if self.decode_clusters and splits < 16 and kernel is None:
+                    cluster = 1
+                    while cluster * 2 <= min(splits, 8):
+                        cluster *= 2
+                    check(self.lib.mb_paged_attention_decode_cluster(
+                        _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                        cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
+                        tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim,
+                        cache.page_size, float(scale), int(window), cluster, self._stream()),
+                        "paged_attention (decode clusters)")
+                    self.launches += 1
+                    return
             else:
                 splits = self._prompt_splits(batch, num_kv_heads, group)
         else:

@@ -404,13 +404,17 @@ ATTENTION_CASES = [
     (14, 2, 64, 64, (200, 3), (500, 131), 0),
     (7, 7, 64, 128, (150,), (400,), 0),
     (4, 2, 64, 16, (300, 1, 70), (600, 200, 70), 100),
+    (14, 2, 64, 16, (1, 1, 1, 1), (2048, 300, 64, 1), 0),
+    (16, 8, 128, 16, (2, 1), (500, 129), 0),
+    (4, 2, 64, 16, (1, 2), (700, 300), 128),
+    (7, 1, 64, 64, (2,), (333,), 0),
 ]
 
 
 def attention_close(got, want, dtype, kernel):
     """The tensor-core kernels round the probabilities to bfloat16 before P.V and the result
     once more: two roundings of 2^-8, against one for the CUDA-core kernel."""
-    if kernel in ("mma", "tcgen05"):
+    if kernel in ("mma", "tcgen05", "clusters"):
         err = float((got.double() - want.double()).abs().max()) / float(want.abs().max())
         assert err <= 2 * 2.0 ** -8, f"attention (mma): relative error {err:.3e}"
     else:
@@ -418,8 +422,9 @@ def attention_close(got, want, dtype, kernel):
 
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
-                                          ("mma", torch.bfloat16), ("tcgen05", torch.bfloat16)],
-                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05"])
+                                          ("mma", torch.bfloat16), ("tcgen05", torch.bfloat16),
+                                          ("clusters", torch.bfloat16)],
+                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05", "bf16-clusters"])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("case", range(len(ATTENTION_CASES)), ids=lambda i: f"case{i}")
 def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
@@ -432,8 +437,16 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     if kernel == "tcgen05" and not ops.lib.mb_attention_tcgen05_supports(
             d, page, n_q, n_kv, (n_q + 2 * n_kv) * d):
         pytest.skip("left to the other attention kernels")
-    # for the tensor-memory kernel the split is the number of CTAs that share a row tile
-    clusters = (None,) if kernel != "tcgen05" else ((1,) if splits == 1 else (2, 4))
+    if kernel == "clusters" and not (ops.lib.mb_attention_mma_supports(d)
+                                     and max(q_lens) * (n_q // n_kv) <= 16):
+        pytest.skip("the cluster kernel is for decode-like batches of head size 64 or 128")
+    # for the tensor-memory kernel the split is the number of CTAs that share a row tile, for
+    # the decode clusters the number of blocks of a (sequence, KV head)
+    clusters = (None,)
+    if kernel == "tcgen05":
+        clusters = (1,) if splits == 1 else (2, 4)
+    elif kernel == "clusters":
+        clusters = (1,) if splits == 1 else (2, 4, 8)
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 5
     drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
     batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=3, seed=1,
@@ -459,15 +472,19 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     twin.paged_attention(qkv_twin, n_q, n_kv, d, batch, cache_twin, d ** -0.5, window, want)
     for cluster in clusters:
         ops.prompt_cluster = cluster
+        if kernel == "clusters":
+            ops.decode_splits = cluster
         got = torch.zeros_like(want)
-        ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got, kernel=kernel)
+        ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got,
+                            kernel=None if kernel == "clusters" else kernel)
         ops.check_errors()
         assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
         attention_close(got[live], want[live], dtype, kernel)
 
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
-                                          ("mma", torch.bfloat16)], ids=["f32", "bf16", "bf16-mma"])
+                                          ("mma", torch.bfloat16), (None, torch.bfloat16)],
+                         ids=["f32", "bf16", "bf16-mma", "bf16-clusters"])
 @pytest.mark.parametrize("splits", [1, 5])
 def test_attention_finds_one_far_key(twin, dtype, kernel, splits):
     """Among 700 keys one far key matches the query strongly; the output must be that
