@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
                                    int T, int N, int K, int half_n, int rowt, int ksplit,
                                    const __nv_bfloat16* __restrict__ next_norm_w,
                                    __nv_bfloat16* __restrict__ next_x,
-                                   float* __restrict__ next_ss) {
+                                   float* __restrict__ next_ss, int h_stable) {
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
     __shared__ float rstd_s[TOK];
@@ -216,6 +216,25 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
         const int chunks = K / 32;
         const int per = (chunks + ksplit - 1) / ksplit;
         skinny_prefetch_weights(w, n0, K, ks * per, ks * per + per < chunks ? ks * per + per : chunks);
+    }
+    // The stream element this thread will add to (EPI 3, one element per thread when the
+    // block has at least 16 TOK threads per tile): read before the wait when the caller says
+    // that the kernel in front does not write the stream.
+    // Bias and the next norm's weight of that element are weights: read before the wait too.
+    float h_early = 0.f, bias_early = 0.f, next_w_early = 0.f;
+    const bool one_each = EPI != 2 && (int)blockDim.x >= rowt * 16 * TOK;
+    const bool early = EPI == 3 && h_stable && one_each;
+    if (one_each) {
+        const int idx = threadIdx.x;
+        if (idx < rowt * 16 * TOK) {
+            const int r = idx % 16, tok = (idx / 16) % TOK, tile = idx / (16 * TOK);
+            const int n = (blockIdx.x * rowt + tile) * 16 + r;
+            if (tok < T && n < N) {
+                if (early) h_early = reinterpret_cast<const float*>(out)[(int64_t)tok * N + n];
+                if (bias) bias_early = __bfloat162float(bias[n]);
+                if (EPI == 3 && next_norm_w) next_w_early = __bfloat162float(next_norm_w[n]);
+            }
+        }
     }
     grid_dependency_sync();
     skinny_row_scale(in, T, scale_s);     // read after the barrier that follows the product
@@ -264,20 +283,20 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
             float v = 0.f;
             for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
             v *= scale_s[tok < T ? tok : 0];
-            if (bias && live) v += __bfloat162float(bias[n]);
+            if (bias && live) v += one_each ? bias_early : __bfloat162float(bias[n]);
             float sq = 0.f;
             if (live) {
                 if (EPI == 0) {
                     reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
                 } else if (EPI == 3) {
                     float* at = reinterpret_cast<float*>(out) + (int64_t)tok * N + n;
-                    const float updated = *at + v;
+                    const float updated = (early ? h_early : *at) + v;
                     *at = updated;
                     if (next_norm_w) {
                         // for the product after the next norm: the stream times that norm's
                         // weight, and this tile's share of the row's sum of squares
-                        next_x[(int64_t)tok * N + n] =
-                            __float2bfloat16_rn(updated * __bfloat162float(next_norm_w[n]));
+                        next_x[(int64_t)tok * N + n] = __float2bfloat16_rn(
+                            updated * (one_each ? next_w_early : __bfloat162float(next_norm_w[n])));
                         sq = updated * updated;
                     }
                 } else {
@@ -297,8 +316,8 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
 // One block per head of the packed q/k/v projection: D/16 row tiles, each shared by
 // `ksplit` warps. After the product: bias, rotation of q and k heads (pairs i, i + D/2),
 // q written to the qkv buffer, k and v written to the token's slot of the cache page.
-// Where each token goes (position, page) is looked up before the product starts, so that
-// those loads overlap the weight stream.
+// Where each token goes (position, page), the bias and the rotation angles are fetched
+// before the kernel waits for the one in front.
 template <int NT, int D, bool NORM>
 __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(SkinnyInput in,
                                        const __nv_bfloat16* __restrict__ w,
@@ -320,7 +339,6 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         skinny_prefetch_weights(w, blockIdx.x * D + rt_ * 16, K, ks_ * per_,
                                 ks_ * per_ + per_ < chunks_ ? ks_ * per_ + per_ : chunks_);
     }
-    grid_dependency_sync();
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];          // [ROWT * ksplit][16][TOK]
     float* val = red + ROWT * ksplit * 16 * TOK;  // [TOK][D]
@@ -328,7 +346,12 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
     __shared__ int tok_page[TOK];           // -2: padding token, -1: no page
     __shared__ float rstd_s[TOK];
     __shared__ float scale_s[TOK];
+    __shared__ float bias_s[D];
+    __shared__ float cos_s[TOK][D / 2], sin_s[TOK][D / 2];
     const int head = blockIdx.x;  // 0..n_q-1 q heads, then k heads, then v heads
+    // Positions, block tables, bias and rotation angles do not depend on the kernel in front
+    // (they were on the device before the step began): all of them are fetched before the
+    // wait, so that after it only the activations are missing.
     if (threadIdx.x < TOK) {
         const int tok = threadIdx.x;
         int pos = 0, page = -2;
@@ -342,6 +365,18 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         tok_pos[tok] = pos;
         tok_page[tok] = page;
     }
+    for (int r = threadIdx.x; r < D; r += blockDim.x)
+        bias_s[r] = bias ? __bfloat162float(bias[head * D + r]) : 0.f;
+    if (cos_t && head < n_q + n_kv) {
+        for (int idx = threadIdx.x; idx < TOK * (D / 2); idx += blockDim.x) {
+            const int i = idx % (D / 2), tok = idx / (D / 2);
+            int pos = 0;
+            if (tok < T && seq_of_token[tok] >= 0) pos = positions[tok];
+            cos_s[tok][i] = cos_t[(int64_t)pos * (D / 2) + i];
+            sin_s[tok][i] = sin_t[(int64_t)pos * (D / 2) + i];
+        }
+    }
+    grid_dependency_sync();
     skinny_row_scale(in, T, scale_s);
     if (NORM) {
         skinny_row_rstd(in, T, K, rstd_s);
@@ -366,7 +401,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         float v = 0.f;
         for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + rr * TOK + tok];
         v *= scale_s[tok < T ? tok : 0];
-        if (bias) v += __bfloat162float(bias[head * D + r]);
+        v += bias_s[r];
         // the separate kernels round the projection to bfloat16 before rotating it
         val[tok * D + r] = __bfloat162float(__float2bfloat16_rn(v));
     }
@@ -381,7 +416,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         const int pos = tok_pos[tok];
         float a = val[tok * D + i], b = val[tok * D + i + D / 2];
         if (!is_v && cos_t) {
-            const float c = cos_t[(int64_t)pos * (D / 2) + i], s = sin_t[(int64_t)pos * (D / 2) + i];
+            const float c = cos_s[tok][i], s = sin_s[tok][i];
             const float ra = a * c - b * s, rb = b * c + a * s;
             a = ra;
             b = rb;
@@ -414,7 +449,9 @@ static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
 // when a larger amount is needed).
 template <typename KernelT>
 static int raise_smem(KernelT kernel, size_t bytes) {
-    static size_t raised = 48 * 1024;  // one per kernel instantiation
+    // (one per kernel instantiation; the kernels also hold up to 12 KB of static shared
+    // memory, and the 48 KB that need no asking cover both kinds together)
+    static size_t raised = 32 * 1024;
     if (bytes <= raised) return MB_OK;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
         cudaSuccess)
@@ -460,13 +497,13 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, true>), blocks, threads, smem, s, in,    \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
-                          (const bf*)next_w, (bf*)next_x, next_ss);                              \
+                          (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
         } else {                                                                                 \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
             if (rc == MB_OK)                                                                     \
                 MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, false>), blocks, threads, smem, s, in,   \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
-                          (const bf*)next_w, (bf*)next_x, next_ss);                              \
+                          (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
         }                                                                                        \
     } while (0)
 
@@ -478,10 +515,13 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
 // 16-column tile; the result rows are multiplied by rsqrt(sum / ss_k + ss_eps).
 // With mode 3 and `next_w` given the product leaves exactly that for the product after the
 // next norm: next_x [T, N] = bfloat16(updated stream * next_w) and next_ss [T, N / 16].
+// `h_stable` (mode 3) says that the kernel launched just before this one does not write
+// `out`: the stream is then read before the wait for that kernel.
 MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, const int* rows,
                              float eps, const float* ss_part, int ss_tiles, float ss_eps, int ss_k,
                              const void* w, const void* bias, void* out, int mode, int T, int N,
-                             int K, const void* next_w, void* next_x, float* next_ss, void* stream) {
+                             int K, const void* next_w, void* next_x, float* next_ss, int h_stable,
+                             void* stream) {
     if (next_w && (mode != 3 || !next_x || !next_ss)) return MB_ERR_UNSUPPORTED_SIZE;
     if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
     if (mode != 0 && mode != 1 && mode != 3) return MB_ERR_BAD_DTYPE;
@@ -523,6 +563,7 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     const int threads = rowt * ksplit * 32;
     const int N = 2 * width, half_n = width;
     const void* bias = nullptr;
+    const int h_stable = 0;
     const void* next_w = nullptr;
     void* next_x = nullptr;
     float* next_ss = nullptr;

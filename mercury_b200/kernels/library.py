@@ -47,7 +47,7 @@ _SIGNATURES = {
                                c_void_p],
     "mb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float,
                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                       c_void_p, c_void_p, c_void_p],
+                       c_void_p, c_void_p, c_int, c_void_p],
     "mb_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                               c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_gemm_skinny_qkv_rope": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float,

@@ -85,6 +85,11 @@ class CudaOps:
         self._pinned_stream: int | None = None
         self.launches = 0
         self.library_calls = 0
+        # Which launch (by count) last wrote a float32 residual stream. A residual product
+        # reads the stream before it waits for the kernel in front (see mb_gemm_skinny) unless
+        # that kernel is this writer. Only this library's kernels let their successor start
+        # early, and each of them that writes a stream is noted here.
+        self._last_stream_write = -1
         # split-K partial sums stay float32
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -127,6 +132,10 @@ class CudaOps:
                                 out.shape[0], out.shape[1], table.shape[0], self._stream()),
               "embed")
         self.launches += 1
+        self._note_stream_write()
+
+    def _note_stream_write(self) -> None:
+        self._last_stream_write = self.launches + self.library_calls
 
     def patch_tokens(self, token_ids, token_from, sampled):
         """token_ids[t] = sampled[token_from[t]] wherever token_from[t] >= 0: ids that the
@@ -143,6 +152,8 @@ class CudaOps:
                                       _ptr(out), _ptr(rows), count, h.shape[1], float(eps),
                                       _flag(out.dtype), self._stream()), "add_rmsnorm")
         self.launches += 1
+        if rows is None:
+            self._note_stream_write()
 
     def _error_word(self) -> torch.Tensor:
         if self._tc_error is None:
@@ -205,11 +216,13 @@ class CudaOps:
                     and then_norm.weight.dtype == torch.bfloat16)
             normed = ctx.buffer("normed", m, n) if fuse else None
             sums = ctx.buffer("norm_sums", m, n // 16, dtype="float32") if fuse else None
+            stable = self._last_stream_write != self.launches + self.library_calls
             check(self.lib.mb_gemm_skinny(
                 *self._skinny_input(x), _ptr(weight), _ptr(bias), _ptr(h), 3, m, n, k,
-                _ptr(then_norm.weight) if fuse else None, _ptr(normed), _ptr(sums),
+                _ptr(then_norm.weight) if fuse else None, _ptr(normed), _ptr(sums), int(stable),
                 self._stream()), "linear_residual (skinny)")
             self.launches += 1
+            self._note_stream_write()
             if fuse:
                 from ..parts.norm import PendingScaled
 
@@ -234,7 +247,7 @@ class CudaOps:
                 and (n * k <= self.skinny_max_elements or self.gemm == "simt")):
             check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
                                           _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
-                                          None, None, None, self._stream()),
+                                          None, None, None, 0, self._stream()),
                   "linear (skinny)")
             self.launches += 1
             return
