@@ -52,8 +52,9 @@ class CudaOps:
         self.attention = "auto"
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
-        # 8 blocks, merged through distributed shared memory, while fewer than 16 ranges are
-        # wanted; beyond that the ranges go through global memory as before
+        # 8 blocks, merged through distributed shared memory, while fewer than 32 ranges are
+        # wanted; beyond that (very long contexts in a small batch) the ranges go through
+        # global memory as before
         self.decode_clusters = True
         self.prompt_splits: int | None = None   # override of the key split of prompt portions
         # Normalising inside the consuming product saves a launch but makes every block
@@ -435,7 +436,7 @@ class CudaOps:
             small = batch.max_q_len * group <= 16
             if small:
                 splits = self._splits(batch, num_kv_heads, group, 16, 64)
-                if self.decode_clusters and splits < 16 and kernel is None:
+                if self.decode_clusters and splits < 32 and kernel is None:
                     cluster = 1
                     while cluster * 2 <= min(splits, 8):
                         cluster *= 2
