@@ -129,6 +129,25 @@ inline cudaLaunchConfig_t launch_config(dim3 grid, dim3 block, size_t smem, cuda
         cudaLaunchKernelEx(&config_, kernel, __VA_ARGS__);                             \
     } while (0)
 
+// The same with the blocks grouped into thread-block clusters of (cx, cy, cz).
+#define MB_LAUNCH_CLUSTER(kernel, grid, block, smem, stream, cx, cy, cz, ...)                     \
+    do {                                                                                          \
+        cudaLaunchConfig_t config_ = mb::launch_config(grid, block, smem, stream);                \
+        cudaLaunchAttribute attrs_[2];                                                            \
+        int count_ = 0;                                                                           \
+        if (config_.numAttrs) attrs_[count_++] = config_.attrs[0];                                \
+        if ((cx) * (cy) * (cz) > 1) {                                                             \
+            attrs_[count_].id = cudaLaunchAttributeClusterDimension;                              \
+            attrs_[count_].val.clusterDim.x = (unsigned)(cx);                                     \
+            attrs_[count_].val.clusterDim.y = (unsigned)(cy);                                     \
+            attrs_[count_].val.clusterDim.z = (unsigned)(cz);                                     \
+            ++count_;                                                                             \
+        }                                                                                         \
+        config_.attrs = attrs_;                                                                   \
+        config_.numAttrs = count_;                                                                \
+        cudaLaunchKernelEx(&config_, kernel, __VA_ARGS__);                                        \
+    } while (0)
+
 inline int launch_status() {
     return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_LAUNCH;
 }

@@ -171,6 +171,39 @@ __device__ __forceinline__ void skinny_prefetch_weights(const __nv_bfloat16* __r
     }
 }
 
+// K may also be shared between the blocks of a thread-block cluster (`slices` along y): block
+// `slice` walks its part of K, leaves its sums in the shared memory of the cluster's first
+// block, and after one cluster barrier the first block alone runs the epilogue. A product
+// with few row tiles and a long K (down-proj, q/k/v) so gets more SMs to pull its weights.
+__device__ __forceinline__ void cluster_rank_size(uint32_t& rank, uint32_t& size) {
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(size));
+}
+
+__device__ __forceinline__ void cluster_store_to_first(float* local_slot, float v) {
+    uint32_t remote;
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(local_slot);
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// This block's part [s0, s1) of the K chunks and, inside it, this warp's share.
+__device__ __forceinline__ void skinny_share(int chunks, uint32_t slice, uint32_t slices, int ks, int ksplit,
+                                             int& c_begin, int& c_end) {
+    const int per_slice = (chunks + (int)slices - 1) / (int)slices;
+    const int s0 = (int)slice * per_slice;
+    const int s1 = s0 + per_slice < chunks ? s0 + per_slice : chunks;
+    const int per = (s1 - s0 + ksplit - 1) / ksplit;
+    c_begin = s0 + ks * per;
+    c_end = c_begin + per < s1 ? c_begin + per : s1;
+    if (c_begin > c_end) c_begin = c_end;
+}
+
 // Every warp leaves its 16 x (8 NT) partial tile in shared memory: red[warp][row][token].
 template <int NT>
 __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT][4]) {
@@ -212,11 +245,11 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
         n0 = (blockIdx.x * rowt + rt) * 16;
     }
     const int limit = EPI == 2 ? ((rt & 1) + 1) * half_n : N;
-    if (n0 < limit) {
-        const int chunks = K / 32;
-        const int per = (chunks + ksplit - 1) / ksplit;
-        skinny_prefetch_weights(w, n0, K, ks * per, ks * per + per < chunks ? ks * per + per : chunks);
-    }
+    uint32_t slice, slices;
+    cluster_rank_size(slice, slices);
+    int c_begin, c_end;
+    skinny_share(K / 32, slice, slices, ks, ksplit, c_begin, c_end);
+    if (n0 < limit) skinny_prefetch_weights(w, n0, K, c_begin, c_end);
     // The stream element this thread will add to (EPI 3, one element per thread when the
     // block has at least 16 TOK threads per tile): read before the wait when the caller says
     // that the kernel in front does not write the stream.
@@ -245,15 +278,24 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    if (n0 < limit) {
-        const int chunks = K / 32;
-        const int per = (chunks + ksplit - 1) / ksplit;
-        const int c_begin = ks * per;
-        const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
-        skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
-    }
+    if (n0 < limit) skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
     store_partial<NT>(red, acc);
     __syncthreads();
+
+    // gathered[j][idx]: the sums of the cluster's block j + 1, in the first block's memory
+    float* gathered = red + rowt * ksplit * 16 * TOK;
+    if (EPI != 2 && slices > 1) {
+        if (slice != 0) {
+            for (int idx = threadIdx.x; idx < rowt * 16 * TOK; idx += blockDim.x) {
+                const int r = idx % 16, tok = (idx / 16) % TOK, tile = idx / (16 * TOK);
+                float v = 0.f;
+                for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
+                cluster_store_to_first(gathered + (slice - 1) * rowt * 16 * TOK + idx, v);
+            }
+        }
+        cluster_barrier();
+        if (slice != 0) return;
+    }
 
     if (EPI == 2) {
         // element (pair tile p, row r, token): silu(gate) * up
@@ -282,6 +324,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
             const bool live = tok < T && n < N;
             float v = 0.f;
             for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
+            for (uint32_t j = 1; j < slices; ++j) v += gathered[(j - 1) * rowt * 16 * TOK + idx];
             v *= scale_s[tok < T ? tok : 0];
             if (bias && live) v += one_each ? bias_early : __bfloat162float(bias[n]);
             float sq = 0.f;
@@ -332,12 +375,14 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
                                        __nv_bfloat16* __restrict__ v_pages, int T, int K, int n_q,
                                        int n_kv, int page_size, int store, int ksplit) {
     constexpr int ROWT = D / 16;
+    uint32_t slice, slices;
+    cluster_rank_size(slice, slices);
+    int c_begin, c_end;
     {
         const int w_ = threadIdx.x >> 5;
         const int rt_ = w_ / ksplit, ks_ = w_ - rt_ * ksplit;
-        const int chunks_ = K / 32, per_ = (chunks_ + ksplit - 1) / ksplit;
-        skinny_prefetch_weights(w, blockIdx.x * D + rt_ * 16, K, ks_ * per_,
-                                ks_ * per_ + per_ < chunks_ ? ks_ * per_ + per_ : chunks_);
+        skinny_share(K / 32, slice, slices, ks_, ksplit, c_begin, c_end);
+        skinny_prefetch_weights(w, blockIdx.x * D + rt_ * 16, K, c_begin, c_end);
     }
     constexpr int TOK = 8 * NT;
     extern __shared__ float red[];          // [ROWT * ksplit][16][TOK]
@@ -388,18 +433,30 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    const int chunks = K / 32;
-    const int per = (chunks + ksplit - 1) / ksplit;
-    const int c_begin = ks * per;
-    const int c_end = c_begin + per < chunks ? c_begin + per : chunks;
     skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
     store_partial<NT>(red, acc);
     __syncthreads();
+    // gathered[j][idx]: the sums of the cluster's block j + 1, in the first block's memory
+    float* gathered = val + TOK * D;
+    if (slices > 1) {
+        if (slice != 0) {
+            for (int idx = threadIdx.x; idx < D * TOK; idx += blockDim.x) {
+                const int r = idx % D, tok = idx / D;
+                const int tile = r / 16, rr = r % 16;
+                float v = 0.f;
+                for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + rr * TOK + tok];
+                cluster_store_to_first(gathered + (slice - 1) * D * TOK + idx, v);
+            }
+        }
+        cluster_barrier();
+        if (slice != 0) return;
+    }
     for (int idx = threadIdx.x; idx < D * TOK; idx += blockDim.x) {
         const int r = idx % D, tok = idx / D;
         const int tile = r / 16, rr = r % 16;
         float v = 0.f;
         for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + rr * TOK + tok];
+        for (uint32_t j = 1; j < slices; ++j) v += gathered[(j - 1) * D * TOK + idx];
         v *= scale_s[tok < T ? tok : 0];
         v += bias_s[r];
         // the separate kernels round the projection to bfloat16 before rotating it
@@ -445,6 +502,17 @@ static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
     return want < 1 ? 1 : want;
 }
 
+// Blocks of a cluster that share K: a product with few blocks and a long K is cut so that
+// more SMs pull its weights. 0 = decide here; tests and tuning runs set it.
+static int g_slices_plain = 0, g_slices_qkv = 0;
+
+static int pick_slices(int blocks, int chunks, int forced) {
+    if (forced > 0) return forced;
+    int slices = 1;
+    while (slices < 4 && blocks * slices * 2 <= 148 && chunks / (slices * 2) >= 16) slices *= 2;
+    return slices;
+}
+
 // Dynamic shared memory beyond 48 KB has to be asked for once per kernel (and again only
 // when a larger amount is needed).
 template <typename KernelT>
@@ -463,6 +531,17 @@ static int raise_smem(KernelT kernel, size_t bytes) {
 }  // namespace mb
 
 using namespace mb;
+
+// Force the number of blocks that share K in the plain and in the q/k/v few-token products
+// (1, 2 or 4; 0 = let the library decide).
+MB_EXPORT int mb_gemm_skinny_set_slices(int plain, int qkv) {
+    const bool ok = (plain == 0 || plain == 1 || plain == 2 || plain == 4) &&
+                    (qkv == 0 || qkv == 1 || qkv == 2 || qkv == 4);
+    if (!ok) return MB_ERR_UNSUPPORTED_SIZE;
+    g_slices_plain = plain;
+    g_slices_qkv = qkv;
+    return MB_OK;
+}
 
 // At most 16 tokens: beyond that the activations no longer come cheaply through L1 and the
 // library product (or a tensor-core tile kernel) is the better tool.
@@ -495,13 +574,15 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
         if (norm_w) {                                                                            \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, true>, smem);                           \
             if (rc == MB_OK)                                                                     \
-                MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, true>), blocks, threads, smem, s, in,    \
+                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, true>), dim3(blocks, slices), threads, \
+                          smem, s, 1, slices, 1, in,                                            \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
                           (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
         } else {                                                                                 \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
             if (rc == MB_OK)                                                                     \
-                MB_LAUNCH((skinny_gemm_kernel<NT, EPI_, false>), blocks, threads, smem, s, in,   \
+                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, false>), dim3(blocks, slices), threads, \
+                          smem, s, 1, slices, 1, in,                                            \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
                           (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
         }                                                                                        \
@@ -530,14 +611,16 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
     const int nt = (T + 7) / 8;
     const int tiles = N / 16;
-    const int ksplit = pick_ksplit(tiles, K / 32, norm_w ? 16 : 32);
+    // (blocks if K were not shared: one per row tile once a tile has 8 warps or more)
+    const int slices = norm_w ? 1 : pick_slices(tiles, K / 32, g_slices_plain);
+    const int ksplit = pick_ksplit(tiles * slices, (K / 32 + slices - 1) / slices, norm_w ? 16 : 32);
     const int rowt = ksplit >= 8 ? 1 : 8 / ksplit;
     const int blocks = (tiles + rowt - 1) / rowt;
     const int threads = rowt * ksplit * 32;
     const int half_n = 0;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
-        const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
+        const size_t smem = (size_t)rowt * (ksplit + slices - 1) * 16 * 8 * NT * sizeof(float);
         if (mode == 0) MB_SK_LAUNCH_GEMM(0);
         else if (mode == 1) MB_SK_LAUNCH_GEMM(1);
         else MB_SK_LAUNCH_GEMM(3);
@@ -567,6 +650,7 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     const void* next_w = nullptr;
     void* next_x = nullptr;
     float* next_ss = nullptr;
+    const int slices = 1;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
@@ -583,7 +667,8 @@ MB_EXPORT int mb_gemm_skinny_qkv_supports(int T, int K, int d, int rot) {
     do {                                                                                         \
         rc = raise_smem(skinny_qkv_rope_kernel<NT, DD, NORM_>, smem);                            \
         if (rc == MB_OK)                                                                         \
-            MB_LAUNCH((skinny_qkv_rope_kernel<NT, DD, NORM_>), heads, threads, smem, s, in,      \
+            MB_LAUNCH_CLUSTER((skinny_qkv_rope_kernel<NT, DD, NORM_>), dim3(heads, slices), threads,  \
+                      smem, s, 1, slices, 1, in,                                                \
                       (const bf*)w, (const bf*)bias, (bf*)qkv, c, sin_t, positions, seq_of_token, \
                       table, max_pages, (bf*)k_pages, (bf*)v_pages, T, K, n_q, n_kv, page_size,  \
                       store, ksplit);                                                            \
@@ -606,12 +691,14 @@ MB_EXPORT int mb_gemm_skinny_qkv_rope(const void* x, const float* h, const void*
     const int nt = (T + 7) / 8;
     const int heads = n_q + 2 * n_kv;
     const int rowt = d / 16;
-    const int ksplit = pick_ksplit(heads * rowt, K / 32, (norm_w ? 16 : 32) / rowt);
+    const int slices = norm_w ? 1 : pick_slices(heads, K / 32, g_slices_qkv);
+    const int ksplit = pick_ksplit(heads * rowt * slices, (K / 32 + slices - 1) / slices,
+                                   (norm_w ? 16 : 32) / rowt);
     const int threads = rowt * ksplit * 32;
     const float* c = rot ? cos_t : nullptr;
     int rc = MB_OK;
     MB_SK_NT_SWITCH(nt, {
-        const size_t smem = ((size_t)rowt * ksplit * 16 + d) * 8 * NT * sizeof(float);
+        const size_t smem = ((size_t)rowt * ksplit * 16 + (size_t)d * slices) * 8 * NT * sizeof(float);
         if (d == 64) {
             if (norm_w) MB_SK_LAUNCH_QKV(64, true); else MB_SK_LAUNCH_QKV(64, false);
         } else {

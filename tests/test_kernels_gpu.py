@@ -297,6 +297,27 @@ def test_products_that_normalise_their_own_input(ops, twin, m, hidden):
         assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 4 * 2.0 ** -8
 
 
+@pytest.mark.parametrize("slices", [2, 4])
+def test_products_with_k_shared_between_the_blocks_of_a_cluster(ops, twin, slices):
+    """The few-token products may cut K over the blocks of a thread-block cluster (they do
+    so by themselves only for long K and few row tiles): forced here on every shape."""
+    lib = ops.lib
+    assert lib.mb_gemm_skinny_set_slices(slices, slices) == 0
+    try:
+        for m, n, k in ((1, 1152, 896), (8, 896, 4864), (16, 9728, 896), (13, 48, 96), (3, 896, 64)):
+            test_linear(ops, twin, m, n, k, torch.bfloat16, torch.bfloat16, torch.bfloat16)
+            test_linear(ops, twin, m, n, k, torch.bfloat16, torch.bfloat16, torch.float32)
+        for m, n, k in ((1, 896, 896), (8, 896, 4864), (16, 1536, 320)):
+            test_linear_residual(ops, twin, m, n, k)
+            test_linear_residual_leaves_the_next_norm(ops, twin, m, n, k)
+        for shape in ((14, 2, 64, 16, 896), (12, 2, 128, 16, 1536), (3, 1, 64, 8, 96)):
+            test_qkv_rope_store_fused(ops, twin, *shape, (1, 1, 1), (40, 17, 300))
+            test_qkv_rope_store_fused(ops, twin, *shape, (1,) * 9, tuple(range(5, 50, 5)))
+    finally:
+        assert lib.mb_gemm_skinny_set_slices(0, 0) == 0
+    assert lib.mb_gemm_skinny_set_slices(3, 1) != 0
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,page,hidden", [(14, 2, 64, 16, 896), (12, 2, 128, 16, 1536),
                                                     (3, 1, 64, 8, 96), (4, 4, 128, 32, 64)])
 @pytest.mark.parametrize("q_lens,kv_lens", [((1, 1, 1), (40, 17, 300)), ((1,) * 9, tuple(range(5, 50, 5))),
