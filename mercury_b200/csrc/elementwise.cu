@@ -226,6 +226,65 @@ __global__ void add_rmsnorm_bf16_regs_kernel(float* __restrict__ h,
     }
 }
 
+// The same for many rows (prompt steps): one warp per row, eight rows per block, so that the
+// sum of squares needs shuffles only and each thread has a row's worth of loads in flight.
+// hidden a multiple of 4 and at most 128 * ITEMS.
+template <int ITEMS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_bf16_warp_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                             const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
+                             int count, int hidden, float eps) {
+    grid_dependency_sync();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= count) return;
+    const int64_t at = (int64_t)r * hidden;
+    float4 x[ITEMS];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * 32 + lane) * 4;
+        x[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < hidden) x[it] = *reinterpret_cast<const float4*>(h + at + c);
+    }
+    if (delta) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int c = (it * 32 + lane) * 4;
+            if (c < hidden) {
+                const uint2 dq = *reinterpret_cast<const uint2*>(delta + at + c);
+                const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dq.x));
+                const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dq.y));
+                x[it].x += d0.x;
+                x[it].y += d0.y;
+                x[it].z += d1.x;
+                x[it].w += d1.y;
+                *reinterpret_cast<float4*>(h + at + c) = x[it];
+            }
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it)
+        ss += x[it].x * x[it].x + x[it].y * x[it].y + x[it].z * x[it].z + x[it].w * x[it].w;
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * 32 + lane) * 4;
+        if (c < hidden) {
+            const uint2 wq = *reinterpret_cast<const uint2*>(weight + c);
+            const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.x));
+            const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.y));
+            uint2 oq;
+            *reinterpret_cast<__nv_bfloat162*>(&oq.x) =
+                __floats2bfloat162_rn(x[it].x * rstd * w0.x, x[it].y * rstd * w0.y);
+            *reinterpret_cast<__nv_bfloat162*>(&oq.y) =
+                __floats2bfloat162_rn(x[it].z * rstd * w1.x, x[it].w * rstd * w1.y);
+            *reinterpret_cast<uint2*>(out + at + c) = oq;
+        }
+    }
+}
+
 // bfloat16, the whole head rotated, head size a multiple of 16: one thread per (token, head,
 // run of eight pairs), through 16-byte accesses (a thread holds features [8j, 8j+8) of the
 // first half and the matching eight of the second half).
@@ -343,7 +402,17 @@ MB_EXPORT int mb_add_rmsnorm(float* h, const void* delta, const void* weight, in
             h, (const float*)delta, weight, weight_dtype, (float*)out, rows, hidden, eps);
     else if (dtype == MB_BF16 && weight_dtype == MB_BF16 && hidden % 4 == 0 && hidden <= 8192) {
         typedef __nv_bfloat16 bf;
-        if (hidden <= 1024)
+        // many whole rows: a warp per row (the block-per-row kernels are for the few rows of
+        // a decode step, where a row's latency counts, and for picked rows)
+        if (rows == nullptr && count >= 256 && hidden <= 2048) {
+            const int blocks = (count + 7) / 8;
+            if (hidden <= 1024)
+                MB_LAUNCH((add_rmsnorm_bf16_warp_kernel<8>), blocks, 256, 0, s, h, (const bf*)delta,
+                          (const bf*)weight, (bf*)out, count, hidden, eps);
+            else
+                MB_LAUNCH((add_rmsnorm_bf16_warp_kernel<16>), blocks, 256, 0, s, h, (const bf*)delta,
+                          (const bf*)weight, (bf*)out, count, hidden, eps);
+        } else if (hidden <= 1024)
             MB_LAUNCH((add_rmsnorm_bf16_regs_kernel<2>), count, 128, 0, s, 
                 h, (const bf*)delta, (const bf*)weight, (bf*)out, rows, hidden, eps);
         else if (hidden <= 4096)

@@ -138,6 +138,7 @@ class ModelRunner:
         self.max_pages = max_pages
         self.use_graphs = cuda_graphs and self.device.type == "cuda" and self.model.capturable
         self._graphs: dict[int, tuple] = {}
+        self.dependent_launch_buckets = 16   # largest batch bucket captured with dependent launch
         self.graph_replays = 0
         self.graph_launches = 0      # kernels run by replayed graphs
         self._shape_graphs: dict[tuple, tuple] = {}   # other steps, by the shape of the batch
@@ -271,7 +272,8 @@ class ModelRunner:
             # cached keys before they wait. Prompt steps run without it: their grids are
             # larger than the device and early blocks would only take room (the same holds
             # for decode batches beyond 16, whose products are the library's).
-            dependent = getattr(self.ops, "set_dependent_launch", None) if bucket <= 16 else None
+            dependent = (getattr(self.ops, "set_dependent_launch", None)
+                         if bucket <= self.dependent_launch_buckets else None)
             if dependent is not None:
                 dependent(True)
             try:

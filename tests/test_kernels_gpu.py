@@ -60,7 +60,8 @@ def test_embed(ops, twin, table_dtype):
 # ------------------------------------------------------------------------------ norm
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("rows,cols", [(1, 896), (7, 1536), (64, 100), (1000, 896), (3, 4100)])
+@pytest.mark.parametrize("rows,cols", [(1, 896), (7, 1536), (64, 100), (1000, 896), (3, 4100),
+                                       (259, 1536), (300, 2048), (257, 100), (2048, 3584)])
 @pytest.mark.parametrize("with_delta", [True, False])
 def test_add_rmsnorm(ops, twin, dtype, rows, cols, with_delta):
     h = rand((rows, cols), torch.float32, 1)
