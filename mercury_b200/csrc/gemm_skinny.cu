@@ -224,14 +224,28 @@ __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT]
 // block alternate gate / up, and `half_n` is the width of the result), 3 = added into the
 // float32 rows of `out`.
 template <int NT, int EPI, bool NORM>
-__global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyInput in,
+__global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyInput in_all,
                                    const __nv_bfloat16* __restrict__ w,
-                                   const __nv_bfloat16* __restrict__ bias, void* __restrict__ out,
-                                   int T, int N, int K, int half_n, int rowt, int ksplit,
+                                   const __nv_bfloat16* __restrict__ bias, void* __restrict__ out_all,
+                                   int T_all, int N, int K, int half_n, int rowt, int ksplit,
                                    const __nv_bfloat16* __restrict__ next_norm_w,
-                                   __nv_bfloat16* __restrict__ next_x,
-                                   float* __restrict__ next_ss, int h_stable) {
+                                   __nv_bfloat16* __restrict__ next_x_all,
+                                   float* __restrict__ next_ss_all, int h_stable) {
     constexpr int TOK = 8 * NT;
+    // Tokens beyond the first TOK belong to the blocks further along z: block z takes tokens
+    // [z TOK, z TOK + TOK), with every pointer that is indexed by token moved there.
+    SkinnyInput in = in_all;
+    const int t0 = blockIdx.z * TOK;
+    const int T = T_all - t0 < TOK ? T_all - t0 : TOK;
+    if (in.x) in.x += (int64_t)t0 * K;
+    if (in.rows) in.rows += t0;
+    else if (in.h) in.h += (int64_t)t0 * K;
+    if (in.ss_part) in.ss_part += (int64_t)t0 * in.ss_tiles;
+    void* out = EPI == 0 ? (void*)(reinterpret_cast<__nv_bfloat16*>(out_all) + (int64_t)t0 * N)
+              : EPI == 2 ? (void*)(reinterpret_cast<__nv_bfloat16*>(out_all) + (int64_t)t0 * half_n)
+                         : (void*)(reinterpret_cast<float*>(out_all) + (int64_t)t0 * N);
+    __nv_bfloat16* next_x = next_x_all ? next_x_all + (int64_t)t0 * N : nullptr;
+    float* next_ss = next_ss_all ? next_ss_all + (int64_t)t0 * (N / 16) : nullptr;
     extern __shared__ float red[];  // [rowt * ksplit][16][TOK]
     __shared__ float rstd_s[TOK];
     __shared__ float scale_s[TOK];
@@ -574,14 +588,14 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
         if (norm_w) {                                                                            \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, true>, smem);                           \
             if (rc == MB_OK)                                                                     \
-                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, true>), dim3(blocks, slices), threads, \
+                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, true>), dim3(blocks, slices, groups), threads, \
                           smem, s, 1, slices, 1, in,                                            \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
                           (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
         } else {                                                                                 \
             rc = raise_smem(skinny_gemm_kernel<NT, EPI_, false>, smem);                          \
             if (rc == MB_OK)                                                                     \
-                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, false>), dim3(blocks, slices), threads, \
+                MB_LAUNCH_CLUSTER((skinny_gemm_kernel<NT, EPI_, false>), dim3(blocks, slices, groups), threads, \
                           smem, s, 1, slices, 1, in,                                            \
                           (const bf*)w, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,     \
                           (const bf*)next_w, (bf*)next_x, next_ss, h_stable);                    \
@@ -619,12 +633,17 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
     const int threads = rowt * ksplit * 32;
     const int half_n = 0;
     int rc = MB_OK;
-    MB_SK_NT_SWITCH(nt, {
+    // eight tokens per block; further tokens go to further blocks along z (measured on B200:
+    // sixteen tokens in one block need more registers than a 1024-thread block has, and the
+    // spills made the sixteen-token step 1.7 times the eight-token step)
+    const int groups = nt;
+    {
+        constexpr int NT = 1;
         const size_t smem = (size_t)rowt * (ksplit + slices - 1) * 16 * 8 * NT * sizeof(float);
         if (mode == 0) MB_SK_LAUNCH_GEMM(0);
         else if (mode == 1) MB_SK_LAUNCH_GEMM(1);
         else MB_SK_LAUNCH_GEMM(3);
-    })
+    }
     return rc != MB_OK ? rc : launch_status();
 }
 
@@ -652,10 +671,12 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     float* next_ss = nullptr;
     const int slices = 1;
     int rc = MB_OK;
-    MB_SK_NT_SWITCH(nt, {
+    const int groups = nt;
+    {
+        constexpr int NT = 1;
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
         MB_SK_LAUNCH_GEMM(2);
-    })
+    }
     return rc != MB_OK ? rc : launch_status();
 }
 
