@@ -155,6 +155,8 @@ __device__ __forceinline__ void skinny_mainloop(const SkinnyInput& in, const flo
     }
 }
 
+constexpr int SKINNY_PREFETCH_CHUNKS = 8;   // 512 bytes of each weight row
+
 // Ask L2 for this warp's share of the weight rows. Issued before the kernel waits for its
 // predecessor (weights do not depend on it), so that with programmatic dependent launch the
 // weight stream overlaps the tail of the kernel before.
@@ -165,6 +167,9 @@ __device__ __forceinline__ void skinny_prefetch_weights(const __nv_bfloat16* __r
     if (t4 != 0) return;
     const __nv_bfloat16* wa = w + (int64_t)(n0 + g) * K;
     const __nv_bfloat16* wb = w + (int64_t)(n0 + g + 8) * K;
+    // a long share is not asked for in full: every resident block doing so would push more
+    // through L2 than it holds (the loads of the main loop stream the rest)
+    if (c_end > c_begin + SKINNY_PREFETCH_CHUNKS) c_end = c_begin + SKINNY_PREFETCH_CHUNKS;
     for (int c = c_begin; c < c_end; c += 2) {
         asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + c * 32));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + c * 32));
