@@ -22,7 +22,7 @@
 // (mercury/model/qwen2.py:29-31 for the formula).
 // Sizes it takes: K a multiple of 32, N a multiple of 16, at most 64 tokens; the callers
 // fall back to the general kernels otherwise.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace mb {
 
@@ -375,6 +375,184 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyIn
     }
 }
 
+// The same product for matrices that are bound by HBM alone (tens of megabytes and more):
+// the weights do not come by per-thread loads but by TMA. Every warp owns a ring of
+// SKINNY_FED_STAGES boxes of 16 rows x 64 k (2 KB, 128-byte swizzle) of its own row tile and
+// K share, filled by copies that its first lane issues and waits for on the warp's own
+// mbarriers; the ring is filled before the kernel waits for the one in front. A warp keeps
+// 8 KB in flight without holding a register for it, 16 warps 128 KB per SM, which is what
+// the per-thread loads above could not: they stream at 3.6 TB/s, this at the rate of a TMA
+// copy. The fragments are read from shared memory in the same permuted-k order as above
+// (16 bytes per lane: the swizzle keeps the eight rows of a quarter-warp apart), the
+// activations still come through L1, and the epilogues are those of skinny_gemm_kernel.
+// K a multiple of 64; at most 16 warps per block; eight tokens per block, more along z.
+constexpr int SKINNY_FED_STAGES = 4;
+
+template <int EPI, int NT>
+__global__ void __launch_bounds__(512)
+skinny_fed_kernel(const __grid_constant__ CUtensorMap wmap, SkinnyInput in_all,
+                  const __nv_bfloat16* __restrict__ bias, void* __restrict__ out_all, int T_all, int N,
+                  int K, int half_n, int rowt, int ksplit,
+                  const __nv_bfloat16* __restrict__ next_norm_w, __nv_bfloat16* __restrict__ next_x_all,
+                  float* __restrict__ next_ss_all, int* __restrict__ error) {
+    constexpr int TOK = 8 * NT;
+    constexpr int STG = SKINNY_FED_STAGES;
+    SkinnyInput in = in_all;
+    const int t0 = blockIdx.z * TOK;
+    const int T = T_all - t0 < TOK ? T_all - t0 : TOK;
+    if (in.x) in.x += (int64_t)t0 * K;
+    if (in.ss_part) in.ss_part += (int64_t)t0 * in.ss_tiles;
+    void* out = EPI == 0 ? (void*)(reinterpret_cast<__nv_bfloat16*>(out_all) + (int64_t)t0 * N)
+              : EPI == 2 ? (void*)(reinterpret_cast<__nv_bfloat16*>(out_all) + (int64_t)t0 * half_n)
+                         : (void*)(reinterpret_cast<float*>(out_all) + (int64_t)t0 * N);
+    __nv_bfloat16* next_x = next_x_all ? next_x_all + (int64_t)t0 * N : nullptr;
+    float* next_ss = next_ss_all ? next_ss_all + (int64_t)t0 * (N / 16) : nullptr;
+
+    extern __shared__ __align__(1024) unsigned char fed_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(fed_raw) + 1023) & ~(uintptr_t)1023);   // [warps][STG][2048]
+    float* red = reinterpret_cast<float*>(ring + (size_t)rowt * ksplit * STG * 2048);  // [warps][16][TOK]
+    __shared__ uint64_t full[16][STG];
+    __shared__ float scale_s[TOK];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int rt = warp / ksplit, ks = warp - rt * ksplit;
+    int n0;
+    if (EPI == 2) {
+        const int pair = blockIdx.x * (rowt / 2) + rt / 2;
+        n0 = (rt & 1) * half_n + pair * 16;
+    } else {
+        n0 = (blockIdx.x * rowt + rt) * 16;
+    }
+    const int limit = EPI == 2 ? ((rt & 1) + 1) * half_n : N;
+    // this warp's boxes of 64 k
+    const int boxes_all = K / 64;
+    const int per = (boxes_all + ksplit - 1) / ksplit;
+    const int b_begin = ks * per < boxes_all ? ks * per : boxes_all;
+    const int b_end = b_begin + per < boxes_all ? b_begin + per : boxes_all;
+    const int boxes = n0 < limit ? b_end - b_begin : 0;
+    unsigned char* mine = ring + (size_t)warp * STG * 2048;
+    if (lane == 0) {
+        for (int st = 0; st < STG; ++st) mbar_init(&full[warp][st], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int st = 0; st < STG && st < boxes; ++st) {
+            mbar_expect_tx(&full[warp][st], 2048u);
+            tma_load_2d(mine + st * 2048, &wmap, (b_begin + st) * 64, n0, &full[warp][st]);
+        }
+    }
+    __syncwarp();
+    grid_dependency_sync();
+    skinny_row_scale(in, T, scale_s);     // read after the barrier that follows the product
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    {
+        const __nv_bfloat16* xr[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            int tok = nt * 8 + g;
+            if (tok > T - 1) tok = T - 1;      // padding tokens read a real row; their columns are dropped
+            xr[nt] = in.x + (int64_t)tok * K + 8 * t4;
+        }
+        const uint32_t sw = (uint32_t)(g & 7);
+        bool ok = true;
+        for (int b = 0; b < boxes; ++b) {
+            const int st = b % STG;
+            // the activations of this box: asked for before the wait for its weights
+            uint4 x0[NT], x1[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                x0[nt] = *reinterpret_cast<const uint4*>(xr[nt] + (int64_t)(b_begin + b) * 64);
+                x1[nt] = *reinterpret_cast<const uint4*>(xr[nt] + (int64_t)(b_begin + b) * 64 + 32);
+            }
+            ok = mbar_wait(&full[warp][st], (uint32_t)((b / STG) & 1), error, 7);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const unsigned char* box = mine + st * 2048;
+            // rows g and g + 8, 16-byte piece t4 of the first and of the second 32 k
+            const uint4 a0 = *reinterpret_cast<const uint4*>(box + g * 128 + (((uint32_t)t4) ^ sw) * 16);
+            const uint4 b0 = *reinterpret_cast<const uint4*>(box + (g + 8) * 128 + (((uint32_t)t4) ^ sw) * 16);
+            const uint4 a1 = *reinterpret_cast<const uint4*>(box + g * 128 + (((uint32_t)(4 + t4)) ^ sw) * 16);
+            const uint4 b1 = *reinterpret_cast<const uint4*>(box + (g + 8) * 128 + (((uint32_t)(4 + t4)) ^ sw) * 16);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma_bf16_16816(acc[nt], a0.x, b0.x, a0.y, b0.y, x0[nt].x, x0[nt].y);
+                mma_bf16_16816(acc[nt], a0.z, b0.z, a0.w, b0.w, x0[nt].z, x0[nt].w);
+                mma_bf16_16816(acc[nt], a1.x, b1.x, a1.y, b1.y, x1[nt].x, x1[nt].y);
+                mma_bf16_16816(acc[nt], a1.z, b1.z, a1.w, b1.w, x1[nt].z, x1[nt].w);
+            }
+            __syncwarp();      // every lane has used what it read of the box: fill it again
+            if (lane == 0 && b + STG < boxes) {
+                mbar_expect_tx(&full[warp][st], 2048u);
+                tma_load_2d(mine + st * 2048, &wmap, (b_begin + b + STG) * 64, n0, &full[warp][st]);
+            }
+        }
+    }
+    {
+        float* part = red + warp * 16 * TOK;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            part[g * TOK + nt * 8 + 2 * t4] = acc[nt][0];
+            part[g * TOK + nt * 8 + 2 * t4 + 1] = acc[nt][1];
+            part[(g + 8) * TOK + nt * 8 + 2 * t4] = acc[nt][2];
+            part[(g + 8) * TOK + nt * 8 + 2 * t4 + 1] = acc[nt][3];
+        }
+    }
+    __syncthreads();
+
+    if (EPI == 2) {
+        for (int idx = threadIdx.x; idx < (rowt / 2) * 16 * TOK; idx += blockDim.x) {
+            const int r = idx % 16, tok = (idx / 16) % TOK, p = idx / (16 * TOK);
+            const int n = (blockIdx.x * (rowt / 2) + p) * 16 + r;
+            if (tok >= T || n >= half_n) continue;
+            float gate = 0.f, up = 0.f;
+            for (int k = 0; k < ksplit; ++k) {
+                gate += red[((2 * p) * ksplit + k) * 16 * TOK + r * TOK + tok];
+                up += red[((2 * p + 1) * ksplit + k) * 16 * TOK + r * TOK + tok];
+            }
+            gate = __bfloat162float(__float2bfloat16_rn(gate * scale_s[tok]));
+            up = __bfloat162float(__float2bfloat16_rn(up * scale_s[tok]));
+            reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * half_n + n] =
+                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < rowt * 16 * TOK; idx += blockDim.x) {
+            const int r = idx % 16, tok = (idx / 16) % TOK, tile = idx / (16 * TOK);
+            const int tile_global = blockIdx.x * rowt + tile;
+            const int n = tile_global * 16 + r;
+            const bool live = tok < T && n < N;
+            float v = 0.f;
+            for (int k = 0; k < ksplit; ++k) v += red[(tile * ksplit + k) * 16 * TOK + r * TOK + tok];
+            v *= scale_s[tok < T ? tok : 0];
+            if (bias && live) v += __bfloat162float(bias[n]);
+            float sq = 0.f;
+            if (live) {
+                if (EPI == 0) {
+                    reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+                } else if (EPI == 3) {
+                    float* at = reinterpret_cast<float*>(out) + (int64_t)tok * N + n;
+                    const float updated = *at + v;
+                    *at = updated;
+                    if (next_norm_w) {
+                        next_x[(int64_t)tok * N + n] =
+                            __float2bfloat16_rn(updated * __bfloat162float(next_norm_w[n]));
+                        sq = updated * updated;
+                    }
+                } else {
+                    reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+                }
+            }
+            if (EPI == 3 && next_norm_w) {
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (r == 0 && tok < T && tile_global * 16 < N)
+                    next_ss[(int64_t)tok * (N / 16) + tile_global] = sq;
+            }
+        }
+    }
+}
+
 // One block per head of the packed q/k/v projection: D/16 row tiles, each shared by
 // `ksplit` warps. After the product: bias, rotation of q and k heads (pairs i, i + D/2),
 // q written to the qkv buffer, k and v written to the token's slot of the cache page.
@@ -524,6 +702,8 @@ static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
 // Blocks of a cluster that share K: a product with few blocks and a long K is cut so that
 // more SMs pull its weights. 0 = decide here; tests and tuning runs set it.
 static int g_slices_plain = 0, g_slices_qkv = 0;
+// Matrices of at least this many elements go to the TMA-fed kernel (0 = never).
+static long long g_fed_min_elements = 32ll * 1024 * 1024;
 
 static int pick_slices(int blocks, int chunks, int forced) {
     if (forced > 0) return forced;
@@ -536,20 +716,31 @@ static int pick_slices(int blocks, int chunks, int forced) {
 // when a larger amount is needed).
 template <typename KernelT>
 static int raise_smem(KernelT kernel, size_t bytes) {
-    // (one per kernel instantiation; the kernels also hold up to 12 KB of static shared
-    // memory, and the 48 KB that need no asking cover both kinds together)
-    static size_t raised = 32 * 1024;
-    if (bytes <= raised) return MB_OK;
+    // per kernel (instantiations of one template share their function type, so the amount
+    // already asked for is kept by address). The kernels also hold up to 12 KB of static
+    // shared memory, and the 48 KB that need no asking cover both kinds together.
+    static std::unordered_map<const void*, size_t> raised;
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    size_t& have = raised[reinterpret_cast<const void*>(kernel)];
+    if (have == 0) have = 32 * 1024;
+    if (bytes <= have) return MB_OK;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
         cudaSuccess)
         return MB_ERR_UNSUPPORTED_SIZE;
-    raised = bytes;
+    have = bytes;
     return MB_OK;
 }
 
 }  // namespace mb
 
 using namespace mb;
+
+// From how many weight elements on a few-token product takes the TMA-fed kernel (0 = never).
+MB_EXPORT int mb_gemm_skinny_set_fed_min(long long elements) {
+    g_fed_min_elements = elements;
+    return MB_OK;
+}
 
 // Force the number of blocks that share K in the plain and in the q/k/v few-token products
 // (1, 2 or 4; 0 = let the library decide).
@@ -607,6 +798,67 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
         }                                                                                        \
     } while (0)
 
+// The TMA-fed form of the product, for large matrices. pairs > 0 selects the gated form (w
+// holds 2 * pairs * 16 rows, gate rows first). Returns MB_ERR_UNSUPPORTED_SIZE if the shape is
+// not for it (the caller then takes the other kernel).
+static int launch_fed(const SkinnyInput& in, const void* w, const void* bias, void* out, int mode, int T,
+                      int N, int K, int pairs, const void* next_w, void* next_x, float* next_ss,
+                      int* error, cudaStream_t s) {
+    typedef __nv_bfloat16 bf;
+    if (K % 64 || in.norm_w != nullptr || error == nullptr || ((uintptr_t)w & 15)) return MB_ERR_UNSUPPORTED_SIZE;
+    const int rows_total = pairs > 0 ? 2 * pairs * 16 : N;
+    CUtensorMap map;
+    if (!make_map(&map, w, rows_total, K, 16)) return MB_ERR_UNSUPPORTED_SIZE;
+    const int tiles = rows_total / 16;
+    const int boxes = K / 64;
+    // about sixteen warps per SM over the whole device; a warp walks two boxes at least
+    // blocks of eight warps (three of them on an SM: one block's start and end overlap the
+    // others' streaming)
+    // blocks, where the matrix has tiles enough; with few tiles and a long K a tile gets a
+    // block of up to sixteen warps of its own)
+    int ksplit = (148 * 16) / tiles;
+    const int most = pairs > 0 ? 8 : 16;
+    if (ksplit > most) ksplit = most;
+    if (ksplit > boxes / 2) ksplit = boxes / 2;
+    if (ksplit < 1) ksplit = 1;
+    int rowt, blocks;
+    if (pairs > 0) {
+        const int per_block = 4 / ksplit > 0 ? 4 / ksplit : 1;
+        rowt = 2 * per_block;
+        blocks = (pairs + per_block - 1) / per_block;
+    } else {
+        rowt = 8 / ksplit > 0 ? 8 / ksplit : 1;
+        blocks = (tiles + rowt - 1) / rowt;
+    }
+    const int warps = rowt * ksplit;
+    const int threads = warps * 32;
+    const int nt = T > 8 ? 2 : 1;      // sixteen tokens per block where there are more than eight
+    const size_t smem = (size_t)warps * (SKINNY_FED_STAGES * 2048 + 16 * 8 * nt * sizeof(float)) + 1024;
+    const int groups = (T + 8 * nt - 1) / (8 * nt);
+    const int half_n = pairs > 0 ? pairs * 16 : 0;
+    int rc;
+#define MB_FED_(EPI_, NT_)                                                                        \
+    do {                                                                                          \
+        rc = raise_smem(skinny_fed_kernel<EPI_, NT_>, smem);                                      \
+        if (rc == MB_OK)                                                                          \
+            MB_LAUNCH((skinny_fed_kernel<EPI_, NT_>), dim3(blocks, 1, groups), threads, smem, s,  \
+                      map, in, (const bf*)bias, out, T, N, K, half_n, rowt, ksplit,               \
+                      (const bf*)next_w, (bf*)next_x, next_ss, error);                            \
+    } while (0)
+#define MB_FED(EPI_)                                                                              \
+    do {                                                                                          \
+        if (nt == 1) MB_FED_(EPI_, 1);                                                            \
+        else MB_FED_(EPI_, 2);                                                                    \
+    } while (0)
+    if (pairs > 0) MB_FED(2);
+    else if (mode == 0) MB_FED(0);
+    else if (mode == 1) MB_FED(1);
+    else MB_FED(3);
+#undef MB_FED_
+#undef MB_FED
+    return rc != MB_OK ? rc : launch_status();
+}
+
 // The activations are either `x` (bfloat16 [T, K]) or, when `norm_w` is given, the float32
 // stream `h` [*, K] normalised with `norm_w` and `eps`, rows picked by `rows` if not null.
 // mode: 0 = bfloat16 out, 1 = float32 out, 3 = add into the float32 rows of `out`.
@@ -621,13 +873,18 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
                              float eps, const float* ss_part, int ss_tiles, float ss_eps, int ss_k,
                              const void* w, const void* bias, void* out, int mode, int T, int N,
                              int K, const void* next_w, void* next_x, float* next_ss, int h_stable,
-                             void* stream) {
+                             int* error, void* stream) {
     if (next_w && (mode != 3 || !next_x || !next_ss)) return MB_ERR_UNSUPPORTED_SIZE;
     if (!mb_gemm_skinny_supports(T, N, K)) return MB_ERR_UNSUPPORTED_SIZE;
     if (mode != 0 && mode != 1 && mode != 3) return MB_ERR_BAD_DTYPE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
+    // large matrices: weights by TMA (`error` as for mb_gemm_tcgen05, code 7; null: never)
+    if (g_fed_min_elements > 0 && (long long)N * K >= g_fed_min_elements) {
+        const int rc_fed = launch_fed(in, w, bias, out, mode, T, N, K, 0, next_w, next_x, next_ss, error, s);
+        if (rc_fed != MB_ERR_UNSUPPORTED_SIZE) return rc_fed;
+    }
     const int nt = (T + 7) / 8;
     const int tiles = N / 16;
     // (blocks if K were not shared: one per row tile once a tile has 8 warps or more)
@@ -656,11 +913,16 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
 MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* norm_w,
                                     const int* rows, float eps, const float* ss_part, int ss_tiles,
                                     float ss_eps, int ss_k, const void* w, void* out, int T,
-                                    int width, int K, void* stream) {
+                                    int width, int K, int* error, void* stream) {
     if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
+    if (g_fed_min_elements > 0 && 2ll * width * K >= g_fed_min_elements) {
+        const int rc_fed = launch_fed(in, w, nullptr, out, 0, T, 2 * width, K, width / 16, nullptr, nullptr,
+                                      nullptr, error, s);
+        if (rc_fed != MB_ERR_UNSUPPORTED_SIZE) return rc_fed;
+    }
     const int nt = (T + 7) / 8;
     const int pairs = width / 16;
     const int ksplit = pick_ksplit(2 * pairs, K / 32, norm_w ? 8 : 16);

@@ -221,8 +221,9 @@ class CudaOps:
             check(self.lib.mb_gemm_skinny(
                 *self._skinny_input(x), _ptr(weight), _ptr(bias), _ptr(h), 3, m, n, k,
                 _ptr(then_norm.weight) if fuse else None, _ptr(normed), _ptr(sums), int(stable),
-                self._stream()), "linear_residual (skinny)")
+                _ptr(self._error_word()), self._stream()), "linear_residual (skinny)")
             self.launches += 1
+            self._tc_pending = True
             self._note_stream_write()
             if fuse:
                 from ..parts.norm import PendingScaled
@@ -248,9 +249,11 @@ class CudaOps:
                 and (n * k <= self.skinny_max_elements or self.gemm == "simt")):
             check(self.lib.mb_gemm_skinny(*self._skinny_input(x), _ptr(weight), _ptr(bias),
                                           _ptr(out), 0 if out.dtype == torch.bfloat16 else 1, m, n, k,
-                                          None, None, None, 0, self._stream()),
+                                          None, None, None, 0, _ptr(self._error_word()),
+                                          self._stream()),
                   "linear (skinny)")
             self.launches += 1
+            self._tc_pending = True
             return
         if pending is not None:
             x = pending.materialize()
@@ -299,9 +302,11 @@ class CudaOps:
                 and self.lib.mb_gemm_skinny_supports(m, width, k)
                 and 2 * width * k <= self.skinny_max_elements):
             check(self.lib.mb_gemm_skinny_swiglu(*self._skinny_input(x), _ptr(weight), _ptr(out),
-                                                 m, width, k, self._stream()),
+                                                 m, width, k, _ptr(self._error_word()),
+                                                 self._stream()),
                   "linear_swiglu (skinny)")
             self.launches += 1
+            self._tc_pending = True
             return
         if self._pending(x) is not None:
             x = x.materialize()

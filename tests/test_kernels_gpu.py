@@ -298,6 +298,26 @@ def test_products_that_normalise_their_own_input(ops, twin, m, hidden):
         assert float((got.double() - want.double()).abs().max() / want.double().abs().max()) <= 4 * 2.0 ** -8
 
 
+def test_products_fed_by_tma(ops, twin):
+    """Large matrices take the few-token kernel whose weights come by TMA into per-warp rings
+    (by itself from 32 Mi elements on): forced here on small shapes too, every epilogue."""
+    lib = ops.lib
+    assert lib.mb_gemm_skinny_set_fed_min(1) == 0
+    try:
+        for m, n, k in ((1, 1152, 896), (8, 896, 4864), (16, 9728, 896), (13, 48, 64), (3, 896, 64),
+                        (2, 151936, 64), (9, 4112, 320)):
+            test_linear(ops, twin, m, n, k, torch.bfloat16, torch.bfloat16, torch.bfloat16)
+            test_linear(ops, twin, m, n, k, torch.bfloat16, torch.bfloat16, torch.float32)
+        for m, n, k in ((1, 896, 896), (8, 896, 4864), (16, 1536, 320)):
+            test_linear_residual(ops, twin, m, n, k)
+            test_linear_residual_leaves_the_next_norm(ops, twin, m, n, k)
+        for m, width, k in ((1, 4864, 896), (8, 128, 64), (12, 336, 128), (16, 4864, 896), (3, 48, 4864)):
+            test_linear_swiglu(ops, twin, m, width, k)
+        ops.check_errors()
+    finally:
+        assert lib.mb_gemm_skinny_set_fed_min(32 * 1024 * 1024) == 0
+
+
 @pytest.mark.parametrize("slices", [2, 4])
 def test_products_with_k_shared_between_the_blocks_of_a_cluster(ops, twin, slices):
     """The few-token products may cut K over the blocks of a thread-block cluster (they do
