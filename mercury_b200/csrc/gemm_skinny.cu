@@ -703,7 +703,9 @@ static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
 // more SMs pull its weights. 0 = decide here; tests and tuning runs set it.
 static int g_slices_plain = 0, g_slices_qkv = 0;
 // Matrices of at least this many elements go to the TMA-fed kernel (0 = never).
-static long long g_fed_min_elements = 32ll * 1024 * 1024;
+static long long g_fed_min_elements = 16ll * 1024 * 1024;
+// (the gated product: measured slower than the other kernel at 2 x 8960 x 1536)
+static long long g_fed_min_gated = 64ll * 1024 * 1024;
 
 static int pick_slices(int blocks, int chunks, int forced) {
     if (forced > 0) return forced;
@@ -918,7 +920,7 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
-    if (g_fed_min_elements > 0 && 2ll * width * K >= g_fed_min_elements) {
+    if (g_fed_min_elements > 0 && 2ll * width * K >= (g_fed_min_elements > g_fed_min_gated || g_fed_min_elements < 1024 ? g_fed_min_elements : g_fed_min_gated)) {
         const int rc_fed = launch_fed(in, w, nullptr, out, 0, T, 2 * width, K, width / 16, nullptr, nullptr,
                                       nullptr, error, s);
         if (rc_fed != MB_ERR_UNSUPPORTED_SIZE) return rc_fed;

@@ -47,6 +47,9 @@ class CudaOps:
         # alone, and there the library's kernel streams faster (measured on B200 with 8
         # tokens, weights cold: 151936 x 896 in 52 us against 76 us, 5.3 against 3.6 TB/s)
         self.skinny_max_elements = 96 * 1024 * 1024
+        # ... and from this many on, weights come by TMA (gemm_skinny.cu: skinny_fed_kernel);
+        # only those launches have a wait that can give up and so an error word to look at
+        self.fed_min_elements = 16 * 1024 * 1024
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head size 64, the
         # mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
@@ -73,6 +76,7 @@ class CudaOps:
         if major != 10:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}x")
         self.lib = library.load()
+        self.lib.mb_gemm_skinny_set_fed_min(self.fed_min_elements)
         # let each kernel be scheduled while its predecessor drains (see csrc/common.cuh)
         self.dependent_launch = bool(dependent_launch)     # True: on every launch, not only in graphs
         self.lib.mb_set_dependent_launch(int(dependent_launch))
@@ -171,9 +175,11 @@ class CudaOps:
         code = int(self._tc_error.item())
         if code:
             self._tc_error.zero_()
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue",
-                    4: "the producer's drain"}.get(code, f"code {code}")
-            raise KernelError(f"a tcgen05 product gave up waiting in {role}; its output is invalid")
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue or the softmax",
+                    4: "the producer's drain or the wait for the output", 5: "the MMA issuer (P)",
+                    6: "the meeting of a row's two softmax threads",
+                    7: "a weight ring of a few-token product"}.get(code, f"code {code}")
+            raise KernelError(f"a kernel gave up waiting in {role}; its output is invalid")
 
     # -- inputs that may still be an unevaluated norm (parts/norm.py: PendingNorm)
 
@@ -223,7 +229,7 @@ class CudaOps:
                 _ptr(then_norm.weight) if fuse else None, _ptr(normed), _ptr(sums), int(stable),
                 _ptr(self._error_word()), self._stream()), "linear_residual (skinny)")
             self.launches += 1
-            self._tc_pending = True
+            self._tc_pending = self._tc_pending or n * k >= self.fed_min_elements
             self._note_stream_write()
             if fuse:
                 from ..parts.norm import PendingScaled
@@ -253,7 +259,7 @@ class CudaOps:
                                           self._stream()),
                   "linear (skinny)")
             self.launches += 1
-            self._tc_pending = True
+            self._tc_pending = self._tc_pending or n * k >= self.fed_min_elements
             return
         if pending is not None:
             x = pending.materialize()
@@ -306,7 +312,7 @@ class CudaOps:
                                                  self._stream()),
                   "linear_swiglu (skinny)")
             self.launches += 1
-            self._tc_pending = True
+            self._tc_pending = self._tc_pending or 2 * width * k >= self.fed_min_elements
             return
         if self._pending(x) is not None:
             x = x.materialize()
