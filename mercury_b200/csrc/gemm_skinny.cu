@@ -703,7 +703,7 @@ static int pick_ksplit(int tiles, int chunks, int max_ksplit) {
 // more SMs pull its weights. 0 = decide here; tests and tuning runs set it.
 static int g_slices_plain = 0, g_slices_qkv = 0;
 // Matrices of at least this many elements go to the TMA-fed kernel (0 = never).
-static long long g_fed_min_elements = 16ll * 1024 * 1024;
+static long long g_fed_min_elements = 12ll * 1024 * 1024;
 // (the gated product: measured slower than the other kernel at 2 x 8960 x 1536)
 static long long g_fed_min_gated = 64ll * 1024 * 1024;
 

@@ -49,7 +49,7 @@ class CudaOps:
         self.skinny_max_elements = 96 * 1024 * 1024
         # ... and from this many on, weights come by TMA (gemm_skinny.cu: skinny_fed_kernel);
         # only those launches have a wait that can give up and so an error word to look at
-        self.fed_min_elements = 16 * 1024 * 1024
+        self.fed_min_elements = 12 * 1024 * 1024
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head size 64, the
         # mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"

@@ -300,7 +300,7 @@ def test_products_that_normalise_their_own_input(ops, twin, m, hidden):
 
 def test_products_fed_by_tma(ops, twin):
     """Large matrices take the few-token kernel whose weights come by TMA into per-warp rings
-    (by itself from 16 Mi elements on, the gated product from 64 Mi): forced here on small shapes too, every epilogue."""
+    (by itself from 12 Mi elements on, the gated product from 64 Mi): forced here on small shapes too, every epilogue."""
     lib = ops.lib
     assert lib.mb_gemm_skinny_set_fed_min(1) == 0
     try:
@@ -315,7 +315,7 @@ def test_products_fed_by_tma(ops, twin):
             test_linear_swiglu(ops, twin, m, width, k)
         ops.check_errors()
     finally:
-        assert lib.mb_gemm_skinny_set_fed_min(16 * 1024 * 1024) == 0
+        assert lib.mb_gemm_skinny_set_fed_min(12 * 1024 * 1024) == 0
 
 
 @pytest.mark.parametrize("slices", [2, 4])
