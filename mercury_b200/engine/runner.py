@@ -288,6 +288,12 @@ class ModelRunner:
         graph.replay()
         self.graph_replays += 1
         self.graph_launches += kernels
+        # kernels with bounded waits (TMA-fed products) report through an error word; inside a
+        # graph nobody looks at it, so it is read now and then (a read is a synchronisation)
+        check = getattr(self.ops, "check_errors", None)
+        if check is not None and self.graph_replays % 256 == 0:
+            self.ops._tc_pending = True
+            check()
         self.finish(entries)
         if not wanted:
             return None
