@@ -652,14 +652,23 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
-                                const __nv_bfloat16* __restrict__ k_pages,
-                                const __nv_bfloat16* __restrict__ v_pages,
+                                const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages,
                                 const int* __restrict__ table, int max_pages,
                                 const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
                                 __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size,
-                                float scale, int window) {
+                                float scale, int window, const float* __restrict__ cos_t,
+                                const float* __restrict__ sin_t, int raw, int store) {
+    // raw: q, k and v in `qkv` are the projection as it came out of the product (bias added,
+    // not rotated, nothing stored): this kernel rotates the queries as it loads them, and the
+    // block whose key range holds this step's positions rotates the new keys, writes them and
+    // the new values into the pages (if `store`) and into its own tiles. The product in front
+    // then needs no block per head, and every tile of the pages can be copied before the wait.
     constexpr int CH = D / 8;
     constexpr int STAGES = D == 64 ? 5 : 3;
+    __nv_bfloat16* k_pages_out = const_cast<__nv_bfloat16*>(k_pages);
+    __nv_bfloat16* v_pages_out = const_cast<__nv_bfloat16*>(v_pages);
+    __shared__ __align__(16) __nv_bfloat16 new_k[16][D]; // this step's keys, rotated
+    __shared__ __align__(16) __nv_bfloat16 new_v[16][D];
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][D]
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
@@ -701,7 +710,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     auto load_tile = [&](int stage, int kt) {
         const int key = kt * MMA_BN + lj;
         int page = -1;
-        if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+        if (key < kv_len && !(raw && key >= first_pos))
+            page = table[(int64_t)seq * max_pages + key / page_size];
         const bool valid = page >= 0;
         const int64_t at =
             valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
@@ -720,25 +730,88 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
 #pragma unroll
     for (int st = 0; st < STAGES; ++st) {
         const int kt = t_lo + st;
-        if (kt < t_hi && kt < t_new) load_tile(st, kt);
+        if (kt < t_hi && (kt < t_new || raw)) load_tile(st, kt);
         asm volatile("cp.async.commit_group;\n" ::);
     }
     grid_dependency_sync();
 
     // ---- after it: the queries, and the tiles of the first STAGES that had to wait
-    for (int idx = tid; idx < 16 * CH; idx += 128) {
-        const int r = idx / CH, c = idx - r * CH;
-        const int tok = r / group, hg = r - tok * group;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (r < rows)
-            val = *reinterpret_cast<const uint4*>(qkv + (int64_t)(q_begin + tok) * q_row_stride +
-                                                  (kvh * group + hg) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
-    }
+    if (!raw) {
+        for (int idx = tid; idx < 16 * CH; idx += 128) {
+            const int r = idx / CH, c = idx - r * CH;
+            const int tok = r / group, hg = r - tok * group;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (r < rows)
+                val = *reinterpret_cast<const uint4*>(qkv + (int64_t)(q_begin + tok) * q_row_stride +
+                                                      (kvh * group + hg) * D + c * 8);
+            *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
+        }
 #pragma unroll
-    for (int st = 0; st < STAGES; ++st) {
-        const int kt = t_lo + st;
-        if (kt < t_hi && kt >= t_new) load_tile(st, kt);
+        for (int st = 0; st < STAGES; ++st) {
+            const int kt = t_lo + st;
+            if (kt < t_hi && kt >= t_new) load_tile(st, kt);
+        }
+    } else {
+        // (the angles are read beside the values they turn: the same trip to L2)
+        const bool rotate = cos_t != nullptr;
+        // eight pairs (i, i + D/2) at a time: 16 bytes of each half of the head, rotated in
+        // float32 with the angles of the token's position, rounded once
+        auto turn8 = [&](const __nv_bfloat16* head, int pos_of, int c, uint4& lo, uint4& hi) {
+            lo = *reinterpret_cast<const uint4*>(head + c * 8);
+            hi = *reinterpret_cast<const uint4*>(head + D / 2 + c * 8);
+            if (!rotate) return;
+            const float4* cs = reinterpret_cast<const float4*>(cos_t + (int64_t)pos_of * (D / 2) + c * 8);
+            const float4* sn = reinterpret_cast<const float4*>(sin_t + (int64_t)pos_of * (D / 2) + c * 8);
+            const float4 c0 = cs[0], c1 = cs[1], s0 = sn[0], s1 = sn[1];
+            const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&lo);
+            __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(&hi);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float x = __bfloat162float(a[e]), y = __bfloat162float(b[e]);
+                a[e] = __float2bfloat16_rn(x * cc[e] - y * ss[e]);
+                b[e] = __float2bfloat16_rn(y * cc[e] + x * ss[e]);
+            }
+        };
+        constexpr int HC = CH / 2;         // 16-byte pieces in half a head
+        for (int idx = tid; idx < 16 * HC; idx += 128) {
+            const int r = idx / HC, c = idx - r * HC;
+            const int tok = r / group, hg = r - tok * group;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (r < rows)
+                turn8(qkv + (int64_t)(q_begin + tok) * q_row_stride + (kvh * group + hg) * D,
+                      first_pos + tok, c, lo, hi);
+            *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = lo;
+            *reinterpret_cast<uint4*>(q_s + r * D + (((c + HC) ^ (r & 7)) * 8)) = hi;
+        }
+        // this step's keys and values, if their tiles are this block's: rotated keys and the
+        // values into shared memory (they are put into their tiles when those come up) and
+        // into the pages
+        for (int idx = tid; idx < q_len * HC; idx += 128) {
+            const int tok = idx / HC, c = idx - tok * HC;
+            const int key = first_pos + tok, kt = key / MMA_BN;
+            if (kt < t_lo || kt >= t_hi) continue;
+            const __nv_bfloat16* src = qkv + (int64_t)(q_begin + tok) * q_row_stride + (n_q + kvh) * D;
+            uint4 klo, khi;
+            turn8(src, key, c, klo, khi);
+            const uint4 vlo = *reinterpret_cast<const uint4*>(src + n_kv * D + c * 8);
+            const uint4 vhi = *reinterpret_cast<const uint4*>(src + n_kv * D + D / 2 + c * 8);
+            *reinterpret_cast<uint4*>(&new_k[tok][c * 8]) = klo;
+            *reinterpret_cast<uint4*>(&new_k[tok][D / 2 + c * 8]) = khi;
+            *reinterpret_cast<uint4*>(&new_v[tok][c * 8]) = vlo;
+            *reinterpret_cast<uint4*>(&new_v[tok][D / 2 + c * 8]) = vhi;
+            if (store) {
+                const int page = table[(int64_t)seq * max_pages + key / page_size];
+                if (page >= 0) {
+                    const int64_t at = (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D;
+                    *reinterpret_cast<uint4*>(k_pages_out + at + c * 8) = klo;
+                    *reinterpret_cast<uint4*>(k_pages_out + at + D / 2 + c * 8) = khi;
+                    *reinterpret_cast<uint4*>(v_pages_out + at + c * 8) = vlo;
+                    *reinterpret_cast<uint4*>(v_pages_out + at + D / 2 + c * 8) = vhi;
+                }
+            }
+        }
     }
     asm volatile("cp.async.commit_group;\n" ::);
 
@@ -772,7 +845,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = t_lo + it;
         const int stage = it % STAGES;
-        if (kt >= t_new) {
+        if (kt >= t_new && !raw) {
             asm volatile("cp.async.wait_group 0;\n" ::);
         } else {
             asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
@@ -783,8 +856,23 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
             asm volatile("cp.async.commit_group;\n" ::);
         }
-        const __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
-        const __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
+        __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
+        __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
+        if (raw && kt >= t_new) {
+            // this step's keys and values take their rows of the tile (the copy left zeros)
+            for (int idx = tid; idx < q_len * CH; idx += 128) {
+                const int tok = idx / CH, c = idx - tok * CH;
+                const int key = first_pos + tok;
+                if (key / MMA_BN != kt) continue;
+                const int row = key % MMA_BN;
+                const int sw = (c ^ (row & 7)) * 8;
+                *reinterpret_cast<uint4*>(kt_s + row * D + sw) =
+                    *reinterpret_cast<const uint4*>(&new_k[tok][c * 8]);
+                *reinterpret_cast<uint4*>(vt_s + row * D + sw) =
+                    *reinterpret_cast<const uint4*>(&new_v[tok][c * 8]);
+            }
+            __syncthreads();
+        }
 
         // this warp's 16 keys of the tile
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -957,6 +1045,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                                     const void* v_pages, const int* table, int max_pages,
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
                                     int page_size, float scale, int window, int num_seqs, int cluster,
+                                    const float* cos_t, const float* sin_t, int raw, int store,
                                     cudaStream_t s) {
     constexpr int STAGES = D == 64 ? 5 : 3;
     const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16);
@@ -983,7 +1072,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     config.numAttrs = num_attrs;
     cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D>, (const bf*)qkv, q_row_stride,
                        (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start, kv_len, (bf*)out,
-                       n_q, n_kv, page_size, scale, window);
+                       n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store);
     return launch_status();
 }
 
@@ -1048,27 +1137,34 @@ MB_EXPORT int mb_attention_mma_supports(int d) { return d == 64 || d == 128; }
 
 // Decode-like batches (at most 16 rows per sequence and KV head) with the key ranges of a
 // (sequence, KV head) as one cluster of `cluster` blocks (1, 2, 4 or 8): no scratch, no
-// counters, one launch. bfloat16, head sizes 64 and 128.
+// counters, one launch. bfloat16, head sizes 64 and 128. With `raw` the q/k/v rows are the
+// bare projection: the kernel rotates with `cos_t` / `sin_t` ([positions, d/2], null = no
+// rotation, the whole head otherwise) and, with `store`, writes this step's keys and values
+// into the pages itself.
 MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
                                                 const void* v_pages, const int* table, int max_pages,
                                                 const int* q_start, const int* kv_len, void* out,
                                                 int tokens, int num_seqs, int max_q_len, int n_q,
                                                 int n_kv, int d, int page_size, float scale, int window,
-                                                int cluster, void* stream) {
+                                                int cluster, const float* cos_t, const float* sin_t,
+                                                int raw, int store, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
     if (q_row_stride % 8) return MB_ERR_ALIGNMENT;
     if (max_q_len * (n_q / n_kv) > 16 || n_kv > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return MB_ERR_UNSUPPORTED_SIZE;
+    // bare projections are only taken by the call that also stores the new keys: a layer that
+    // reads another layer's cache must find this step's keys in the pages
+    if (raw && !store) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 64)
         return launch_attention_decode_cluster<64>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
                                                    q_start, kv_len, out, n_q, n_kv, page_size, scale,
-                                                   window, num_seqs, cluster, s);
+                                                   window, num_seqs, cluster, cos_t, sin_t, raw, store, s);
     return launch_attention_decode_cluster<128>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
                                                 q_start, kv_len, out, n_q, n_kv, page_size, scale, window,
-                                                num_seqs, cluster, s);
+                                                num_seqs, cluster, cos_t, sin_t, raw, store, s);
 }
 
 // Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.

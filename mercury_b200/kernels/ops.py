@@ -448,16 +448,9 @@ class CudaOps:
             if small:
                 splits = self._splits(batch, num_kv_heads, group, 16, 64)
                 if self.decode_clusters and splits < 32 and kernel is None:
-                    cluster = 1
-                    while cluster * 2 <= min(splits, 8):
-                        cluster *= 2
-                    check(self.lib.mb_paged_attention_decode_cluster(
-                        _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
-                        cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
-                        tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim,
-                        cache.page_size, float(scale), int(window), cluster, self._stream()),
-                        "paged_attention (decode clusters)")
-                    self.launches += 1
+                    cluster = self._cluster_of(splits)
+                    self._decode_cluster(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
+                                         window, out, cluster, None, False)
                     return
             else:
                 splits = self._prompt_splits(batch, num_kv_heads, group)
@@ -487,6 +480,56 @@ class CudaOps:
             check(self.lib.mb_paged_attention_simt(*common, _flag(qkv.dtype), self._stream()),
                   "paged_attention")
         self.launches += 1 if splits == 1 else 2
+
+    def _decode_cluster(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
+                        out, cluster, tables, raw):
+        cos, sin = tables if tables is not None else (None, None)
+        check(self.lib.mb_paged_attention_decode_cluster(
+            _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+            cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
+            qkv.shape[0], batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim,
+            cache.page_size, float(scale), int(window), cluster, _ptr(cos), _ptr(sin), int(raw),
+            int(cache.write), self._stream()), "paged_attention (decode clusters)")
+        self.launches += 1
+
+    @staticmethod
+    def _cluster_of(splits: int) -> int:
+        cluster = 1
+        while cluster * 2 <= min(splits, 8):
+            cluster *= 2
+        return cluster
+
+    def qkv_attention(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables, batch,
+                      cache, scale, window, out):
+        """Projection of q/k/v, rotation, store of the new keys and values, and attention over
+        the cache. For decode-like batches (bfloat16, head size 64 or 128, whole-head rotation
+        or none) the projection is the plain few-token product (as many blocks as row tiles,
+        where the fused q/k/v kernel has one per head), and the attention kernel rotates the
+        queries as it loads them and rotates and stores the new keys itself; otherwise
+        `qkv_rope_store` followed by `paged_attention`. Measured on B200 inside the captured
+        decode step (2048-token contexts): Qwen2.5-0.5B sizes, head size 64: batch 8 0.671 ->
+        0.660 ms, batch 1 0.667 -> 0.633 ms, batch 16 1.23 -> 1.11 ms; 1.5B sizes, head size
+        128: 1.515 -> 1.569 ms, hence the head-size condition."""
+        m, k = x.shape
+        group = num_heads // num_kv_heads
+        cos = tables[0] if tables is not None else None
+        fused = (self.decode_clusters and self.skinny and weight.dtype == torch.bfloat16
+                 and x.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
+                 and cache is not None and cache.write and cache.k.dtype == torch.bfloat16
+                 and qkv.dtype == torch.bfloat16 and batch.max_q_len * group <= 16
+                 and head_dim == 64      # measured: at head size 128 the two-kernel form is ahead
+                 and (cos is None or 2 * cos.shape[1] == head_dim)
+                 and self.lib.mb_gemm_skinny_supports(m, weight.shape[0], k))
+        splits = self._splits(batch, num_kv_heads, group, 16, 64) if fused else 0
+        if not fused or splits >= 32:
+            self.qkv_rope_store(x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
+                                batch, cache)
+            self.paged_attention(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
+                                 out)
+            return
+        self.linear(x, weight, bias, qkv)
+        self._decode_cluster(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
+                             out, self._cluster_of(splits), tables, True)
 
     def argmax(self, logits, out):
         rows = logits.shape[0]

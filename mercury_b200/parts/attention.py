@@ -92,6 +92,14 @@ class GroupedQueryAttention(Mixer):
         ops = ctx.ops
         qkv = ctx.buffer("qkv", tokens, self.q_size + 2 * self.kv_size)
         tables = self.position.rotary_tables()
+        attended = ctx.buffer("attended", tokens, self.q_size)
+        fused = getattr(ops, "qkv_attention", None)
+        if fused is not None and (tables is not None or isinstance(self.position, NoPositionEncoding)):
+            # projection, bias, rotation, store into the pages and attention: the kernels
+            # choose how to share the work between them
+            fused(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads, self.num_kv_heads,
+                  self.head_dim, tables, ctx.batch, cache, self.scale, self.window, attended)
+            return self._project_out(attended, ctx, residual, then_norm, tokens)
         if tables is not None or isinstance(self.position, NoPositionEncoding):
             # projection, bias, rotation and the store into the pages, fused where it pays
             ops.qkv_rope_store(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads,
@@ -103,11 +111,14 @@ class GroupedQueryAttention(Mixer):
             self.position.apply(qkv, (self.num_heads, self.num_kv_heads, self.head_dim), ctx)
             ops.rope_cache_write(qkv, self.num_heads, self.num_kv_heads, self.head_dim, None,
                                  ctx.batch, cache)
-        attended = ctx.buffer("attended", tokens, self.q_size)
         ops.paged_attention(
             qkv, self.num_heads, self.num_kv_heads, self.head_dim, ctx.batch, cache,
             self.scale, self.window, attended,
         )
+        return self._project_out(attended, ctx, residual, then_norm, tokens)
+
+    def _project_out(self, attended, ctx, residual, then_norm, tokens):
+        ops = ctx.ops
         if residual is not None:
             return ops.linear_residual(attended, self.out_weight, self.out_b, residual, ctx,
                                        "mixer_out", then_norm=then_norm)

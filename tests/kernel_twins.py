@@ -113,6 +113,12 @@ class TorchOps:
         cache.k[page[keep], :, offset[keep], :] = k[keep].to(cache.k.dtype)
         cache.v[page[keep], :, offset[keep], :] = v[keep].to(cache.v.dtype)
 
+    def qkv_attention(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables, batch,
+                      cache, scale, window, out):
+        self.qkv_rope_store(x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables, batch,
+                            cache)
+        self.paged_attention(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window, out)
+
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
                         window, out):
         group = num_heads // num_kv_heads

@@ -318,6 +318,81 @@ def test_products_fed_by_tma(ops, twin):
         assert lib.mb_gemm_skinny_set_fed_min(12 * 1024 * 1024) == 0
 
 
+QKV_ATTENTION_CASES = [
+    # n_q, n_kv, d, page, hidden, q_lens, kv_lens, window, rotate
+    (14, 2, 64, 16, 896, (1, 1, 1), (2048, 300, 1), 0, True),
+    (14, 2, 64, 16, 896, (1,) * 8, (64, 65, 63, 128, 129, 640, 700, 17), 0, True),
+    (4, 2, 64, 16, 128, (2, 1, 3, 8), (700, 300, 3, 72), 128, True),       # several new tokens
+    (8, 8, 128, 32, 256, (1, 9, 16), (45, 60, 130), 16, True),
+    (12, 2, 128, 16, 1536, (1, 2), (500, 129), 0, True),
+    (7, 1, 64, 64, 64, (2, 1), (333, 64), 0, False),                         # no rotation
+    (8, 1, 64, 8, 96, (1, 1, 1), (64, 65, 1000), 0, True),
+]
+
+
+@pytest.mark.parametrize("splits", [1, 2, 8])
+@pytest.mark.parametrize("case", range(len(QKV_ATTENTION_CASES)), ids=lambda i: f"case{i}")
+def test_projection_rotation_store_and_attention_in_one_op(twin, case, splits):
+    """`qkv_attention` on decode-like batches: the plain product leaves bare q/k/v, the cluster
+    attention kernel rotates the queries, rotates and stores the new keys and values, and
+    attends. Pages, poisoned outside the sequences' keys, and output against the twin."""
+    from mercury_b200.kernels.ops import CudaOps
+
+    n_q, n_kv, d, page, hidden, q_lens, kv_lens, window, rotate = QKV_ATTENTION_CASES[case]
+    ops = CudaOps("cuda", decode_splits=splits)
+    num_pages = sum(-(-kv // page) for kv in kv_lens) + 4
+    drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
+    batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=2, seed=3, drop_before=drop)
+    k, v = fill_cache(batch, table, kv_lens, q_lens, n_kv, d, page, num_pages, torch.bfloat16, 4, True)
+    tokens = batch.num_tokens
+    x = rand((tokens, hidden), torch.bfloat16, 23)
+    w = rand(((n_q + 2 * n_kv) * d, hidden), torch.bfloat16, 24, 0.1)
+    bias = rand(((n_q + 2 * n_kv) * d,), torch.bfloat16, 25)
+    angles = torch.rand((max(kv_lens) + 1, d // 2), generator=torch.Generator().manual_seed(5)) * 6
+    tables = (angles.cos().cuda(), angles.sin().cuda()) if rotate else None
+    qkv = torch.zeros((tokens, (n_q + 2 * n_kv) * d), dtype=torch.bfloat16, device="cuda")
+    qkv_twin = qkv.clone()
+    k_twin, v_twin = k.clone(), v.clone()
+    got = torch.zeros((tokens, n_q * d), dtype=torch.bfloat16, device="cuda")
+    want = torch.zeros_like(got)
+    launches = ops.launches
+    ops.qkv_attention(x, w, bias, qkv, n_q, n_kv, d, tables, batch, LayerCache(k, v, page, table, True),
+                      d ** -0.5, window, got)
+    one_op = d == 64
+    assert ops.launches - launches == 2, "product (or fused q/k/v kernel), then attention"
+    twin.qkv_attention(x, w, bias, qkv_twin, n_q, n_kv, d, tables, batch,
+                       LayerCache(k_twin, v_twin, page, table, True), d ** -0.5, window, want)
+    assert torch.equal(torch.isnan(k), torch.isnan(k_twin)), "keys stored in the wrong slots"
+    assert torch.equal(torch.isnan(v), torch.isnan(v_twin)), "values stored in the wrong slots"
+    for mine, theirs in ((k, k_twin), (v, v_twin)):
+        a, b = torch.nan_to_num(mine).double(), torch.nan_to_num(theirs).double()
+        assert float((a - b).abs().max() / b.abs().max()) <= 4 * 2.0 ** -8
+    live = batch.seq_of_token >= 0
+    assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
+    attention_close(got[live], want[live], torch.bfloat16, "clusters")
+    if not one_op:
+        # the kernels of the one-op path take head size 128 too (the op leaves it to the other
+        # form because that is faster there): run them directly
+        k3, v3 = fill_cache(batch, table, kv_lens, q_lens, n_kv, d, page, num_pages, torch.bfloat16, 4, True)
+        ops.linear(x, w, bias, qkv)
+        got.zero_()
+        ops._decode_cluster(qkv, n_q, n_kv, d, batch, LayerCache(k3, v3, page, table, True), d ** -0.5,
+                            window, got, ops._cluster_of(splits), tables, True)
+        assert torch.equal(torch.isnan(k3), torch.isnan(k_twin))
+        assert torch.equal(torch.isnan(v3), torch.isnan(v_twin))
+        for mine, theirs in ((k3, k_twin), (v3, v_twin)):
+            a, b = torch.nan_to_num(mine).double(), torch.nan_to_num(theirs).double()
+            assert float((a - b).abs().max() / b.abs().max()) <= 4 * 2.0 ** -8
+        assert torch.isfinite(got[live]).all()
+        attention_close(got[live], want[live], torch.bfloat16, "clusters")
+    # a call that only reads another layer's cache must not take the one-op path
+    launches = ops.launches
+    ops.qkv_attention(x, w, bias, qkv, n_q, n_kv, d, tables, batch, LayerCache(k, v, page, table, False),
+                      d ** -0.5, window, got)
+    assert ops.launches - launches == 2          # the fused q/k/v kernel, then attention
+    attention_close(got[live], want[live], torch.bfloat16, "clusters")
+
+
 @pytest.mark.parametrize("slices", [2, 4])
 def test_products_with_k_shared_between_the_blocks_of_a_cluster(ops, twin, slices):
     """The few-token products may cut K over the blocks of a thread-block cluster (they do
