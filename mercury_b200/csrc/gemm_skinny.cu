@@ -229,7 +229,8 @@ __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT]
 // block alternate gate / up, and `half_n` is the width of the result), 3 = added into the
 // float32 rows of `out`.
 template <int NT, int EPI, bool NORM>
-__global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_gemm_kernel(SkinnyInput in_all,
+__global__ void __launch_bounds__(NORM ? 512 : (EPI == 2 ? 448 : 1024), (EPI == 2 && !NORM) ? 3 : 1)
+skinny_gemm_kernel(SkinnyInput in_all,
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ bias, void* __restrict__ out_all,
                                    int T_all, int N, int K, int half_n, int rowt, int ksplit,
@@ -927,7 +928,9 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     }
     const int nt = (T + 7) / 8;
     const int pairs = width / 16;
-    const int ksplit = pick_ksplit(2 * pairs, K / 32, norm_w ? 8 : 16);
+    // (at most 14 warps: the gated kernel is built for three blocks of 448 threads per SM, so
+    // that all its blocks are resident beside the blocks of the kernel in front)
+    const int ksplit = pick_ksplit(2 * pairs, K / 32, 7);
     const int pairs_per_block = ksplit >= 4 ? 1 : 4 / ksplit;
     const int rowt = 2 * pairs_per_block;
     const int blocks = (pairs + pairs_per_block - 1) / pairs_per_block;
