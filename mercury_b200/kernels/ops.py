@@ -503,23 +503,24 @@ class CudaOps:
                       cache, scale, window, out):
         """Projection of q/k/v, rotation, store of the new keys and values, and attention over
         the cache. For decode-like batches (bfloat16, head size 64 or 128, whole-head rotation
-        or none) the projection is the plain few-token product (as many blocks as row tiles,
-        where the fused q/k/v kernel has one per head), and the attention kernel rotates the
+        or none) the projection is the plain product for that many tokens (few tokens: as many
+        blocks as row tiles, where the fused q/k/v kernel has one per head; more: the
+        library's, and the rotary/store kernel's launch is saved), and the attention kernel rotates the
         queries as it loads them and rotates and stores the new keys itself; otherwise
         `qkv_rope_store` followed by `paged_attention`. Measured on B200 inside the captured
         decode step (2048-token contexts): Qwen2.5-0.5B sizes, head size 64: batch 8 0.671 ->
-        0.660 ms, batch 1 0.667 -> 0.633 ms, batch 16 1.23 -> 1.11 ms; 1.5B sizes, head size
+        0.660 ms, batch 1 0.667 -> 0.633 ms, batch 16 1.23 -> 1.11 ms, batch 32 1.27 -> 1.19 ms, batch 64 1.49 ->
+        1.42 ms; 1.5B sizes, head size
         128: 1.515 -> 1.569 ms, hence the head-size condition."""
         m, k = x.shape
         group = num_heads // num_kv_heads
         cos = tables[0] if tables is not None else None
-        fused = (self.decode_clusters and self.skinny and weight.dtype == torch.bfloat16
+        fused = (self.decode_clusters and weight.dtype == torch.bfloat16
                  and x.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
                  and cache is not None and cache.write and cache.k.dtype == torch.bfloat16
                  and qkv.dtype == torch.bfloat16 and batch.max_q_len * group <= 16
                  and head_dim == 64      # measured: at head size 128 the two-kernel form is ahead
-                 and (cos is None or 2 * cos.shape[1] == head_dim)
-                 and self.lib.mb_gemm_skinny_supports(m, weight.shape[0], k))
+                 and (cos is None or 2 * cos.shape[1] == head_dim))
         splits = self._splits(batch, num_kv_heads, group, 16, 64) if fused else 0
         if not fused or splits >= 32:
             self.qkv_rope_store(x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
