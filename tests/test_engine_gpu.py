@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 
 
 def make_engine(name, dtype="float32", num_blocks=64, policy="fcfs", max_running=4, chunk=24,
-                budget=64, model_len=192):
+                budget=64, model_len=192, lookahead=True):
     from mercury_b200 import Engine, EngineConfig
     from mercury_b200.engine.runner import ModelRunner
 
@@ -31,7 +31,8 @@ def make_engine(name, dtype="float32", num_blocks=64, policy="fcfs", max_running
                          max_step_tokens=budget, max_model_len=model_len)
     cfg = EngineConfig(model="(memory)", dtype=dtype, block_size=page, num_blocks=num_blocks,
                        max_running=max_running, max_batched_tokens=budget, prefill_chunk=chunk,
-                       max_model_len=model_len, policy=policy, debug_invariants=True)
+                       max_model_len=model_len, policy=policy, debug_invariants=True,
+                       lookahead=lookahead)
     return Engine(cfg, runner=runner)
 
 
@@ -102,6 +103,46 @@ def test_warm_prefix_cache_preemption_and_policies_keep_the_tokens():
     assert tight.generate(prompts, SamplingParams(), 10) == want
     assert tight.sched.stats["preemptions"] > 0, "the pool was meant to run out"
     assert tight.leaked_pages() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_launching_ahead_changes_no_token_on_the_device(dtype):
+    """The step after the one in flight takes its token ids from the device (patch_tokens):
+    same tokens and same reasons to end as with every step read back first, with requests
+    ending by length at different times and one ending on an end-of-sequence token."""
+    from mercury_b200 import SamplingParams
+
+    name = "B"
+    prompts = prompts_for(name, (5, 17, 33, 60, 44, 9))
+    limits = [12, 3, 9, 1, 7, 15]
+
+    def run(lookahead, eos):
+        engine = make_engine(name, dtype, lookahead=lookahead)
+        engine.eos_ids = set(eos)
+        got = {i: [[], None] for i in range(len(prompts))}
+
+        def sink_for(i):
+            def sink(event):
+                if event.kind == "token":
+                    got[i][0].append(event.token)
+                elif event.kind == "done":
+                    got[i][1] = event.finish_reason
+            return sink
+
+        for i, (prompt, limit) in enumerate(zip(prompts, limits)):
+            engine.submit(f"r{i}", prompt, limit, sink_for(i), SamplingParams(), arrival=float(i))
+        engine.run_until_idle()
+        assert engine.leaked_pages() == 0
+        return [tuple(map(tuple, [got[i][0]])) + (got[i][1],) for i in range(len(prompts))], engine
+
+    plain, _ = run(False, ())
+    ahead, engine = run(True, ())
+    assert ahead == plain and engine.metrics.counters["steps_launched_ahead"] > 5
+    eos = plain[5][0][2]                       # the third token of the longest output
+    stopped, _ = run(False, (eos,))
+    assert stopped[5][1] == "stop"
+    ahead, engine = run(True, (eos,))
+    assert ahead == stopped and engine.metrics.counters["surplus_tokens"] >= 1
 
 
 def test_refusals_and_events():
