@@ -1,5 +1,5 @@
 // Products with few rows of activations (decode steps): out[t, n] = sum_k x[t, k] w[n, k],
-// for up to 64 tokens, bfloat16 operands, float32 accumulation, on the tensor cores
+// for up to 16 tokens, bfloat16 operands, float32 accumulation, on the tensor cores
 // (mma.sync m16n8k16) with the roles swapped: 16 weight rows are the M side of the MMA and
 // 8 tokens its N side, so that no tensor-core work is wasted on padding tokens.
 //
@@ -20,8 +20,9 @@
 // then every block first computes the rows' 1/rms itself (the stream is a few KB) and
 // builds the normalised bfloat16 activations on the fly, which saves the norm's own launch
 // (mercury/model/qwen2.py:29-31 for the formula).
-// Sizes it takes: K a multiple of 32, N a multiple of 16, at most 64 tokens; the callers
-// fall back to the general kernels otherwise.
+// Sizes it takes: K a multiple of 32, N a multiple of 16, at most 16 tokens (eight per
+// block, the second eight in a block further along z); the callers fall back to the general
+// kernels otherwise.
 #include "tcgen05.cuh"
 
 namespace mb {
