@@ -645,10 +645,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // cache except the tile with the newest key is copied into shared memory BEFORE the block
 // waits for the kernel in front (which writes only the newest key and the queries), so that
 // after the wait only the queries, and in one block of the cluster one tile, are fetched.
-// (2) The ranges are merged through distributed shared memory: every block leaves its
-// (maximum, sum, output) in its own shared memory and, after a cluster barrier, each block
-// finishes a share of the rows from all the others' memories; nothing goes through global
-// memory, and there is no ticket to take.
+// (2) The ranges are merged through distributed shared memory: each block finishes a share
+// of the rows. With head size 64 every block writes its (maximum, sum, output) of a row
+// into the shared memory of the block that finishes the row, and after one cluster barrier
+// each block works from its own memory and leaves. With head size 128 (where that landing
+// area would cost the second block per SM) every block keeps its result, and after a cluster
+// barrier each block reads its rows from all the others' memories; a second barrier keeps
+// the memories alive meanwhile. Nothing goes through global memory, and there is no ticket.
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
@@ -675,6 +678,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
     float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][D], after the loop
     float* o_part = o_red + 4 * 16 * D;                                   // [16][D], this block's result
+    // where the other blocks leave their results for this block's rows (head size 64 only):
+    // [range][row of this block][D], then [range][row of this block][maximum, sum]; no
+    // other use, since a block that is done early writes here while this one still runs
+    constexpr bool PUSH = D == 64;
+    float* land_o = reinterpret_cast<float*>(v_s + STAGES * MMA_BN * D);
+    float* land_ml = land_o + 16 * D;
     __shared__ float ml_red[4][16][2];
     __shared__ float ml_part[16][2];                                      // row maximum (log2 units), sum
 
@@ -977,23 +986,97 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
 #pragma unroll
         for (int w = 0; w < 4; ++w)
             if (ml_red[w][r][0] > -INFINITY) sum += ml_red[w][r][1] * fast_exp2(ml_red[w][r][0] - big);
-        for (int c = (tid & 7); c < D; c += 8) {
-            const float v = o_red[(0 * 16 + r) * D + c] + o_red[(1 * 16 + r) * D + c] +
-                            o_red[(2 * 16 + r) * D + c] + o_red[(3 * 16 + r) * D + c];
-            if (num_splits == 1) {
-                if (r < rows)
-                    out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
-                        __float2bfloat16_rn(sum > 0.f ? v / sum : 0.f);
-            } else {
-                o_part[r * D + c] = v;
+        if (PUSH && num_splits > 1) {
+            // row r is finished by block r / per_block: its landing slot for this range
+            const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
+            const uint32_t owner = (uint32_t)(r / per_block);
+            const int slot = (int)split * per_block + (r - (int)owner * per_block);
+            uint32_t dst_o, dst_ml;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                         : "=r"(dst_o)
+                         : "r"((uint32_t)__cvta_generic_to_shared(land_o + slot * D)), "r"(owner));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                         : "=r"(dst_ml)
+                         : "r"((uint32_t)__cvta_generic_to_shared(land_ml + slot * 2)), "r"(owner));
+            if (r < rows) {
+                for (int c4 = (tid & 7); c4 < D / 4; c4 += 8) {
+                    float4 v = *reinterpret_cast<const float4*>(o_red + (0 * 16 + r) * D + 4 * c4);
+#pragma unroll
+                    for (int w = 1; w < 4; ++w) {
+                        const float4 u = *reinterpret_cast<const float4*>(o_red + (w * 16 + r) * D + 4 * c4);
+                        v.x += u.x;
+                        v.y += u.y;
+                        v.z += u.z;
+                        v.w += u.w;
+                    }
+                    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst_o + 16 * c4),
+                                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                                 : "memory");
+                }
+                if ((tid & 7) == 0)
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dst_ml), "f"(big), "f"(sum)
+                                 : "memory");
             }
-        }
-        if ((tid & 7) == 0) {
-            ml_part[r][0] = big;
-            ml_part[r][1] = sum;
+        } else {
+            for (int c = (tid & 7); c < D; c += 8) {
+                const float v = o_red[(0 * 16 + r) * D + c] + o_red[(1 * 16 + r) * D + c] +
+                                o_red[(2 * 16 + r) * D + c] + o_red[(3 * 16 + r) * D + c];
+                if (num_splits == 1) {
+                    if (r < rows)
+                        out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
+                            __float2bfloat16_rn(sum > 0.f ? v / sum : 0.f);
+                } else {
+                    o_part[r * D + c] = v;
+                }
+            }
+            if ((tid & 7) == 0) {
+                ml_part[r][0] = big;
+                ml_part[r][1] = sum;
+            }
         }
     }
     if (num_splits == 1) return;
+
+    if (PUSH) {
+        // ---- the ranges have met in the memory of the blocks that finish them: after the
+        // barrier (the writes above are released by the arrival) nobody touches another
+        // block's memory again, so a block may leave as soon as its own rows are out
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
+        const int r_first = (int)split * per_block;
+        for (int e = tid; e < per_block * D; e += 128) {
+            const int r_local = e / D, c = e % D;
+            const int r = r_first + r_local;
+            if (r >= rows) continue;
+            float mz[8], vz[8], lz[8];
+            float big = -INFINITY;
+#pragma unroll
+            for (int z = 0; z < 8; ++z) {
+                mz[z] = -INFINITY;
+                vz[z] = lz[z] = 0.f;
+                if (z < (int)num_splits) {
+                    const int slot = z * per_block + r_local;
+                    mz[z] = land_ml[slot * 2];
+                    lz[z] = land_ml[slot * 2 + 1];
+                    vz[z] = land_o[slot * D + c];
+                }
+            }
+#pragma unroll
+            for (int z = 0; z < 8; ++z) big = fmaxf(big, mz[z]);
+            float acc = 0.f, denom = 0.f;
+#pragma unroll
+            for (int z = 0; z < 8; ++z) {
+                const float w = mz[z] > -INFINITY ? fast_exp2(mz[z] - big) : 0.f;
+                acc += w * vz[z];
+                denom += w * lz[z];
+            }
+            const int tok = r / group, hg = r - tok * group;
+            out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
+                __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+        }
+        return;
+    }
 
     // ---- the ranges meet: every block finishes its share of the rows from all the blocks
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -1048,7 +1131,9 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                                     const float* cos_t, const float* sin_t, int raw, int store,
                                     cudaStream_t s) {
     constexpr int STAGES = D == 64 ? 5 : 3;
-    const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16);
+    // queries and key/value stages; with head size 64 also the landing area of the merge
+    const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16) +
+                        (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
         if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D>,
