@@ -742,6 +742,20 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         if (kt < t_hi && (kt < t_new || raw)) load_tile(st, kt);
         asm volatile("cp.async.commit_group;\n" ::);
     }
+    // raw: which piece of this step's keys and values this thread will turn and store (threads
+    // other than the ones that load the queries, where there are any: the two loads then
+    // travel together), and its page, looked up now
+    constexpr int HC = CH / 2;             // 16-byte pieces in half a head
+    const int new_idx = (tid + 128 - (16 * HC) % 128) % 128;
+    int new_tok = 0, new_c = 0, new_page = -1;
+    bool new_mine = false;
+    if (raw && new_idx < q_len * HC) {
+        new_tok = new_idx / HC;
+        new_c = new_idx - new_tok * HC;
+        const int key = first_pos + new_tok, kt = key / MMA_BN;
+        new_mine = kt >= t_lo && kt < t_hi;
+        if (new_mine && store) new_page = table[(int64_t)seq * max_pages + key / page_size];
+    }
     grid_dependency_sync();
 
     // ---- after it: the queries, and the tiles of the first STAGES that had to wait
@@ -783,7 +797,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
                 b[e] = __float2bfloat16_rn(y * cc[e] + x * ss[e]);
             }
         };
-        constexpr int HC = CH / 2;         // 16-byte pieces in half a head
         for (int idx = tid; idx < 16 * HC; idx += 128) {
             const int r = idx / HC, c = idx - r * HC;
             const int tok = r / group, hg = r - tok * group;
@@ -797,10 +810,9 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         // this step's keys and values, if their tiles are this block's: rotated keys and the
         // values into shared memory (they are put into their tiles when those come up) and
         // into the pages
-        for (int idx = tid; idx < q_len * HC; idx += 128) {
-            const int tok = idx / HC, c = idx - tok * HC;
-            const int key = first_pos + tok, kt = key / MMA_BN;
-            if (kt < t_lo || kt >= t_hi) continue;
+        if (new_mine) {
+            const int tok = new_tok, c = new_c;
+            const int key = first_pos + tok;
             const __nv_bfloat16* src = qkv + (int64_t)(q_begin + tok) * q_row_stride + (n_q + kvh) * D;
             uint4 klo, khi;
             turn8(src, key, c, klo, khi);
@@ -811,7 +823,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             *reinterpret_cast<uint4*>(&new_v[tok][c * 8]) = vlo;
             *reinterpret_cast<uint4*>(&new_v[tok][D / 2 + c * 8]) = vhi;
             if (store) {
-                const int page = table[(int64_t)seq * max_pages + key / page_size];
+                const int page = new_page;
                 if (page >= 0) {
                     const int64_t at = (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D;
                     *reinterpret_cast<uint4*>(k_pages_out + at + c * 8) = klo;
@@ -838,6 +850,10 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float scale2 = scale * 1.4426950408889634f;
 
+    // raw, and no more tiles than stages: every tile was asked for before the wait and none
+    // is refilled, so one wait and the barrier below stand for the per-tile ones
+    const bool resident = raw && n_tiles <= STAGES;
+    if (resident) asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
     uint32_t qf[D / 16][4];
 #pragma unroll
@@ -854,13 +870,15 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = t_lo + it;
         const int stage = it % STAGES;
-        if (kt >= t_new && !raw) {
-            asm volatile("cp.async.wait_group 0;\n" ::);
-        } else {
-            asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+        if (!resident) {
+            if (kt >= t_new && !raw) {
+                asm volatile("cp.async.wait_group 0;\n" ::);
+            } else {
+                asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+            }
+            __syncthreads();   // tile `it` has landed for everyone; the stage of tile it-1 is free
         }
-        __syncthreads();   // tile `it` has landed for everyone; the stage of tile it-1 is free
-        if (it >= 1) {
+        if (it >= 1 && !resident) {
             const int next = it - 1 + STAGES;
             if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
             asm volatile("cp.async.commit_group;\n" ::);
@@ -961,19 +979,15 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             ml_red[warp][g + h * 8][1] = l[h];
         }
     }
-    __syncthreads();
+    // (each warp's output goes in as it is, on its own maximum; the weights that bring the
+    // four onto the common maximum are applied where they are summed)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = g + h * 8;
-        float big = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
-        const float mine = m[h] > -INFINITY ? fast_exp2(m[h] - big) : 0.f;
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            float2 v = make_float2(o[i][2 * h] * mine, o[i][2 * h + 1] * mine);
-            *reinterpret_cast<float2*>(o_red + (warp * 16 + r) * D + i * 8 + 2 * t4) = v;
-        }
+        for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<float2*>(o_red + (warp * 16 + r) * D + i * 8 + 2 * t4) =
+                make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     __syncthreads();
     // 128 threads: thread -> (row = tid / 8, 8 threads across D)
@@ -981,11 +995,14 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         const int r = tid >> 3;
         const int tok = r / group, hg = r - tok * group;
         float big = -INFINITY, sum = 0.f;
+        float wgt[4];
 #pragma unroll
         for (int w = 0; w < 4; ++w) big = fmaxf(big, ml_red[w][r][0]);
 #pragma unroll
-        for (int w = 0; w < 4; ++w)
-            if (ml_red[w][r][0] > -INFINITY) sum += ml_red[w][r][1] * fast_exp2(ml_red[w][r][0] - big);
+        for (int w = 0; w < 4; ++w) {
+            wgt[w] = ml_red[w][r][0] > -INFINITY ? fast_exp2(ml_red[w][r][0] - big) : 0.f;
+            sum += ml_red[w][r][1] * wgt[w];
+        }
         if (PUSH && num_splits > 1) {
             // row r is finished by block r / per_block: its landing slot for this range
             const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
@@ -1000,14 +1017,14 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
                          : "r"((uint32_t)__cvta_generic_to_shared(land_ml + slot * 2)), "r"(owner));
             if (r < rows) {
                 for (int c4 = (tid & 7); c4 < D / 4; c4 += 8) {
-                    float4 v = *reinterpret_cast<const float4*>(o_red + (0 * 16 + r) * D + 4 * c4);
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int w = 1; w < 4; ++w) {
+                    for (int w = 0; w < 4; ++w) {
                         const float4 u = *reinterpret_cast<const float4*>(o_red + (w * 16 + r) * D + 4 * c4);
-                        v.x += u.x;
-                        v.y += u.y;
-                        v.z += u.z;
-                        v.w += u.w;
+                        v.x += wgt[w] * u.x;
+                        v.y += wgt[w] * u.y;
+                        v.z += wgt[w] * u.z;
+                        v.w += wgt[w] * u.w;
                     }
                     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst_o + 16 * c4),
                                  "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
@@ -1019,8 +1036,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             }
         } else {
             for (int c = (tid & 7); c < D; c += 8) {
-                const float v = o_red[(0 * 16 + r) * D + c] + o_red[(1 * 16 + r) * D + c] +
-                                o_red[(2 * 16 + r) * D + c] + o_red[(3 * 16 + r) * D + c];
+                const float v = wgt[0] * o_red[(0 * 16 + r) * D + c] + wgt[1] * o_red[(1 * 16 + r) * D + c] +
+                                wgt[2] * o_red[(2 * 16 + r) * D + c] + wgt[3] * o_red[(3 * 16 + r) * D + c];
                 if (num_splits == 1) {
                     if (r < rows)
                         out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
