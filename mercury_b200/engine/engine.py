@@ -147,6 +147,12 @@ class Engine:
             p = params[i] if isinstance(params, list) else params
             self.submit(rid, prompt, max_tokens, sink_for(rid), p, arrival=float(base + i))
         if errors:
+            # nothing of a refused call stays queued
+            mine = set(outs)
+            self._commands = [c for c in self._commands
+                              if not (c[0] == "add" and c[1].rid in mine)]
+            for rid in mine:
+                self._sinks.pop(rid, None)
             raise ValueError("; ".join(errors))
         self.run_until_idle()
         return [outs[f"gen-{base + i}"] for i in range(len(prompts))]

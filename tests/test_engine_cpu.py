@@ -118,3 +118,18 @@ def test_abort_while_a_step_is_under_way():
     assert engine.leaked_pages() == 0 and not engine.sched.has_work()
     aborted = [r for r in engine.metrics.finished if r["rid"] == "r1"][0]
     assert aborted["output_tokens"] == len([e for e in events[1] if e.kind == "token"])
+
+
+def test_a_refused_generate_call_leaves_nothing_queued():
+    name = "A"
+    vocab = RAW[name]["vocab_size"]
+    engine = make_engine(name, True)
+    good = random_tokens(9, vocab, 5)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        engine.generate([good, [vocab + 3]], max_tokens=4)
+    assert not engine._commands and not engine._sinks
+    # the engine goes on as if the refused call had not been made
+    tokens = engine.generate([good], max_tokens=4)
+    assert len(tokens) == 1 and len(tokens[0]) == 4
+    assert engine.metrics.counters["finished_requests"] == 1
+    assert engine.leaked_pages() == 0
