@@ -100,6 +100,8 @@ class Engine:
         params = params or SamplingParams()
         arrival = self.clock() if arrival is None else arrival
         ceiling = min(self.runner.max_model_len, self.cfg.kv_capacity_tokens)
+        if rid in self._sinks:
+            return self._reject(rid, sink, f"a request named {rid!r} is still under way")
         if not prompt_ids:
             return self._reject(rid, sink, "prompt must contain at least one token")
         if max_tokens < 1:

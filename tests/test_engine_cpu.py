@@ -133,3 +133,20 @@ def test_a_refused_generate_call_leaves_nothing_queued():
     assert len(tokens) == 1 and len(tokens[0]) == 4
     assert engine.metrics.counters["finished_requests"] == 1
     assert engine.leaked_pages() == 0
+
+
+def test_a_name_in_use_is_refused():
+    name = "A"
+    vocab = RAW[name]["vocab_size"]
+    engine = make_engine(name, True)
+    first, second = [], []
+    engine.submit("same", random_tokens(7, vocab, 1), 3, first.append)
+    engine.submit("same", random_tokens(5, vocab, 2), 3, second.append)
+    assert [e.kind for e in second] == ["error"] and "still under way" in second[0].message
+    engine.run_until_idle()
+    assert [e.kind for e in first] == ["token"] * 3 + ["done"]
+    # once it has ended the name is free again
+    engine.submit("same", random_tokens(5, vocab, 2), 2, second.append)
+    engine.run_until_idle()
+    assert [e.kind for e in second] == ["error", "token", "token", "done"]
+    assert engine.leaked_pages() == 0
