@@ -431,6 +431,17 @@ def run_reference(args) -> dict:
         from mercury.request import SamplingParams as RefParams
     except Exception as err:  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"import failed: {type(err).__name__}: {err}"}
+    try:
+        return _time_reference(args, torch, config_from_dict, write_random_model, RefConfig,
+                               RefEngine, RefParams)
+    except Exception as err:  # noqa: BLE001
+        return {"impl": "reference",
+                "unavailable": " ".join(f"the reference failed while running: "
+                                        f"{type(err).__name__}: {err}".split())[:300]}
+
+
+def _time_reference(args, torch, config_from_dict, write_random_model, RefConfig, RefEngine,
+                    RefParams) -> dict:
     _entry, config = config_from_dict(QWEN25_05B)
     vocab = QWEN25_05B["vocab_size"]
     with tempfile.TemporaryDirectory() as tmp:
