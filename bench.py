@@ -431,6 +431,8 @@ def run_reference(args) -> dict:
         from mercury.request import SamplingParams as RefParams
     except Exception as err:  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"import failed: {type(err).__name__}: {err}"}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device on this box"}
     try:
         return _time_reference(args, torch, config_from_dict, write_random_model, RefConfig,
                                RefEngine, RefParams)
