@@ -97,6 +97,10 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, const 
 // predecessor's memory to be complete; without the attribute it does nothing. Right after
 // it the kernel lets its own successor be scheduled. This hides most of the launch latency
 // between the many small kernels of a decode step.
+// What a kernel does before this call must not depend on the kernel in front (weights,
+// block tables, positions are fine) and must not take a resource that the kernel in front
+// may still be waiting for: above all, tensor memory is allocated only after it, or blocks
+// of the kernel in front that are not yet placed could wait for tensor memory for ever.
 __device__ __forceinline__ void grid_dependency_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
