@@ -1,7 +1,7 @@
 """Random scenarios on the CPU (PyTorch kernel twins): requests that arrive over time, small
 pools, every policy, portions of every size, end-of-sequence tokens, sampling and aborts.
-Launching a step ahead must change no request's tokens or ending, no page may leak, and no
-stand-in may reach a sink."""
+Launching a step ahead must change no request's tokens or ending, greedy requests must give
+the plain implementation's tokens, no page may leak, and no stand-in may reach a sink."""
 
 from __future__ import annotations
 
@@ -9,8 +9,9 @@ import random
 
 import pytest
 
+from plain_qwen2 import plain_generate
 from test_engine_cpu import make_engine
-from tiny import PAGE_SIZE, RAW, random_tokens
+from tiny import PAGE_SIZE, RAW, random_tokens, tiny_model
 
 
 def scenario(seed: int):
@@ -99,6 +100,17 @@ def test_random_scenarios_with_and_without_launching_ahead(seed):
             assert long_[:len(short)] == short
         else:
             assert ahead[i] == plain[i], f"request {i}"
+    # greedy requests against the plain implementation (whole sequences, no cache)
+    name, prompts, limits, params, _arrive, _args, eos, _aborts = sc
+    raw, _config, tensors = tiny_model(name)
+    for i, p in enumerate(params):
+        if not p.greedy or i in aborts:
+            continue
+        want = plain_generate(raw, tensors, prompts[i], limits[i])
+        if not p.ignore_eos:
+            ends = [j for j, token in enumerate(want) if token in eos]
+            want = want[:ends[0] + 1] if ends else want
+        assert ahead[i]["tokens"] == want, f"request {i}"
 
 
 def test_the_scenarios_cover_what_they_are_meant_to():
