@@ -32,7 +32,9 @@ def main(reference_root: str) -> None:
 
     from tiny import RAW, random_tokens, tiny_model
 
-    for name in ("A", "B"):
+    # (name, tokens): D and E add one KV head under 7 and under 32 query heads, head sizes
+    # 64 and 80; C is left out, its sliding window is not something the reference computes
+    for name, length in (("A", 40), ("B", 40), ("D", 24), ("E", 24)):
         raw, _cfg, tensors = tiny_model(name)
         ref_cfg = ModelConfig.from_dict(raw)
         model = Qwen2ForCausalLM(ref_cfg, fused_norm=False).to(torch.float32).eval()
@@ -46,7 +48,7 @@ def main(reference_root: str) -> None:
         model.init_rotary("cpu", torch.float32, 128)
         runner = ModelRunner(engine_cfg, alloc=BlockAllocator(16, 16), model=model,
                              model_config=ref_cfg)
-        tokens = random_tokens(40, RAW[name]["vocab_size"], 9)
+        tokens = random_tokens(length, RAW[name]["vocab_size"], 9)
         logits = runner.forward_prompt(tokens, all_positions=True)
         logits.numpy().astype("<f4").tofile(HERE / f"tiny_{name}.f32")
         (HERE / f"tiny_{name}.json").write_text(json.dumps(

@@ -63,7 +63,7 @@ def test_sampling_rules():
     assert P.plain_uniform(7, 0) != P.plain_uniform(8, 0)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_plain_matches_the_reference_model(name):
     """Logits the reference's own Qwen2ForCausalLM produced on the CPU in float32 for the
     same random weights (made once by tests/golden/make_golden.py, stored as float32)."""
