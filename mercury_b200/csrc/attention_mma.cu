@@ -1237,6 +1237,14 @@ using namespace mb;
 // CUDA-core kernel.
 MB_EXPORT int mb_attention_mma_supports(int d) { return d == 64 || d == 128; }
 
+// Whether a decode-like step should hand the cluster kernel the bare projections (`raw`: it
+// then rotates the queries and rotates and stores the new keys itself) instead of running the
+// fused q/k/v kernel in front of it. Measured inside the captured decode step on B200: at head
+// size 64 the bare form is ahead (batch 8: 0.671 -> 0.660 ms per step), at head size 128 it is
+// behind (1.515 -> 1.569 ms: the kernel's landing area for a new key doubles and one block
+// fewer fits an SM), so the answer is a property of this kernel, asked for here.
+MB_EXPORT int mb_attention_decode_raw_pays(int d) { return d == 64; }
+
 // Decode-like batches (at most 16 rows per sequence and KV head) with the key ranges of a
 // (sequence, KV head) as one cluster of `cluster` blocks (1, 2, 4 or 8): no scratch, no
 // counters, one launch. bfloat16, head sizes 64 and 128. With `raw` the q/k/v rows are the

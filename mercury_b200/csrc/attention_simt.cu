@@ -367,6 +367,13 @@ MB_EXPORT int mb_paged_attention_static(const void* qkv, int q_row_stride, const
                                         int dtype, void* stream) {
     if (num_splits < 1) num_splits = 1;
     if (tokens < 0 || n_q <= 0 || d <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    if (num_splits == 1)
+        // One split keeps its results in registers and writes the output directly: nothing
+        // of the array is used, so its size sets no limit and its address is not needed.
+        return mb_paged_attention_simt(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                       q_start, kv_len, seq_of_token, out, nullptr, 0, tokens,
+                                       num_seqs, max_q_len, n_q, n_kv, d, page_size, scale, window,
+                                       1, dtype, stream);
     const long long need = (long long)tokens * n_q * num_splits * (d + 2);
     if (need > MB_STATIC_SCRATCH_FLOATS) return MB_ERR_SCRATCH;
     int device = -1;
@@ -374,7 +381,9 @@ MB_EXPORT int mb_paged_attention_static(const void* qkv, int q_row_stride, const
         return MB_ERR_LAUNCH;
     if (g_static_scratch_address[device] == nullptr) {
         // In host code `g_static_scratch` is only a handle for the symbol; the address the
-        // kernels need comes from the runtime, for the device that is current now.
+        // kernels need comes from the runtime, for the device that is current now. Two
+        // threads making their first call at once both look the address up and both store
+        // the same value: a race without consequence.
         float* address = nullptr;
         if (cudaGetSymbolAddress((void**)&address, g_static_scratch) != cudaSuccess ||
             address == nullptr)
@@ -382,7 +391,7 @@ MB_EXPORT int mb_paged_attention_static(const void* qkv, int q_row_stride, const
         g_static_scratch_address[device] = address;
     }
     // The split kernel writes every (row, split) pair that the merge kernel reads, so the
-    // array needs no clearing between calls. With one split no scratch is touched at all.
+    // array needs no clearing between calls.
     return mb_paged_attention_simt(qkv, q_row_stride, k_pages, v_pages, table, max_pages, q_start,
                                    kv_len, seq_of_token, out, g_static_scratch_address[device],
                                    MB_STATIC_SCRATCH_FLOATS, tokens, num_seqs, max_q_len, n_q, n_kv,

@@ -357,14 +357,6 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
     }
 }
 
-template <typename TI, typename TO>
-__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, int64_t n) {
-    grid_dependency_sync();
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-         i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = from_float<TO>(to_float(in[i]));
-}
-
 }  // namespace mb
 
 namespace mb {
@@ -474,20 +466,6 @@ MB_EXPORT int mb_rope_store(void* qkv, const float* cos_t, const float* sin_t, i
         MB_LAUNCH((rope_store_kernel<__nv_bfloat16>), tokens, 256, 0, s, 
             (__nv_bfloat16*)qkv, cos_t, sin_t, rot, positions, seq_of_token, table, max_pages,
             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_q, n_kv, d, page_size, store);
-    else
-        return MB_ERR_BAD_DTYPE;
-    return launch_status();
-}
-
-MB_EXPORT int mb_convert(const void* in, int in_dtype, void* out, int out_dtype, long long n,
-                         void* stream) {
-    if (n <= 0) return MB_OK;
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == MB_BF16 && out_dtype == MB_F32)
-        MB_LAUNCH((convert_kernel<__nv_bfloat16, float>), blocks, 256, 0, s, (const __nv_bfloat16*)in, (float*)out, (int64_t)n);
-    else if (in_dtype == MB_F32 && out_dtype == MB_BF16)
-        MB_LAUNCH((convert_kernel<float, __nv_bfloat16>), blocks, 256, 0, s, (const float*)in, (__nv_bfloat16*)out, (int64_t)n);
     else
         return MB_ERR_BAD_DTYPE;
     return launch_status();

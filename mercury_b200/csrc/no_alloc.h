@@ -11,13 +11,17 @@
 // a file-scope `__device__` array inside the library.
 //
 // What the caller has to know:
-//   * Size limit: tokens * n_q * num_splits * (head_dim + 2) floats must not exceed
-//     MB_STATIC_SCRATCH_FLOATS (4 Mi floats = 16 MiB). Larger problems are refused with
-//     MB_ERR_SCRATCH (5) and nothing is launched. Every GPU on which the library is loaded
+//   * Size limit, for num_splits > 1: tokens * n_q * num_splits * (head_dim + 2) floats
+//     must not exceed MB_STATIC_SCRATCH_FLOATS (4 Mi floats = 16 MiB). Larger problems are
+//     refused with MB_ERR_SCRATCH (5) and nothing is launched. With num_splits <= 1 the
+//     array is not used and no limit applies. Every GPU on which the library is loaded
 //     holds these 16 MiB until the process exits.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and remembers it. Make that first
-//     call outside any stream capture. Later calls only launch kernels.
+//     call outside any stream capture. Later calls only launch kernels. The address is
+//     kept per device in a plain table: two threads that make their first call on a device
+//     at the same moment both look it up and store the same value, which is harmless.
+//     The device is the one that is current at the call, which must be the stream's.
 //   * It calls no cudaMalloc, cudaFree or any other allocating routine; inputs and outputs
 //     are the caller's.
 //   * All calls share the one array, which keeps whatever the last call left in it. Nothing

@@ -26,7 +26,7 @@ from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, request_seed
 from .batch import StepEntry
-from .metrics import EngineMetrics, StepRecord
+from .metrics import EngineMetrics, StepRecord, request_record
 from .request import Request, RequestState
 from .runner import ModelRunner
 from .scheduler import Plan, Scheduler
@@ -76,8 +76,9 @@ class Engine:
         self.runner = runner
         cfg.validate_against(runner.spec.max_positions)
         self.cache = runner.cache
-        # a mixer with state of its own cannot skip tokens that a cached prefix would cover
-        prefix_caching = cfg.prefix_caching and not runner.has_state
+        # a request skips the tokens of a cached prefix in every layer or in none, so one
+        # mixer that has to see every token (state of its own) rules the skip out
+        prefix_caching = cfg.prefix_caching and runner.model.skips_cached_prefix
         self.sched = Scheduler(
             self.cache, policy=cfg.policy, max_running=cfg.max_running,
             prefill_budget=cfg.prefill_budget, max_batched_tokens=cfg.max_batched_tokens,
@@ -183,7 +184,9 @@ class Engine:
         ahead = None
         if self.lookahead and self._can_look_ahead(flight):
             for r in flight.sampling:
-                if len(r.out) + 1 < r.max_tokens:      # it goes on unless this token ends it
+                # it goes on unless this token ends it; a request that has already ended
+                # (end of sequence found one step late, or aborted) gets no stand-in
+                if not r.done and len(r.out) + 1 < r.max_tokens:
                     r.out.append(STAND_IN)
                     r.unread = 1
             ahead = self._launch(flight, time.perf_counter())
@@ -284,10 +287,10 @@ class Engine:
                     r.unread = 0
                 if r is not None:
                     self.metrics.counters["aborted_requests"] += 1
-                    r.finished_at = self.clock()
-                    self.metrics.finished.append(r.record())
+                    r.life.end = self.clock()
+                    self.metrics.finished.append(request_record(r))
                     self._emit(r, StreamEvent(rid=r.rid, kind="done", finish_reason="abort",
-                                              t=r.finished_at), close=True)
+                                              t=r.life.end), close=True)
                 else:
                     self._sinks.pop(payload, None)
 
@@ -299,8 +302,8 @@ class Engine:
         else:
             index = len(r.out)
             r.out.append(int(token))
-        if r.first_token_at is None:
-            r.first_token_at = now
+        if r.life.first_token is None:
+            r.life.first_token = now
         self._emit(r, StreamEvent(rid=r.rid, kind="token", token=int(token), index=index, t=now))
         if r.done:
             return   # the sink raised and the request was aborted
@@ -310,12 +313,10 @@ class Engine:
             self._finish(r, "stop", now)
 
     def _finish(self, r: Request, reason: str, now: float) -> None:
-        r.state = RequestState.FINISHED
-        r.finish_reason = reason
-        r.finished_at = now
+        r.end(RequestState.FINISHED, reason, now)
         self.sched.drop(r)
         self.metrics.counters["finished_requests"] += 1
-        self.metrics.finished.append(r.record())
+        self.metrics.finished.append(request_record(r))
         self._emit(r, StreamEvent(rid=r.rid, kind="done", finish_reason=reason, t=now), close=True)
 
     def _emit(self, r: Request, event: StreamEvent, close: bool = False) -> None:

@@ -20,6 +20,27 @@ class StepRecord:
     preempted: int
 
 
+def request_record(r) -> dict:
+    """One finished (or aborted) request as a row of the metrics; the keys are the
+    reference's (mercury/request.py:80-96)."""
+    life = r.life
+    return {
+        "rid": r.rid,
+        "arrival": life.arrival,
+        "admitted_at": life.first_admission,
+        "first_token_at": life.first_token,
+        "finished_at": life.end,
+        "queue_delay": None if life.first_admission is None else life.first_admission - life.arrival,
+        "prompt_tokens": len(r.prompt),
+        "output_tokens": len(r.out),
+        "cached_tokens": life.cached_tokens,
+        "recomputed_tokens": life.computed_tokens,
+        "preemptions": life.preemptions,
+        "finish_reason": life.end_reason,
+        "state": r.state.value,
+    }
+
+
 def percentile(values: list[float], q: float) -> float:
     if not values:
         return 0.0

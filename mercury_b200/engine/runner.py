@@ -122,9 +122,9 @@ class ModelRunner:
                 (2, pages, layer.need.num_kv_heads, page_size, layer.need.head_dim),
                 dtype=dtype, device=self.device)
             self.kv_layers[cache_id] = (store[0], store[1])
-        self.states: dict[int, torch.Tensor] = {
-            index: torch.zeros((max_seqs, *need.shape), dtype=need.dtype, device=self.device)
-            for index, need in self.model.state_needs.items()
+        self.states: dict[tuple[int, int], torch.Tensor] = {
+            key: torch.zeros((max_seqs, *need.shape), dtype=need.dtype, device=self.device)
+            for key, need in self.model.state_needs.items()
         }
         self.has_state = bool(self.states)
         max_pages = -(-self.max_model_len // page_size)
@@ -232,22 +232,15 @@ class ModelRunner:
             size *= 2
         return min(size, self.max_seqs)
 
-    def _graph_splits(self, bucket: int) -> int:
-        """How many ways the keys of each sequence are split in a captured decode step: the
-        grid is fixed at capture, so it is sized to fill the device for this many sequences
-        whatever their lengths turn out to be."""
-        forced = getattr(self.ops, "decode_splits", None)
-        if forced:
-            return max(1, int(forced))
+    def _graph_splits(self, bucket: int) -> int | None:
+        """How many ways the keys of each sequence are split in a captured step of `bucket`
+        sequences: the grid is fixed at capture, so the kernel set sizes it for its device
+        (`graph_splits`); a kernel set without an opinion decides per launch."""
+        choose = getattr(self.ops, "graph_splits", None)
+        if choose is None:
+            return None
         kv_heads = max((l.need.num_kv_heads for l in self.model.cache_layers.values()), default=1)
-        sms = getattr(self.ops, "sm_count", 148)
-        # measured on B200 at 2048-token contexts: about one block per SM for small batches
-        # (at most a dozen ranges per sequence: a range then holds three or more 64-key
-        # tiles), about two per SM once the batch alone brings 32 or more blocks
-        rows = max(1, bucket * kv_heads)
-        if rows <= 16:
-            return max(1, min(12, sms // rows))
-        return max(1, -(-2 * sms // rows))
+        return choose(bucket, kv_heads)
 
     def _decode_with_graph(self, entries: list[StepEntry], sampled=None) -> torch.Tensor | None:
         """Decode-only steps (one token per entry) replay a CUDA graph captured once per

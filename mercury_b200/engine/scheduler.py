@@ -88,8 +88,7 @@ class Scheduler:
                 if r.rid == rid:
                     queue.remove(r)
                     self._release(r)
-                    r.state = RequestState.ABORTED
-                    r.finish_reason = "abort"
+                    r.end(RequestState.ABORTED, "abort")
                     return r
         return None
 
@@ -112,11 +111,10 @@ class Scheduler:
     def _preempt(self, r: Request) -> None:
         self.running.remove(r)
         self._release(r)
-        r.num_cached = 0
-        r.preemptions += 1
+        r.back_to_waiting()
         r.hashes = self.hashes_of(r.tokens)
         self.stats["preemptions"] += 1
-        self.add(r)
+        bisect.insort(self.waiting, r, key=lambda x: x.arrival)
 
     def _score(self, r: Request, now: float) -> float:
         """Admission priority, high first (mercury/scheduler.py:103-120)."""
@@ -194,13 +192,7 @@ class Scheduler:
                 if self.policy == "fcfs" or starving:
                     break
                 continue
-            r.seq = seq
-            r.num_cached = seq.num_computed
-            r.state = RequestState.RUNNING
-            r.last_admitted_at = now
-            if r.admitted_at is None:
-                r.admitted_at = now
-            r.recomputed_tokens += r.seq_len - r.num_cached
+            r.start_running(seq, now)
             prefill_left -= new_tokens
             count = min(new_tokens, self.prefill_chunk, budget)
             planned[r.rid] = PlannedEntry(r, r.num_computed, count, count == new_tokens)

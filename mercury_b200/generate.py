@@ -103,8 +103,10 @@ def main(argv: list[str] | None = None) -> int:
         raise SystemExit(f"--num-blocks {cfg.num_blocks} x --block-size {cfg.block_size} holds fewer "
                          f"tokens than one request needs ({cfg.max_model_len})")
     engine = Engine(cfg)
+    # no per-request seed: each request then draws from a stream of its own, derived from
+    # the engine's seed (--seed) and the request's name
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p,
-                            ignore_eos=args.ignore_eos, seed=args.seed)
+                            ignore_eos=args.ignore_eos, seed=None)
     outs = engine.generate(prompts, params, args.max_tokens)
     for prompt, out in zip(prompts, outs):
         print(json.dumps({"prompt_tokens": len(prompt), "output_ids": out}), flush=True)

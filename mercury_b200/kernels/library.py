@@ -34,7 +34,6 @@ _SIGNATURES = {
     "mb_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
-    "mb_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
     "mb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                      c_int, c_int, c_void_p],
     "mb_paged_attention_simt": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -101,6 +100,8 @@ def load():
     lib.mb_attention_tcgen05_supports.restype = c_int
     lib.mb_attention_mma_supports.argtypes = [c_int]
     lib.mb_attention_mma_supports.restype = c_int
+    lib.mb_attention_decode_raw_pays.argtypes = [c_int]
+    lib.mb_attention_decode_raw_pays.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_attention_scratch_floats.restype = c_longlong
     _LIB = lib

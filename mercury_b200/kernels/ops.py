@@ -82,7 +82,19 @@ class CudaOps:
         self.lib.mb_set_dependent_launch(int(dependent_launch))
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_splits = decode_splits
+        # Key ranges per (sequence, KV head) of a captured decode step, whose grid is fixed at
+        # capture. Measured on B200 at 2048-token contexts: about `graph_blocks_per_sm_small`
+        # blocks per SM while the batch brings at most `graph_small_rows` (sequence, KV head)
+        # pairs, at most `graph_max_ranges_small` ranges each (a range then still holds three
+        # or more 64-key tiles); about `graph_blocks_per_sm_large` per SM beyond that.
+        self.graph_small_rows = 16
+        self.graph_max_ranges_small = 12
+        self.graph_blocks_per_sm_small = 1
+        self.graph_blocks_per_sm_large = 2
         self._scratch: torch.Tensor | None = None
+        # scratch and counters that a larger request replaced: graphs captured earlier still
+        # write to them, so they are never given back to the allocator
+        self._retired: list[torch.Tensor] = []
         self._counters: torch.Tensor | None = None   # zeroed tickets of the in-kernel split merge
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
@@ -119,9 +131,20 @@ class CudaOps:
 
     def _scratch_for(self, floats: int) -> torch.Tensor:
         if self._scratch is None or self._scratch.numel() < floats:
+            if self._scratch is not None:
+                # a captured graph may hold the old buffer's address: keep it allocated
+                self._retired.append(self._scratch)
             self._scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32,
                                         device=self.device)
         return self._scratch
+
+    def _counters_for(self, count: int) -> torch.Tensor:
+        """Zeroed tickets of the in-kernel split merge (the last block resets its own)."""
+        if self._counters is None or self._counters.numel() < count:
+            if self._counters is not None:
+                self._retired.append(self._counters)
+            self._counters = torch.zeros(max(count, 4096), dtype=torch.int32, device=self.device)
+        return self._counters
 
     @staticmethod
     def _rows(t: torch.Tensor) -> torch.Tensor:
@@ -389,6 +412,17 @@ class CudaOps:
             return 1
         return max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
 
+    def graph_splits(self, sequences: int, num_kv_heads: int) -> int:
+        """How many ways the keys of each sequence are split in a captured decode step of
+        `sequences` rows: sized to fill the device whatever the lengths turn out to be."""
+        if self.decode_splits:
+            return max(1, int(self.decode_splits))
+        rows = max(1, sequences * num_kv_heads)
+        if rows <= self.graph_small_rows:
+            return max(1, min(self.graph_max_ranges_small,
+                              self.graph_blocks_per_sm_small * self.sm_count // rows))
+        return max(1, -(-self.graph_blocks_per_sm_large * self.sm_count // rows))
+
     def _prompt_cluster(self, batch, num_kv_heads, group) -> int:
         """CTAs per row tile of the tensor-memory attention. While every CTA of a causal
         prompt is resident from the start (two per SM), the walk over the keys of the last
@@ -467,11 +501,7 @@ class CudaOps:
         if use_mma:
             counters = None
             if splits > 1 and small:
-                need = batch.num_seqs * num_kv_heads
-                if self._counters is None or self._counters.numel() < need:
-                    self._counters = torch.zeros(max(need, 4096), dtype=torch.int32,
-                                                 device=self.device)
-                counters = self._counters
+                counters = self._counters_for(batch.num_seqs * num_kv_heads)
             check(self.lib.mb_paged_attention_mma(*common, _ptr(counters), self._stream()),
                   "paged_attention (mma)")
             self.launches += 1 if (splits == 1 or counters is not None) else 2
@@ -519,7 +549,8 @@ class CudaOps:
                  and x.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
                  and cache is not None and cache.write and cache.k.dtype == torch.bfloat16
                  and qkv.dtype == torch.bfloat16 and batch.max_q_len * group <= 16
-                 and head_dim == 64      # measured: at head size 128 the two-kernel form is ahead
+                 and self.lib.mb_attention_mma_supports(head_dim)
+                 and self.lib.mb_attention_decode_raw_pays(head_dim)
                  and (cos is None or 2 * cos.shape[1] == head_dim))
         splits = self._splits(batch, num_kv_heads, group, 16, 64) if fused else 0
         if not fused or splits >= 32:
@@ -535,6 +566,8 @@ class CudaOps:
     def argmax(self, logits, out):
         rows = logits.shape[0]
         if self._argmax_scratch is None or self._argmax_scratch.numel() < rows * 128:
+            if self._argmax_scratch is not None:
+                self._retired.append(self._argmax_scratch)
             self._argmax_scratch = torch.empty(max(rows, 64) * 128, dtype=torch.float32,
                                                device=self.device)
         check(self.lib.mb_argmax(_ptr(logits), _ptr(out), rows, logits.shape[1],

@@ -53,12 +53,19 @@ def describe_qwen2(config: Qwen2Config) -> ModelSpec:
         hidden_size=config.hidden_size,
         vocab_size=config.vocab_size,
         max_positions=config.max_position_embeddings,
-        embedding_weight="model.embed_tokens.weight",
+        embedding=PartSpec("lookup", {"vocab_size": config.vocab_size,
+                                      "hidden_size": config.hidden_size,
+                                      "weight_name": "model.embed_tokens.weight"}),
         blocks=blocks,
         schedule=[LayerCall(block=i, cache=i) for i in range(config.num_hidden_layers)],
         final_norm=PartSpec("rmsnorm", {"size": config.hidden_size, "eps": config.rms_norm_eps,
                                         "weight_name": "model.norm.weight"}),
-        head_weight=None if config.tie_word_embeddings else "lm_head.weight",
+        # a tied head reads the embedding's tensor; such a checkpoint may still carry a
+        # copy under the head's own name, which nothing reads (mercury/model/loader.py:88-91)
+        head=PartSpec("linear", {"vocab_size": config.vocab_size, "hidden_size": config.hidden_size,
+                                 "weight_name": "model.embed_tokens.weight"
+                                 if config.tie_word_embeddings else "lm_head.weight"}),
+        optional_tensors=("lm_head.weight",) if config.tie_word_embeddings else (),
         eos_token_ids=config.eos_token_ids,
     )
 

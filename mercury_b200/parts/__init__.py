@@ -3,7 +3,9 @@ kinds."""
 
 from .base import (  # noqa: F401
     CacheNeed,
+    Embedding,
     FeedForward,
+    Head,
     LayerCache,
     Mixer,
     Norm,
@@ -15,6 +17,8 @@ from .base import (  # noqa: F401
     TensorSpec,
     build_part,
     register_arrangement,
+    register_embedding,
+    register_head,
     register_feed_forward,
     register_mixer,
     register_norm,

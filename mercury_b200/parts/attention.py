@@ -13,7 +13,6 @@ from __future__ import annotations
 import torch
 
 from .base import CacheNeed, Mixer, PartSpec, TensorSpec, build_part, register_mixer
-from .rotary import NoPositionEncoding
 
 
 class GroupedQueryAttention(Mixer):
@@ -91,16 +90,17 @@ class GroupedQueryAttention(Mixer):
         tokens = x.shape[0]
         ops = ctx.ops
         qkv = ctx.buffer("qkv", tokens, self.q_size + 2 * self.kv_size)
-        tables = self.position.rotary_tables()
+        form = self.position.fused_form()
+        tables = self.position.rotary_tables() if form == "rotary" else None
         attended = ctx.buffer("attended", tokens, self.q_size)
         fused = getattr(ops, "qkv_attention", None)
-        if fused is not None and (tables is not None or isinstance(self.position, NoPositionEncoding)):
+        if fused is not None and form is not None:
             # projection, bias, rotation, store into the pages and attention: the kernels
             # choose how to share the work between them
             fused(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads, self.num_kv_heads,
                   self.head_dim, tables, ctx.batch, cache, self.scale, self.window, attended)
             return self._project_out(attended, ctx, residual, then_norm, tokens)
-        if tables is not None or isinstance(self.position, NoPositionEncoding):
+        if form is not None:
             # projection, bias, rotation and the store into the pages, fused where it pays
             ops.qkv_rope_store(x, self.qkv_weight, self.qkv_b, qkv, self.num_heads,
                                self.num_kv_heads, self.head_dim, tables, ctx.batch, cache)

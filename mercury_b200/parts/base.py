@@ -9,6 +9,12 @@ different layers.
 
 Interfaces
 ----------
+Embedding (`register_embedding`):
+    forward(token_ids, ctx) -> Tensor         the float32 residual stream [T, hidden]
+
+Head (`register_head`):
+    forward(rows, ctx) -> Tensor              float32 logits [rows, vocab] of normalised rows
+
 Every part:
     tensor_specs() -> list[TensorSpec]        the checkpoint tensors it reads, by full name
     load(tensors, setup)                      take (and pack) them; `setup` is a `PartSetup`
@@ -39,14 +45,24 @@ Norm (`register_norm`):
         those rows are normalised and returned, and h is left as it was.
 
 PositionEncoding (`register_position_encoding`):
+    fused_form() -> "rotary" | "identity" | None   what the rotate-and-store kernels can do
+                                              for this encoding: rotate by its tables, leave
+                                              q and k as they are, or nothing (then `apply`)
     rotary_tables() -> (cos, sin) | None      float32 [positions, rotary_dim/2] tables for
                                               the fused rotate-and-store kernel, or None
-    apply(qkv, layout, ctx)                   for encodings the fused kernel does not cover
+    apply(qkv, layout, ctx)                   for encodings the fused kernel does not cover:
+                                              changes q and k of the packed rows in place
 
-Arrangement (`register_arrangement`): how mixer, feed-forward and norms sit in a block.
-    forward(h, delta, ctx, cache, state) -> Tensor   returns the new pending delta (None if
-                                              it is already in the stream); an arrangement
-                                              with `first_norm()` also takes `next_norm=`
+Arrangement (`register_arrangement`): how mixers, feed-forward and norms sit in a block.
+    mixers() -> list[Mixer]                   every mixer of the block, in a fixed order; a
+                                              `LayerCall` names one cache layer per mixer
+    parts() -> list[Part]                     everything that owns checkpoint tensors
+    forward(h, delta, ctx, caches, states) -> Tensor
+                                              `caches[i]` / `states[i]` belong to `mixers()[i]`
+                                              (None where that mixer wants none); returns the
+                                              new pending delta (None if it is already in the
+                                              stream); an arrangement with `first_norm()`
+                                              also takes `next_norm=`
 """
 
 from __future__ import annotations
@@ -105,6 +121,8 @@ class PartSetup:
     dtype: torch.dtype
     ops: Any
     max_positions: int
+    _by_name: dict = field(default_factory=dict)
+    _derived: dict = field(default_factory=dict)
 
     def place(self, tensor: torch.Tensor) -> torch.Tensor:
         """Move a checkpoint tensor to the device under the storage rule: in the float32
@@ -119,6 +137,20 @@ class PartSetup:
         else:
             target = torch.int32
         return tensor.to(device=self.device, dtype=target).contiguous()
+
+    def place_named(self, tensors: dict, name: str) -> torch.Tensor:
+        """`place(tensors[name])`, once per checkpoint tensor: two parts that read the same
+        tensor (a head tied to the embedding table) share one buffer on the device."""
+        if name not in self._by_name:
+            self._by_name[name] = self.place(tensors[name])
+        return self._by_name[name]
+
+    def derived(self, key: tuple, make: Callable[[], Any]) -> Any:
+        """A table computed from constants (rotation angles, say), made once per `key` and
+        shared by every part that asks for the same one."""
+        if key not in self._derived:
+            self._derived[key] = make()
+        return self._derived[key]
 
 
 @dataclass
@@ -155,6 +187,13 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
+    def skips_cached_prefix(self) -> bool:
+        """Whether a request may start behind a prefix whose pages another request left in
+        the cache, so that this mixer never sees the prefix's tokens. True for a mixer whose
+        memory of earlier tokens is in the pages alone; a mixer with state of its own has to
+        run every token."""
+        return self.state_need() is None
+
     def forward(self, x, ctx, cache, state):  # pragma: no cover - interface
         raise NotImplementedError
 
@@ -169,7 +208,20 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def forward(self, token_ids, ctx):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, rows, ctx):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
+    def fused_form(self) -> str | None:
+        return None
+
     def rotary_tables(self):
         return None
 
@@ -185,6 +237,8 @@ _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
     "norm": {},
     "position_encoding": {},
     "arrangement": {},
+    "embedding": {},
+    "head": {},
 }
 
 
@@ -210,6 +264,14 @@ def register_position_encoding(kind: str, factory) -> None:
 
 def register_arrangement(kind: str, factory) -> None:
     _register("arrangement", kind, factory)
+
+
+def register_embedding(kind: str, factory) -> None:
+    _register("embedding", kind, factory)
+
+
+def register_head(kind: str, factory) -> None:
+    _register("head", kind, factory)
 
 
 def build_part(family: str, spec: PartSpec):

@@ -1,4 +1,4 @@
-"""Arrangements: how a mixer, a feed-forward and their norms sit in one block.
+"""Arrangements: how mixers, a feed-forward and their norms sit in one block.
 
 `PreNormBlock` is mercury/model/qwen2.py:72-94: norm, mixer, norm, feed-forward, with the
 residual sum deferred to the next norm. A block receives the residual stream `h` and the
@@ -18,6 +18,9 @@ class PreNormBlock:
         self.mixer_norm = build_part("norm", mixer_norm)
         self.feed_forward_norm = build_part("norm", feed_forward_norm)
 
+    def mixers(self):
+        return [self.mixer]
+
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
@@ -25,8 +28,9 @@ class PreNormBlock:
         """The norm that opens this block (what the block before may compute ahead)."""
         return self.mixer_norm
 
-    def forward(self, h, delta, ctx, cache, state, next_norm=None):
+    def forward(self, h, delta, ctx, caches, states, next_norm=None):
         mixer, ff = self.mixer, self.feed_forward
+        cache, state = caches[0], states[0]
         x = self.mixer_norm.add_norm(h, delta, ctx,
                                      defer=getattr(mixer, "accepts_pending_norm", False))
         if getattr(mixer, "adds_to_residual", False):

@@ -27,12 +27,20 @@ class RotaryEncoding(PositionEncoding):
         self.sin = None
 
     def load(self, tensors, setup):
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
-        inv_freq = 1.0 / (self.theta ** exponent)
-        positions = torch.arange(setup.max_positions, dtype=torch.float32)
-        angles = torch.outer(positions, inv_freq)
-        self.cos = angles.cos().to(setup.device).contiguous()
-        self.sin = angles.sin().to(setup.device).contiguous()
+        def tables():
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+            inv_freq = 1.0 / (self.theta ** exponent)
+            positions = torch.arange(setup.max_positions, dtype=torch.float32)
+            angles = torch.outer(positions, inv_freq)
+            return (angles.cos().to(setup.device).contiguous(),
+                    angles.sin().to(setup.device).contiguous())
+
+        # every layer with the same constants reads the same pair of tables
+        self.cos, self.sin = setup.derived(
+            ("rotary", self.rotary_dim, self.theta, setup.max_positions, str(setup.device)), tables)
+
+    def fused_form(self):
+        return "rotary"
 
     def rotary_tables(self):
         return self.cos, self.sin
@@ -43,6 +51,9 @@ class NoPositionEncoding(PositionEncoding):
 
     def __init__(self, **_ignored):
         pass
+
+    def fused_form(self):
+        return "identity"
 
 
 register_position_encoding("rotary", RotaryEncoding)

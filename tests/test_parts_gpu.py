@@ -7,7 +7,6 @@ import torch
 
 import plain_qwen2 as P
 from mercury_b200.parts import PartSpec, build_part
-from mercury_b200.parts.embedding import OutputHead, TokenEmbedding
 from part_harness import PartStand
 
 pytestmark = pytest.mark.gpu
@@ -59,15 +58,19 @@ def test_rotary_tables_follow_the_plain_angles():
 def test_embedding_and_head(dtype):
     stand = PartStand(dtype)
     table = rand((331, 80), 3)
-    emb = TokenEmbedding(331, 80, "e")
+    emb = build_part("embedding", PartSpec("lookup", {"vocab_size": 331, "hidden_size": 80,
+                                                      "weight_name": "e"}))
     emb.load({"e": table}, stand.setup)
     entries = stand.batch_for([9])
     ids = torch.randint(0, 331, (9,), dtype=torch.int32).cuda()
     h = emb.forward(ids, stand.ctx)
     assert h.dtype == torch.float32
     assert torch.equal(h.cpu(), P.plain_embedding(table.float(), ids.cpu().long()))
-    head = OutputHead(331, 80, None)
-    head.load({}, stand.setup, tied_table=emb.table)
+    # a head that names the embedding's tensor is tied to it: one buffer for both
+    head = build_part("head", PartSpec("linear", {"vocab_size": 331, "hidden_size": 80,
+                                                  "weight_name": "e"}))
+    head.load({"e": table}, stand.setup)
+    assert head.weight.data_ptr() == emb.table.data_ptr()
     rows = rand((4, 80), 4).cuda().to(dtype)
     logits = head.forward(rows, stand.ctx)
     assert logits.dtype == torch.float32
@@ -133,7 +136,7 @@ def test_pre_norm_block(dtype):
     stand.batch_for([33])
     h = torch.randn((33, hidden), generator=torch.Generator().manual_seed(7))
     h_dev = h.cuda()
-    delta = block.forward(h_dev, None, stand.ctx, stand.layer_cache(kv_heads, head_dim), None)
+    delta = block.forward(h_dev, None, stand.ctx, [stand.layer_cache(kv_heads, head_dim)], [None])
     cfg = {"heads": heads, "kv_heads": kv_heads, "head_dim": head_dim, "theta": 10000.0,
            "eps": 1e-6, "windows": [0]}
     want = P.plain_layer(h.double(), {k: v.double() for k, v in weights.items()}, 0, cfg, torch.arange(33))

@@ -79,9 +79,13 @@ def describe_toy(cfg: ToyConfig) -> ModelSpec:
                                     "feed_forward_norm": norm(f"layers.{i}.n2")})
               for i, m in enumerate((attention, toy))]
     return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size, max_positions=512,
-                     embedding_weight="embed", blocks=blocks,
+                     embedding=PartSpec("lookup", {"vocab_size": cfg.vocab_size, "hidden_size": h,
+                                                   "weight_name": "embed"}),
+                     blocks=blocks,
                      schedule=[LayerCall(0, cache=0), LayerCall(1), LayerCall(0, cache=1)],
-                     final_norm=norm("final_norm"), head_weight="head")
+                     final_norm=norm("final_norm"),
+                     head=PartSpec("linear", {"vocab_size": cfg.vocab_size, "hidden_size": h,
+                                              "weight_name": "head"}))
 
 
 def plain_toy(tensors, cfg, tokens):
