@@ -195,6 +195,22 @@ class CacheManager:
                 pool.release(table[index])
                 table[index] = -1
 
+    # ------------------------------------------------------------------ debugging
+
+    def keep_journal(self) -> None:
+        """From now on note every page that gets a first holder or goes back unhashed."""
+        for pool in self.pools:
+            if pool.journal is None:
+                pool.journal = []
+
+    def drain_journal(self) -> list[list[int]]:
+        """Per group, the pages noted since the last call (each once)."""
+        out = []
+        for pool in self.pools:
+            noted, pool.journal = pool.journal or [], ([] if pool.journal is not None else None)
+            out.append(sorted({page for _what, page in noted}))
+        return out
+
     # ------------------------------------------------------------------ checks
 
     def num_available(self) -> list[int]:

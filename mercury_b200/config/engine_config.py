@@ -8,6 +8,7 @@ does not: `max_batched_tokens` (tokens of one step, decode tokens included) and
 `prefill_chunk` (most tokens of one prompt in one step). `cuda_graphs` replays decode-only
 steps from captured graphs. `prefix_caching` switches the hash lookup at admission.
 `lookahead` lets the engine launch a step before it has read the tokens of the step in front.
+`debug_poison_pages` fills cache pages with NaN whenever they change hands.
 """
 
 from __future__ import annotations
@@ -61,6 +62,7 @@ class EngineConfig:
     lookahead: bool = True
     seed: int = 0
     debug_invariants: bool = False
+    debug_poison_pages: bool = False
     max_step_records: int = 500_000
 
     def __post_init__(self) -> None:

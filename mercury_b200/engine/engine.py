@@ -72,7 +72,7 @@ class Engine:
                 cfg.model, dtype=cfg.torch_dtype, device=cfg.device, page_size=cfg.block_size,
                 num_pages=cfg.num_blocks, max_seqs=cfg.max_running,
                 max_step_tokens=cfg.max_batched_tokens, max_model_len=cfg.max_model_len, ops=ops,
-                cuda_graphs=cfg.cuda_graphs)
+                cuda_graphs=cfg.cuda_graphs, poison_pages=cfg.debug_poison_pages)
         self.runner = runner
         cfg.validate_against(runner.spec.max_positions)
         self.cache = runner.cache
@@ -93,6 +93,9 @@ class Engine:
         self._submitted = 0
         self._flight: _Flight | None = None
         self.lookahead = cfg.lookahead
+        # debugging aid: called as tap(requests, logits) with the float32 logits rows a step
+        # samples from (row i belongs to requests[i], whose next output index is len(out))
+        self.tap: Callable | None = None
 
     # ------------------------------------------------------------------ client side
 
@@ -249,6 +252,8 @@ class Engine:
         sampled = self.sampler.on_device(before.handle) if before and before.handle else None
         logits = self.runner.step(entries, sampled)
         handle = None
+        if sampling and self.tap is not None:
+            self.tap(sampling, logits)
         if sampling:
             handle = self.sampler.begin(logits, [(r.params, r.seed, len(r.out)) for r in sampling])
         return _Flight(plan, sampling, handle, t_start)

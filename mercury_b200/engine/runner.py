@@ -84,10 +84,15 @@ class ModelRunner:
         config: ModelConfig | None = None,
         tensors: dict[str, torch.Tensor] | None = None,
         cuda_graphs: bool = True,
+        poison_pages: bool = False,
     ):
         """`model` is a folder with config.json and safetensors; or pass `config` and
         `tensors` (a `{name: tensor}` dictionary) directly. `ops` is the kernel set; by
-        default the CUDA kernels, which refuse to load without a GPU."""
+        default the CUDA kernels, which refuse to load without a GPU. `poison_pages` is a
+        debugging aid: every page is filled with NaN when it gets its first holder and when
+        it goes back to the free list, so that a kernel that reads a key it should not see
+        (beyond a sequence's length, on a page of another request, left by an earlier
+        owner) yields NaN instead of a plausible number."""
         self.device = torch.device(device)
         self.dtype = dtype
         if config is None:
@@ -127,6 +132,12 @@ class ModelRunner:
             for key, need in self.model.state_needs.items()
         }
         self.has_state = bool(self.states)
+        self.poison_pages = bool(poison_pages)
+        if self.poison_pages:
+            self.cache.keep_journal()
+            for k, v in self.kv_layers.values():
+                k.fill_(float("nan"))
+                v.fill_(float("nan"))
         max_pages = -(-self.max_model_len // page_size)
         self.buffers = BatchBuffers(self.device, max_step_tokens, max_seqs, max_pages,
                                     max(1, len(self.model.group_windows)),
@@ -165,6 +176,20 @@ class ModelRunner:
 
     def close(self, seq: Sequence) -> None:
         self.cache.close(seq)
+        self._poison()
+
+    def _poison(self) -> None:
+        """Overwrite with NaN the pages that changed hands since the last call."""
+        if not self.poison_pages:
+            return
+        for group, pages in enumerate(self.cache.drain_journal()):
+            if not pages:
+                continue
+            index = torch.tensor(pages, dtype=torch.long, device=self.device)
+            for cache_id, layer in self.model.cache_layers.items():
+                if layer.group == group:
+                    for side in self.kv_layers[cache_id]:
+                        side.index_fill_(0, index, float("nan"))
 
     def _reset_fresh_state(self) -> None:
         fresh, self.cache.fresh_slots = self.cache.fresh_slots, []
@@ -192,6 +217,7 @@ class ModelRunner:
                     f"{e.seq.seq_id}: no pages left for tokens up to {end} "
                     f"(available per group: {self.cache.num_available()})")
         self._reset_fresh_state()
+        self._poison()
         batch = self.buffers.build(entries, self.page_size, **capacities)
         if batch.late_tokens:
             if sampled is None:

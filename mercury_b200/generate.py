@@ -56,6 +56,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="read every step's tokens before the next step is launched")
     p.add_argument("--cryptographic-hashes", action="store_true")
     p.add_argument("--debug-invariants", action="store_true")
+    p.add_argument("--debug-poison-pages", action="store_true",
+                   help="fill cache pages with NaN whenever they change hands")
     p.add_argument("--seed", type=int, default=0)
     return p
 
@@ -89,7 +91,8 @@ def main(argv: list[str] | None = None) -> int:
         aging_tokens_per_s=args.aging_tokens_per_s, max_wait_s=args.max_wait_s,
         scan_limit=args.scan_limit, prefix_caching=not args.no_prefix_caching,
         cuda_graphs=not args.no_cuda_graphs, lookahead=not args.no_lookahead, cryptographic_hashes=args.cryptographic_hashes,
-        debug_invariants=args.debug_invariants, seed=args.seed)
+        debug_invariants=args.debug_invariants, debug_poison_pages=args.debug_poison_pages,
+        seed=args.seed)
     if args.num_blocks < 0:
         from .engine.runner import kv_bytes_per_token_of
 

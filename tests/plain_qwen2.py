@@ -7,7 +7,9 @@ Each function cites the file and line of RishDevs/mercury whose formula it resta
 
 The arithmetic runs in `dtype` (float64 by default, so that the oracle's own rounding is
 far below what the engine's 32-bit path is held to; `tests/golden/make_golden.py` runs it
-in float32 beside the reference's own CPU model).
+in float32 beside the reference's own CPU model). It runs where its weights are: on the
+CPU by default; the tests of real layer widths hand it float64 weights on the GPU, where the
+same plain PyTorch functions finish a 2048-token sequence in a moment.
 
 Where the reference has no formula (it never reads `sliding_window`), the rule used is
 stated at the function.
@@ -69,7 +71,7 @@ def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Te
 def plain_rope_angles(positions: torch.Tensor, head_dim: int, theta: float) -> torch.Tensor:
     """angle[p, i] = p * theta^(-2i/d), computed in float32 as the reference's table is
     (mercury/model/rope.py:37-45), then handed on in the oracle's dtype."""
-    exponent = torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim
+    exponent = torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim
     inv_freq = 1.0 / (theta ** exponent)
     return torch.outer(positions.to(torch.float32), inv_freq)
 
@@ -108,7 +110,7 @@ def plain_attention(
     tokens, n_q, _ = q.shape
     group = n_q // k.shape[1]
     out = torch.empty_like(q)
-    pos = torch.arange(tokens)
+    pos = torch.arange(tokens, device=q.device)
     hidden = pos[None, :] > pos[:, None]
     if window > 0:
         hidden = hidden | (pos[None, :] <= pos[:, None] - window)
@@ -160,11 +162,13 @@ def plain_layer(h, w, index, cfg, positions):
 
 
 def plain_hidden(raw_config: dict, weights: dict, token_ids, dtype=torch.float64):
-    """Final-norm hidden states [T, H] of one whole sequence."""
+    """Final-norm hidden states [T, H] of one whole sequence, computed on the device the
+    weights lie on (converting them to `dtype` costs nothing if they already are)."""
     cfg = plain_config(raw_config)
     w = {name: t.to(dtype) for name, t in weights.items() if t.is_floating_point()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(ids.numel())
+    device = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(ids.numel(), device=device)
     h = plain_embedding(w["model.embed_tokens.weight"], ids)
     for index in range(cfg["layers"]):
         h = plain_layer(h, w, index, cfg, positions)
@@ -177,6 +181,16 @@ def plain_logits(raw_config: dict, weights: dict, token_ids, dtype=torch.float64
     hidden, w, cfg = plain_hidden(raw_config, weights, token_ids, dtype)
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return hidden @ head.T
+
+
+def plain_logits_at(raw_config: dict, weights: dict, token_ids, rows, dtype=torch.float64):
+    """Logits [len(rows), V] at the positions `rows` only: the whole sequence goes through
+    the layers, the head is applied to the chosen rows (a [T, V] matrix of a real
+    vocabulary would not be worth building)."""
+    hidden, w, cfg = plain_hidden(raw_config, weights, token_ids, dtype)
+    head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
+    index = torch.as_tensor(list(rows), dtype=torch.long, device=hidden.device)
+    return hidden[index] @ head.T
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -68,10 +68,12 @@ def portions(requests: dict[str, list[int]], sizes=(2, 7, 16, 3, 33, 2, 64, 5, 1
 
 
 def mixed(requests: dict[str, list[int]], max_tokens: int, seed: int = 0, max_live: int = 4,
-          tail: int = 32):
+          tail: int = 32, first_portion: int | None = None):
     """Up to `max_live` requests alive, portions of some beside single decoded tokens of
     others, some left out of a step; a new request starts only when the rounded token
-    counts of the live ones leave room in `max_tokens`, so pages get used again."""
+    counts of the live ones leave room in `max_tokens`, so pages get used again. With
+    `first_portion` a request's first entry brings that many tokens and wants the last one
+    only, so that a replay with prefix caching may start it on cached pages."""
     rng = random.Random(seed)
     waiting = list(requests.items())
     live: dict[str, int] = {}
@@ -93,7 +95,10 @@ def mixed(requests: dict[str, list[int]], max_tokens: int, seed: int = 0, max_li
             tokens = requests[rid]
             at = live[rid]
             prompt_end = max(1, len(tokens) - tail)
-            if at < prompt_end:
+            if at == 0 and first_portion:
+                n = min(first_portion, prompt_end)
+                want = [n - 1]
+            elif at < prompt_end:
                 n = min(rng.choice((2, 3, 5, 8, 13, 16, 21, 40)), prompt_end - at)
                 want = list(range(n)) if rng.random() < 0.5 else [n - 1]
             else:

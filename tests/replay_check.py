@@ -13,7 +13,7 @@ import torch
 
 from mercury_b200.trace_run import replay
 from plain_qwen2 import plain_logits
-from tiny import RAW, random_tokens, tiny_model
+from tiny import PAGE_SIZE, RAW, random_tokens, tiny_model
 
 # max |difference| allowed, as a fraction of the largest |logit| of the request.
 # float32: kernels and oracle differ only in the order of float32 sums.
@@ -39,21 +39,56 @@ def requests_for(name: str, lengths: tuple[int, ...]) -> dict:
 
 
 @lru_cache(maxsize=None)
+def requests_with_shared_prefix(name: str, lengths: tuple[int, ...], shared: int) -> dict:
+    """Like `requests_for`, but each request of the second half begins with the first
+    `shared` tokens of its counterpart in the first half (which, in a replay that admits
+    them in order, has finished or is well under way by then)."""
+    requests = {rid: list(tokens) for rid, tokens in requests_for(name, lengths).items()}
+    names = list(requests)
+    half = len(names) // 2
+    for before, rid in zip(names[:half], names[half:]):
+        n = min(shared, len(requests[rid]) - 1, len(requests[before]))
+        requests[rid][:n] = requests[before][:n]
+    return requests
+
+
+def shared_prefix_case(name: str) -> tuple[int, tuple[int, ...], int]:
+    """(shared tokens, request lengths, pool size in tokens) of the shared-prefix replay of
+    a tiny model: two pages and five tokens shared, every request long enough to hold them
+    before its tail, and a pool that holds about half of what the requests need together."""
+    shared = 2 * PAGE_SIZE[name] + 5
+    lengths = tuple(shared + 34 + extra for extra in (3, 40, 17, 58, 9, 26))
+    return shared, lengths, 256 if PAGE_SIZE[name] <= 16 else 512
+
+
+@lru_cache(maxsize=None)
+def oracle_shared(name: str, lengths: tuple[int, ...], shared: int) -> dict:
+    raw, _config, tensors = sharpened_model(name)
+    return {rid: plain_logits(raw, tensors, tokens).numpy()
+            for rid, tokens in requests_with_shared_prefix(name, lengths, shared).items()}
+
+
+@lru_cache(maxsize=None)
 def oracle(name: str, lengths: tuple[int, ...]) -> dict:
     raw, _config, tensors = sharpened_model(name)
     return {rid: plain_logits(raw, tensors, tokens).numpy()
             for rid, tokens in requests_for(name, lengths).items()}
 
 
-def run_and_check(runner, name, lengths, steps, rows, dtype, tolerance=None) -> float:
-    """Replays `steps` on `runner`; returns the worst relative error seen."""
+def run_and_check(runner, name, lengths, steps, rows, dtype, tolerance=None, want=None,
+                  vocab=None, replay_options=None) -> float:
+    """Replays `steps` on `runner`; returns the worst relative error seen. `want` maps a
+    request id to its whole-sequence logits (default: the tiny model `name` through the
+    plain implementation)."""
     tolerance = TOLERANCE[dtype] if tolerance is None else tolerance
-    want = oracle(name, lengths)
-    vocab = RAW[name]["vocab_size"]
+    want = oracle(name, lengths) if want is None else want
+    vocab = RAW[name]["vocab_size"] if vocab is None else vocab
+    scale = {rid: float(np.abs(w).max()) for rid, w in want.items()}
     worst = 0.0
     with tempfile.TemporaryDirectory() as tmp:
         done = []
-        replay(runner, [json.dumps(s) for s in steps], Path(tmp), done.append)
+        replay(runner, [json.dumps(s) for s in steps], Path(tmp), done.append,
+               **(replay_options or {}))
         assert done == [f"done {s['step']}" for s in steps]
         for step, expected in rows.items():
             path = Path(tmp) / f"{step}.f32"
@@ -63,7 +98,7 @@ def run_and_check(runner, name, lengths, steps, rows, dtype, tolerance=None) -> 
             got = np.fromfile(path, dtype="<f4").reshape(len(expected), vocab)
             for row, (rid, pos) in enumerate(expected):
                 ref = want[rid][pos]
-                err = float(np.abs(got[row].astype(np.float64) - ref).max() / np.abs(want[rid]).max())
+                err = float(np.abs(got[row].astype(np.float64) - ref).max() / scale[rid])
                 assert np.isfinite(got[row]).all(), f"step {step} {rid}@{pos}: non-finite logits"
                 assert err <= tolerance, (
                     f"step {step}: request {rid} position {pos}: relative error {err:.3e} "

@@ -44,10 +44,11 @@ def scenario(seed: int):
     return name, prompts, limits, params, arrive, engine_args, eos, aborts
 
 
-def play(lookahead, name, prompts, limits, params, arrive, engine_args, eos, aborts):
+def play(lookahead, name, prompts, limits, params, arrive, engine_args, eos, aborts,
+         factory=make_engine):
     """Requests are submitted (and aborted) at their step numbers; per request its tokens
     and how it ended, and the engine."""
-    engine = make_engine(name, lookahead, **engine_args)
+    engine = factory(name, lookahead, **engine_args)
     engine.eos_ids = set(eos)
     got = {i: {"tokens": [], "index": [], "end": None} for i in range(len(prompts))}
 

@@ -146,6 +146,57 @@ def test_tcgen05_product(twin, m, n, k, tile, out_dtype):
     close(got, want, out_dtype, terms=k)
 
 
+@pytest.mark.parametrize("m", [256, 300, 2048, 2049])
+@pytest.mark.parametrize("k", [896, 1536, 3584])
+@pytest.mark.parametrize("width", [4864, 200], ids=["w4864", "w200"])
+def test_tcgen05_persistent_gated_product(twin, m, k, width):
+    """The persistent kernel with the SiLU gate in its epilogue, called directly at the
+    prompt-step sizes that select it: full and ragged row tiles, one row beyond a tile,
+    widths that are no multiple of its 128-column tiles, three lengths of the sum."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 71)
+    w = rand((2 * width, k), torch.bfloat16, 72, 0.05)
+    got = torch.zeros((m, width), dtype=torch.bfloat16, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.mb_gemm_tcgen05_persistent(x.data_ptr(), w.data_ptr(), None, got.data_ptr(), 2, m, width,
+                                        k, error.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert int(error.item()) == 0, "a bounded wait in the kernel ran out"
+    gate = x.double() @ w[:width].double().T
+    up = x.double() @ w[width:].double().T
+    want = gate * torch.sigmoid(gate) * up
+    # as the separate kernels do, gate and up are rounded to bfloat16 before the gate and the
+    # result once more: three roundings of 2^-9 each at worst
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert err <= 3 * 2.0 ** -8, err
+    # and every element relative to its own size (a swapped half or a stale accumulator
+    # would pass neither)
+    loose = (got.double() - want).abs() <= 2.0 ** -6 * want.abs() + 2e-3 * want.abs().max()
+    assert bool(loose.all())
+
+
+@pytest.mark.parametrize("mode,out_dtype", [(0, torch.bfloat16), (1, torch.float32)], ids=["bf16out", "f32out"])
+@pytest.mark.parametrize("m,n,k", [(256, 1152, 896), (300, 896, 4864), (2049, 200, 1536)])
+def test_tcgen05_persistent_plain_product(twin, m, n, k, mode, out_dtype):
+    """The persistent kernel's plain modes (bias, bfloat16 or float32 out)."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 73)
+    w = rand((n, k), torch.bfloat16, 74, 0.1)
+    bias = rand((n,), torch.bfloat16, 75)
+    got = torch.zeros((m, n), dtype=out_dtype, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.mb_gemm_tcgen05_persistent(x.data_ptr(), w.data_ptr(), bias.data_ptr(), got.data_ptr(), mode,
+                                        m, n, k, error.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and int(error.item()) == 0
+    want = torch.empty_like(got)
+    twin.linear(x, w, bias, want)
+    close(got, want, out_dtype, terms=k)
+
+
 def test_tcgen05_refuses_an_odd_k():
     from mercury_b200.kernels import library
 

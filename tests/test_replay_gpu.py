@@ -1,7 +1,10 @@
 """Replay on the GPU, in 32-bit and in bfloat16: each request whole; most of it in one step
-and the last 32 tokens one by one; portions of changing size down to two tokens; and mixed,
-up to four live requests with so few pages that they are used again. Every written row is
-compared with the plain implementation."""
+and the last 32 tokens one by one; portions of changing size down to two tokens; mixed,
+up to four live requests with so few pages that they are used again; and mixed with
+requests that start on the cached pages of an earlier request's equal prefix. Every written
+row is compared with the plain implementation. Every runner here poisons its pages: a page
+is filled with NaN whenever it changes hands, so a key read from beyond a sequence's length
+or from a page's earlier owner shows as a non-finite logit."""
 
 from __future__ import annotations
 
@@ -17,7 +20,9 @@ import pytest
 import torch
 
 import replay_cases
-from replay_check import TOLERANCE, oracle, requests_for, run_and_check, sharpened_model
+from replay_check import (TOLERANCE, oracle, oracle_shared, requests_for,
+                          requests_with_shared_prefix, run_and_check, shared_prefix_case,
+                          sharpened_model)
 from tiny import PAGE_SIZE, RAW
 
 pytestmark = pytest.mark.gpu
@@ -35,7 +40,8 @@ def make_runner(name, dtype, num_tokens=MAX_TOKENS):
     page = PAGE_SIZE[name]
     return ModelRunner(config=config, tensors=tensors, dtype=dtype, device="cuda", page_size=page,
                        num_pages=num_tokens // page, max_seqs=4, max_step_tokens=num_tokens,
-                       max_model_len=min(num_tokens, RAW[name]["max_position_embeddings"]))
+                       max_model_len=min(num_tokens, RAW[name]["max_position_embeddings"]),
+                       poison_pages=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
@@ -54,6 +60,23 @@ def test_replay_matches_plain(name, dtype, mode):
         steps, rows = replay_cases.mixed(requests, MAX_TOKENS, seed=3)
     runner = make_runner(name, dtype)
     run_and_check(runner, name, lengths, steps, rows, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_replay_on_cached_prefixes(name, dtype):
+    """Mixed replay with prefix caching: the requests of the second half begin with two
+    pages and a bit of a request of the first half and start on its pages, which are still
+    in the pool; positions behind a cached prefix keep their rotation and their logits. The
+    pool is small enough for cached pages to be evicted and written anew."""
+    shared, lengths, pool = shared_prefix_case(name)
+    requests = requests_with_shared_prefix(name, lengths, shared)
+    steps, rows = replay_cases.mixed(requests, pool, seed=4, max_live=2, first_portion=shared + 3)
+    runner = make_runner(name, dtype, pool)
+    run_and_check(runner, name, lengths, steps, rows, dtype,
+                  want=oracle_shared(name, lengths, shared), replay_options={"prefix_caching": True})
+    assert runner.cache.stats["hit_tokens"] >= 2 * PAGE_SIZE[name], "no request started on cached pages"
+    assert sum(p.evictions for p in runner.cache.pools) > 0, "no cached page was ever evicted"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
@@ -91,15 +114,17 @@ def test_weights_stored_in_32_bit_stay_so_in_the_bfloat16_engine():
     page = PAGE_SIZE[name]
     runner = ModelRunner(config=config, tensors=wide, dtype=torch.bfloat16, device="cuda",
                          page_size=page, num_pages=512 // page, max_seqs=4, max_step_tokens=512,
-                         max_model_len=512)
+                         max_model_len=512, poison_pages=True)
     mixer = runner.model.blocks[0].mixer
     assert mixer.qkv_weight.dtype == torch.float32 and runner.model.embedding.table.dtype == torch.float32
     assert next(iter(runner.kv_layers.values()))[0].dtype == torch.bfloat16
     run_and_check(runner, name, lengths, steps, rows, torch.bfloat16)
 
 
+@pytest.mark.parametrize("switches", [(), ("--prefix-caching", "--poison-pages")],
+                         ids=["plain", "prefix+poison"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(dtype, tmp_path):
+def test_trace_run_program(dtype, switches, tmp_path):
     """The program itself, as a user runs it: a model folder, steps on standard input."""
     from mercury_b200.weights import write_random_model
 
@@ -117,7 +142,7 @@ def test_trace_run_program(dtype, tmp_path):
     out = tmp_path / "out"
     done = subprocess.run(
         [str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out",
-         str(out), "--max-tokens", "512", "--block-size", str(PAGE_SIZE[name])],
+         str(out), "--max-tokens", "512", "--block-size", str(PAGE_SIZE[name]), *switches],
         input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
         timeout=600)
     assert done.returncode == 0, done.stderr
