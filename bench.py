@@ -9,13 +9,20 @@ requests whose contexts hold 2048 tokens. One "step" is one decode step of the w
 
 It prints ONE JSON line:
   value      decoded tokens per second, timed on the device with CUDA events over K steps
-             issued back to back (after W warm-up steps);
+             issued back to back (after W warm-up steps); the block of K steps is timed five
+             times and the median block gives `value` and `ms_per_step` (`repeats` holds the
+             minimum, median and maximum);
   e2e        the same through `Engine.step()`: every step copies its inputs from pinned host
              memory, samples on the device and reads the tokens back to the host;
   prefill    one 2048-token prompt in one step: tokens/s, ms, and flops / time / peak;
+             `prefill_512x4` is the same prompt in four portions of 512;
   roofline   for the decode step: bytes it has to read (every weight once, the cache of
              the live requests) / time, against the measured copy bandwidth;
-  points     decode tokens per second at batch 1 and 64.
+  points     decode tokens per second at batch 1 and 64, `point_rooflines` their fractions;
+  kernels    per class of kernel call, for the decode step and for the prompt step: the
+             milliseconds it takes (CUDA events around every call of a step launched eagerly
+             behind a device-side delay, so that the launches queue up), what the model needs
+             of it (bytes to read, or flops) and that over time over the measured peak.
 Weights (about 1 GB) are far larger than the 126 MB L2, so every step streams them from
 HBM again; no extra L2 flush is needed ("l2" in config says so).
 """
@@ -56,7 +63,22 @@ MODEL_LEN = 4096      # benchmark context length: the most a request may reach
 PREFILL_TOKENS = 2048
 BLOCK = 16
 SEED = 0
+REPEATS = 5           # how often the block of K decode steps is timed
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+METRIC = "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2048-token contexts)"
+
+
+def bench_config(peak_kind: str) -> dict:
+    """The `config` of the JSON line: every size of the run, flat; the same for both arms."""
+    c = QWEN25_05B
+    return {"model": "Qwen2.5-0.5B sizes", "layers": c["num_hidden_layers"],
+            "layers_of_model": c["num_hidden_layers"], "hidden": c["hidden_size"],
+            "q_heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+            "head_dim": c["head_dim"], "intermediate": c["intermediate_size"],
+            "vocab": c["vocab_size"], "tied": c["tie_word_embeddings"], "global_batch": BATCH,
+            "seq_len": CONTEXT, "max_model_len": MODEL_LEN, "kv_block": BLOCK,
+            "parallelism": "single GPU", "l2": "inputs>L2 (1 GB of weights streamed per step)",
+            "peaks": peak_kind}
 
 
 def peaks() -> tuple[dict, str]:
@@ -125,6 +147,42 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+def class_costs(cfg: dict, batch: int, context: int, tokens: int) -> dict:
+    """What each class of kernel call has to move or compute: for a decode step of `batch`
+    requests at `context` tokens ("decode": bytes read) and for a prompt step of `tokens`
+    tokens ("prefill": flops, or bytes for the classes that only move data)."""
+    h, i, v, layers = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    n_q, n_kv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    qkv = (n_q + 2 * n_kv) * d
+    kv_layer = 2 * n_kv * d * 2                   # bytes of keys and values per token and layer
+    decode = {
+        "q/k/v product": ("hbm", layers * 2 * (qkv * h + qkv)),
+        "q/k/v + rotary + store": ("hbm", layers * 2 * (qkv * h + qkv)),
+        "attention": ("hbm", layers * batch * context * kv_layer),
+        "residual product": ("hbm", layers * 2 * (n_q * d * h + h * i)),
+        "gated product": ("hbm", layers * 2 * 2 * i * h),
+        "product": ("hbm", 2 * v * h),
+        "norm": ("hbm", 2 * batch * h * 6),
+        "embedding": ("hbm", batch * h * 6),
+        "sampling": ("hbm", batch * v * 4),
+    }
+    t = tokens
+    prefill = {
+        "q/k/v product": ("tensor", layers * 2 * t * qkv * h),
+        "q/k/v + rotary + store": ("tensor", layers * 2 * t * qkv * h),
+        "rotary + store": ("hbm", layers * t * (2 * qkv * 2 + 2 * n_kv * d * 2)),
+        "attention": ("tensor", 2 * t * t * n_q * d * layers),
+        "residual product": ("tensor", layers * 2 * t * (n_q * d * h + h * i)),
+        "gated product": ("tensor", layers * 2 * t * 2 * i * h),
+        "gate": ("hbm", layers * t * 3 * i * 2),
+        "product": ("hbm", 2 * v * h),
+        # every norm reads the float32 stream and a bfloat16 delta, writes both back
+        "norm": ("hbm", (2 * layers + 1) * t * h * (4 + 2 + 4 + 2)),
+        "embedding": ("hbm", t * h * 6),
+    }
+    return {"decode": decode, "prefill": prefill}
+
+
 def model_numbers(cfg: dict) -> dict:
     """Bytes a decode step must read and flops a prefill must do, from the sizes alone."""
     h, i, v, layers = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
@@ -180,8 +238,9 @@ def fill_contexts(torch, runner, batch, context, vocab):
     return seqs
 
 
-def decode_rate(torch, runner, batch, context, vocab, steps, warmup, load_window=None):
-    """(tokens/s, ms per step, launches per step) of `steps` decode steps of `batch`. With
+def decode_rate(torch, runner, batch, context, vocab, steps, warmup, load_window=None, repeats=1):
+    """(tokens/s, ms per step, launches per step, [ms per step of every repeat]) of `steps`
+    decode steps of `batch`, timed `repeats` times in a row (the median repeat counts). With
     `load_window` (a list) the same steps keep running, untimed, until a second has passed
     since the timed region began, and [start, end] of that stretch is appended: the clock
     sampler needs more than the few dozen milliseconds the timed steps take."""
@@ -190,7 +249,7 @@ def decode_rate(torch, runner, batch, context, vocab, steps, warmup, load_window
     seqs = fill_contexts(torch, runner, batch, context, vocab)
     out = torch.empty(batch, dtype=torch.int32, device="cuda")
     gen = torch.Generator().manual_seed(SEED + 2)
-    feed = torch.randint(0, vocab, (steps + warmup + 1, batch), generator=gen).tolist()
+    feed = torch.randint(0, vocab, (steps * repeats + warmup + 1, batch), generator=gen).tolist()
     turn = [0]
 
     def one():
@@ -205,8 +264,9 @@ def decode_rate(torch, runner, batch, context, vocab, steps, warmup, load_window
         one()
     before = runner.launch_count()
     began = time.time()
-    ms = timed(torch, one, steps)
-    launches = (runner.launch_count() - before) / steps
+    samples = [timed(torch, one, steps) for _ in range(repeats)]
+    ms = statistics.median(samples)
+    launches = (runner.launch_count() - before) / (steps * repeats)
     if load_window is not None:
         while time.time() - began < 1.0 and turn[0] < len(feed) - 1 and \
                 seqs[0].num_computed + 2 < runner.max_model_len:
@@ -215,7 +275,58 @@ def decode_rate(torch, runner, batch, context, vocab, steps, warmup, load_window
         load_window.extend([began, time.time()])
     for s in seqs:
         runner.close(s)
-    return batch * 1e3 / ms, ms, launches
+    return batch * 1e3 / ms, ms, launches, samples
+
+
+def kernel_classes(torch, runner, batch, context, vocab, cfg, peak) -> dict:
+    """Milliseconds per class of kernel call of one decode step of `batch` requests and of
+    one prompt step, each launched eagerly with CUDA events around every call; a delay on
+    the device lets the launches queue up first, so that the events see kernels back to
+    back and not the host's launch loop. Beside each: what the model needs of the class
+    (bytes or flops), and that over time over the measured peak."""
+    from mercury_b200.engine.batch import StepEntry
+
+    costs = class_costs(cfg, batch, context, PREFILL_TOKENS)
+    out = {}
+    seqs = fill_contexts(torch, runner, batch, context, vocab)
+    gen = torch.Generator().manual_seed(SEED + 6)
+    tokens = torch.randint(0, vocab, (8, batch), generator=gen).tolist()
+    prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+    sampled = torch.empty(batch, dtype=torch.int32, device="cuda")
+    runner.time_kernels = True
+    try:
+        rows = []
+        for turn in range(4):                      # the first two are warm-up
+            torch.cuda._sleep(20_000_000)          # about 10 ms: the step's launches queue up behind it
+            logits = runner.step([StepEntry(s, [tokens[turn][i]], [0]) for i, s in enumerate(seqs)])
+            rows.append(dict(runner.last_kernel_ms))
+        decode = {k: statistics.median(r.get(k, 0.0) for r in rows[2:]) for k in rows[-1]}
+        torch.cuda._sleep(20_000_000)
+        runner.ops.begin_timing()
+        runner.ops.argmax(logits, sampled)
+        decode["sampling"] = runner.ops.end_timing().get("sampling", 0.0)
+        for s in seqs:
+            runner.close(s)
+        rows = []
+        for turn in range(3):
+            seq = runner.open(f"classes-{turn}")
+            torch.cuda._sleep(40_000_000)
+            runner.step([StepEntry(seq, prompt, [PREFILL_TOKENS - 1])])
+            rows.append(dict(runner.last_kernel_ms))
+            runner.close(seq)
+        prefill = {k: statistics.median(r.get(k, 0.0) for r in rows[1:]) for k in rows[-1]}
+    finally:
+        runner.time_kernels = False
+    for name, measured in (("decode", decode), ("prefill", prefill)):
+        block = {}
+        for kind, ms in sorted(measured.items()):
+            bound, amount = costs[name].get(kind, ("hbm", 0))
+            top = peak["hbm_gbs"] * 1e9 if bound == "hbm" else peak["bf16_tflops"] * 1e12
+            block[kind] = {"ms": round(ms, 4), "bound": bound,
+                           "frac": round(amount / (ms * 1e-3) / top, 4) if ms > 0 and amount else None}
+        block["sum_ms"] = round(sum(measured.values()), 4)
+        out[name] = block
+    return out
 
 
 def prefill_rate(torch, runner, vocab, reps=5):
@@ -227,6 +338,28 @@ def prefill_rate(torch, runner, vocab, reps=5):
     for rep in range(reps + 2):
         seq = runner.open(f"prefill-{rep}")
         ms = timed(torch, lambda: runner.step([StepEntry(seq, tokens, [PREFILL_TOKENS - 1])]), 1)
+        runner.close(seq)
+        if rep >= 2:
+            times.append(ms)
+    return statistics.median(times)
+
+
+def prefill_portions_rate(torch, runner, vocab, portion=512, reps=5):
+    """The 2048-token prompt as portions of `portion` tokens, one step each; ms for all."""
+    from mercury_b200.engine.batch import StepEntry
+
+    gen = torch.Generator().manual_seed(SEED + 3)
+    tokens = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+    times = []
+
+    def run(seq):
+        for at in range(0, PREFILL_TOKENS, portion):
+            last = at + portion >= PREFILL_TOKENS
+            runner.step([StepEntry(seq, tokens[at:at + portion], [portion - 1] if last else [])])
+
+    for rep in range(reps + 2):
+        seq = runner.open(f"portions-{rep}")
+        ms = timed(torch, lambda: run(seq), 1)
         runner.close(seq)
         if rep >= 2:
             times.append(ms)
@@ -287,41 +420,51 @@ def run_ours(args) -> dict:
     sampler.start()
     runner = make_runner(torch, config, tensors, 64, 64 * (CONTEXT + 256))
     window: list[float] = []
-    value, ms, launches = decode_rate(torch, runner, BATCH, CONTEXT, vocab, args.steps, args.warmup,
-                                      load_window=window)
+    value, ms, launches, samples = decode_rate(torch, runner, BATCH, CONTEXT, vocab, args.steps,
+                                               args.warmup, load_window=window, repeats=REPEATS)
     clocks = sampler.stop(tuple(window))
-    b1, _, _ = decode_rate(torch, runner, 1, CONTEXT, vocab, args.steps, args.warmup)
-    b64, _, _ = decode_rate(torch, runner, 64, CONTEXT, vocab, args.steps, args.warmup)
+    b1, ms1, _, _ = decode_rate(torch, runner, 1, CONTEXT, vocab, args.steps, args.warmup, repeats=3)
+    b64, ms64, _, _ = decode_rate(torch, runner, 64, CONTEXT, vocab, args.steps, args.warmup, repeats=3)
     prefill_ms = prefill_rate(torch, runner, vocab)
+    portions_ms = prefill_portions_rate(torch, runner, vocab)
+    kernels = kernel_classes(torch, runner, BATCH, CONTEXT, vocab, QWEN25_05B, peak)
     del runner
     torch.cuda.empty_cache()
     e2e, h2d, d2h = e2e_rate(torch, config, tensors, BATCH, CONTEXT, vocab, args.steps, args.warmup)
 
-    step_bytes = numbers["weight_bytes"] + BATCH * (CONTEXT + args.warmup + args.steps // 2) * numbers["kv_bytes_per_token"]
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    def step_bytes(batch, steps_before):
+        return numbers["weight_bytes"] + batch * (CONTEXT + steps_before) * numbers["kv_bytes_per_token"]
+
+    def fraction(batch, step_ms, steps_before):
+        return round(step_bytes(batch, steps_before) / (step_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
+
+    middle = args.warmup + REPEATS * args.steps // 2
+    achieved = step_bytes(BATCH, middle) / (ms * 1e-3) / 1e9
     flops = (PREFILL_TOKENS * numbers["gemm_flops_per_token"] + numbers["attn_flops"](PREFILL_TOKENS)
              + numbers["head_flops_per_row"])
     return {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2048-token contexts)",
+        "metric": METRIC,
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random N(0,0.02) weights",
-        "config": {"model": "Qwen2.5-0.5B sizes", "layers": 24, "layers_of_model": 24, "hidden": 896,
-                   "q_heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864,
-                   "vocab": 151936, "tied": True, "global_batch": BATCH, "seq_len": CONTEXT,
-                   "max_model_len": MODEL_LEN, "kv_block": BLOCK, "parallelism": "single GPU",
-                   "l2": "inputs>L2 (1 GB of weights streamed per step)",
-                   "peaks": peak_kind},
+        "config": bench_config(peak_kind),
+        "repeats": {"n": REPEATS, "ms_min": round(min(samples), 4),
+                    "ms_median": round(statistics.median(samples), 4), "ms_max": round(max(samples), 4)},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * args.steps)),
         "prefill": {"value": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "prefill_512x4": {"value": round(PREFILL_TOKENS * 1e3 / portions_ms, 1),
+                          "tokens": PREFILL_TOKENS, "ms": round(portions_ms, 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)},
+        "point_rooflines": {"decode_b1": {"ms": round(ms1, 4), "frac": fraction(1, ms1, args.warmup + 3 * args.steps // 2)},
+                            "decode_b64": {"ms": round(ms64, 4), "frac": fraction(64, ms64, args.warmup + 3 * args.steps // 2)}},
+        "kernels": kernels,
         "clocks": clocks,
     }
 
@@ -363,7 +506,10 @@ def run_part(args) -> dict:
                          graphs=not args.no_graphs, gemm=args.gemm)
     if args.only == "prefill":
         return {"prefill_ms": round(prefill_rate(torch, runner, vocab, reps=args.steps), 3)}
-    rate, ms, launches = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps, args.warmup)
+    if args.only == "kernels":
+        return kernel_classes(torch, runner, batch, CONTEXT, vocab, raw, peaks()[0])
+    rate, ms, launches, _samples = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps,
+                                               args.warmup)
     return {"decode_tokens_per_s": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch,
             "launches_per_step": launches, "graphs": not args.no_graphs}
 
@@ -472,13 +618,20 @@ def _time_reference(args, torch, config_from_dict, write_random_model, RefConfig
         seconds = time.perf_counter() - t0
         clocks = sampler.stop()
         tokens = sum(1 for kind in produced[before:] if kind == "token")
-    return {"impl": "reference", "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, 2048-token contexts)",
-            "value": round(tokens / seconds, 1), "unit": "tokens/s", "n_gpus": 1,
+    rate = round(tokens / seconds, 1)
+    return {"impl": "reference", "metric": METRIC,
+            "value": rate, "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(1e3 * seconds / args.steps, 4), "higher_is_better": True,
-            "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random weights",
-            "config": {"model": "Qwen2.5-0.5B sizes", "global_batch": BATCH, "seq_len": CONTEXT,
-                       "kv_block": BLOCK, "timing": "wall clock around Engine.step, host tokens in and out"},
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random N(0,0.02) weights",
+            "config": bench_config(peaks()[1]),
+            # the reference has no device-timed number: its only clock is the wall clock around
+            # its own Engine.step, host tokens in and out, which is an end-to-end number by
+            # nature; the bytes it copies per step are its own business and not counted here
+            "timing": "wall clock around Engine.step, host tokens in and out",
+            "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": None,
+                    "d2h_bytes_per_step": None},
             "clocks": clocks}
 
 
@@ -488,7 +641,8 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=64)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="mercury_b200", choices=("mercury_b200", "reference"))
-    p.add_argument("--only", default="all", choices=("all", "decode", "prefill", "products", "mixed"),
+    p.add_argument("--only", default="all",
+                   choices=("all", "decode", "prefill", "products", "mixed", "kernels"),
                    help="run one part only (for profilers and side workloads); prints its own JSON")
     p.add_argument("--size", default=None, choices=tuple(SIZES),
                    help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")

@@ -8,7 +8,9 @@ does not: `max_batched_tokens` (tokens of one step, decode tokens included) and
 `prefill_chunk` (most tokens of one prompt in one step). `cuda_graphs` replays decode-only
 steps from captured graphs. `prefix_caching` switches the hash lookup at admission.
 `lookahead` lets the engine launch a step before it has read the tokens of the step in front.
-`debug_poison_pages` fills cache pages with NaN whenever they change hands.
+`debug_poison_pages` fills cache pages with NaN whenever they change hands. `time_kernels`
+runs every step eagerly with CUDA events around each class of kernel call and books the
+milliseconds in the step records (for looking at a step, not for serving).
 """
 
 from __future__ import annotations
@@ -63,6 +65,7 @@ class EngineConfig:
     seed: int = 0
     debug_invariants: bool = False
     debug_poison_pages: bool = False
+    time_kernels: bool = False
     max_step_records: int = 500_000
 
     def __post_init__(self) -> None:

@@ -152,7 +152,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
             const int j = idx / CH, c = idx - j * CH;
             const int key = kt * MMA_BN + j;
             int page = -1;
-            if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+            if (key < kv_len) page = table_page(table, seq, max_pages, key / page_size);
             const bool valid = page >= 0;
             const int64_t at =
                 valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D + c * 8 : 0;
@@ -350,7 +350,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
             for (int kt = lo; kt < hi; ++kt) {
                 const int key = kt * MMA_BN + (threadIdx.x >> 1);
                 if (key >= kv_len_) continue;
-                const int page = table[(int64_t)seq_ * max_pages + key / page_size];
+                const int page = table_page(table, seq_, max_pages, key / page_size);
                 if (page < 0) continue;
                 const int64_t at = (((int64_t)page * n_kv + kvh_) * page_size + (key % page_size)) * D;
                 for (int b = 0; b < D * 2; b += 128) {
@@ -413,7 +413,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
     auto load_tile = [&](int stage, int kt) {
         const int key = kt * MMA_BN + lj;
         int page = -1;
-        if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+        if (key < kv_len) page = table_page(table, seq, max_pages, key / page_size);
         const bool valid = page >= 0;
         const int64_t at =
             valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
@@ -720,7 +720,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
-            page = table[(int64_t)seq * max_pages + key / page_size];
+            page = table_page(table, seq, max_pages, key / page_size);
         const bool valid = page >= 0;
         const int64_t at =
             valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
@@ -754,7 +754,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         new_c = new_idx - new_tok * HC;
         const int key = first_pos + new_tok, kt = key / MMA_BN;
         new_mine = kt >= t_lo && kt < t_hi;
-        if (new_mine && store) new_page = table[(int64_t)seq * max_pages + key / page_size];
+        if (new_mine && store) new_page = table_page(table, seq, max_pages, key / page_size);
     }
     grid_dependency_sync();
 
@@ -783,6 +783,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             lo = *reinterpret_cast<const uint4*>(head + c * 8);
             hi = *reinterpret_cast<const uint4*>(head + D / 2 + c * 8);
             if (!rotate) return;
+            pos_of = checked_position(pos_of);
             const float4* cs = reinterpret_cast<const float4*>(cos_t + (int64_t)pos_of * (D / 2) + c * 8);
             const float4* sn = reinterpret_cast<const float4*>(sin_t + (int64_t)pos_of * (D / 2) + c * 8);
             const float4 c0 = cs[0], c1 = cs[1], s0 = sn[0], s1 = sn[1];

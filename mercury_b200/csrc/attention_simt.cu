@@ -105,7 +105,7 @@ paged_attention_kernel(const T* __restrict__ qkv, int q_row_stride, const T* __r
         if (tid < ATT_KEYS) {
             const int key = kt * ATT_KEYS + tid;
             int page = -1;
-            if (key < kv_len) page = table[(int64_t)seq * max_pages + key / page_size];
+            if (key < kv_len) page = table_page(table, seq, max_pages, key / page_size);
             page_s[tid] = page;
         }
         __syncthreads();

@@ -167,7 +167,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             if (lane < copies) {
                 const int key0 = kt * TA_KEYS + lane * box;
                 if (key0 < kv_len) {
-                    page = table[(int64_t)seq * max_pages + key0 / page_size];
+                    page = table_page(table, seq, max_pages, key0 / page_size);
                     row = (page * n_kv + kvh) * page_size + key0 % page_size;
                 }
             }

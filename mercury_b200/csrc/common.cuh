@@ -85,6 +85,62 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// ---- the checked build ---------------------------------------------------------------
+// Compiled with -DMB_BOUNDS_CHECK (kernels/build.py: build(bounds_check=True); selected at
+// run time by MERCURY_B200_BOUNDS_CHECK=1) every index that a kernel takes from the step's
+// device buffers is compared with its limit before it is used: block-table columns, page
+// numbers, positions (rows of the rotation tables), token ids. A bad index is recorded in a
+// status word (the first one wins; a counter keeps the total), the access is skipped as if
+// the page had been given back, and the kernel goes on: no trap, the context stays usable.
+// The host sets the limits with mb_check_set_limits and reads the word with mb_check_read.
+// In the ordinary build all of this compiles to the plain loads.
+#ifdef MB_BOUNDS_CHECK
+extern __device__ int mb_check_limit[4];   // [0] pages of the pool, [1] rows of the rotation tables
+extern __device__ int mb_check_word[4];    // [0] kind of the first bad index, [1] its value, [2] the limit, [3] how many
+__device__ __forceinline__ void check_report(int kind, int value, int limit) {
+    if (atomicCAS(&mb_check_word[0], 0, kind) == 0) {
+        mb_check_word[1] = value;
+        mb_check_word[2] = limit;
+    }
+    atomicAdd(&mb_check_word[3], 1);
+}
+#endif
+#define MB_CHECK_PAGE 1       // a page number beyond the pool
+#define MB_CHECK_COLUMN 2     // a block-table column beyond the table's width
+#define MB_CHECK_POSITION 3   // a position beyond the rotation tables
+#define MB_CHECK_TOKEN 4      // a token id outside the vocabulary
+#define MB_CHECK_SEQUENCE 5   // a sequence number beyond the batch
+
+// The page of block-table column `column` of sequence `seq` (-1: given back, or refused).
+__device__ __forceinline__ int table_page(const int* __restrict__ table, int seq, int max_pages,
+                                          int column) {
+#ifdef MB_BOUNDS_CHECK
+    if (column < 0 || column >= max_pages) {
+        check_report(MB_CHECK_COLUMN, column, max_pages);
+        return -1;
+    }
+    const int page = table[(int64_t)seq * max_pages + column];
+    if (page >= mb_check_limit[0] && mb_check_limit[0] > 0) {
+        check_report(MB_CHECK_PAGE, page, mb_check_limit[0]);
+        return -1;
+    }
+    return page;
+#else
+    return table[(int64_t)seq * max_pages + column];
+#endif
+}
+
+// A position that indexes the rotation tables (0 when refused).
+__device__ __forceinline__ int checked_position(int pos) {
+#ifdef MB_BOUNDS_CHECK
+    if (pos < 0 || (mb_check_limit[1] > 0 && pos >= mb_check_limit[1])) {
+        check_report(MB_CHECK_POSITION, pos, mb_check_limit[1]);
+        return 0;
+    }
+#endif
+    return pos;
+}
+
 // defined in attention_simt.cu
 int launch_attention_combine(const float* part_acc, const float* part_ml, const int* seq_of_token,
                              void* out, int tokens, int n_q, int d, int num_splits, int dtype,

@@ -16,6 +16,9 @@ __global__ void embed_kernel(const int* __restrict__ ids, const void* __restrict
     const int t = blockIdx.x;
     int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
+#ifdef MB_BOUNDS_CHECK
+    if (!ok && threadIdx.x == 0) check_report(MB_CHECK_TOKEN, id, vocab);
+#endif
     const int64_t base = (int64_t)(ok ? id : 0) * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x)
         out[(int64_t)t * hidden + c] = ok ? load_as_float(table, base + c, table_dtype) : 0.f;
@@ -101,12 +104,12 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
     const int t = blockIdx.x;
     const int seq = seq_of_token[t];
     if (seq < 0) return;
-    const int pos = positions[t];
+    const int pos = checked_position(positions[t]);
     const int half = rot / 2;
     const int64_t row = (int64_t)t * (n_q + 2 * n_kv) * d;
     int64_t slot = -1;
     if (store) {
-        const int page = table[(int64_t)seq * max_pages + pos / page_size];
+        const int page = table_page(table, seq, max_pages, pos / page_size);
         if (page >= 0) slot = (int64_t)page * n_kv * page_size + pos % page_size;
     }
     // rotated heads: q and k. One work item = one (head, pair or pass-through feature).
@@ -307,12 +310,12 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
     const int t = (int)(item / ((int64_t)runs * heads));
     const int seq = seq_of_token[t];
     if (seq < 0) return;
-    const int pos = positions[t];
+    const int pos = checked_position(positions[t]);
     const int i = run * 8;
     __nv_bfloat16* x = qkv + (int64_t)t * heads * d + (int64_t)head * d;
     __nv_bfloat16* dst = nullptr;
     if (head >= n_q && store) {
-        const int page = table[(int64_t)seq * max_pages + pos / page_size];
+        const int page = table_page(table, seq, max_pages, pos / page_size);
         if (page >= 0) {
             const bool is_k = head < n_q + n_kv;
             const int kvh = is_k ? head - n_q : head - n_q - n_kv;
@@ -361,12 +364,59 @@ __global__ void rope_store_bf16_kernel(__nv_bfloat16* __restrict__ qkv,
 
 namespace mb {
 int g_dependent_launch = 0;
+#ifdef MB_BOUNDS_CHECK
+__device__ int mb_check_limit[4] = {0, 0, 0, 0};
+__device__ int mb_check_word[4] = {0, 0, 0, 0};
+#endif
 }
 
 using namespace mb;
 
 // 1: launch every kernel with the programmatic-serialization attribute (see common.cuh).
 MB_EXPORT void mb_set_dependent_launch(int enabled) { g_dependent_launch = enabled ? 1 : 0; }
+
+// 1 if this library is the checked build (see common.cuh), else 0.
+MB_EXPORT int mb_check_enabled() {
+#ifdef MB_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+// Checked build: the limits that indices are compared with from now on (pages of the pool
+// whose tables the next kernels read, rows of the rotation tables; 0 = not checked). Ordered
+// with the kernels of `stream`. A no-op in the ordinary build.
+MB_EXPORT int mb_check_set_limits(int pages, int positions, void* stream) {
+#ifdef MB_BOUNDS_CHECK
+    const int limits[4] = {pages, positions, 0, 0};
+    if (cudaMemcpyToSymbolAsync(mb_check_limit, limits, sizeof(limits), 0, cudaMemcpyHostToDevice,
+                                (cudaStream_t)stream) != cudaSuccess)
+        return MB_ERR_LAUNCH;
+#else
+    (void)pages, (void)positions, (void)stream;
+#endif
+    return MB_OK;
+}
+
+// Checked build: copies the status word (kind, value, limit, count) to `out` (4 ints on the
+// host) after everything on `stream` has run, and clears it. Zeros in the ordinary build.
+MB_EXPORT int mb_check_read(int* out, void* stream) {
+    out[0] = out[1] = out[2] = out[3] = 0;
+#ifdef MB_BOUNDS_CHECK
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemcpyFromSymbolAsync(out, mb_check_word, 4 * sizeof(int), 0, cudaMemcpyDeviceToHost, s) !=
+            cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return MB_ERR_LAUNCH;
+    const int zeros[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbolAsync(mb_check_word, zeros, sizeof(zeros), 0, cudaMemcpyHostToDevice, s) !=
+        cudaSuccess)
+        return MB_ERR_LAUNCH;
+#else
+    (void)stream;
+#endif
+    return MB_OK;
+}
 
 MB_EXPORT int mb_embed(const int* ids, const void* table, int table_dtype, float* out, int tokens,
                        int hidden, int vocab, void* stream) {

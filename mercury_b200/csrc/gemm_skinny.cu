@@ -602,8 +602,8 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         if (tok < T) {
             const int seq = seq_of_token[tok];
             if (seq >= 0) {
-                pos = positions[tok];
-                page = (store && head >= n_q) ? table[(int64_t)seq * max_pages + pos / page_size] : -1;
+                pos = checked_position(positions[tok]);
+                page = (store && head >= n_q) ? table_page(table, seq, max_pages, pos / page_size) : -1;
             }
         }
         tok_pos[tok] = pos;
@@ -615,7 +615,7 @@ __global__ void __launch_bounds__(NORM ? 512 : 1024) skinny_qkv_rope_kernel(Skin
         for (int idx = threadIdx.x; idx < TOK * (D / 2); idx += blockDim.x) {
             const int i = idx % (D / 2), tok = idx / (D / 2);
             int pos = 0;
-            if (tok < T && seq_of_token[tok] >= 0) pos = positions[tok];
+            if (tok < T && seq_of_token[tok] >= 0) pos = checked_position(positions[tok]);
             cos_s[tok][i] = cos_t[(int64_t)pos * (D / 2) + i];
             sin_s[tok][i] = sin_t[(int64_t)pos * (D / 2) + i];
         }

@@ -24,7 +24,9 @@ template <bool OUT_F32, int TC_BN, int TC_STAGES>
 __global__ void __launch_bounds__(128)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __nv_bfloat16* __restrict__ bias, void* __restrict__ out, int M, int N,
-                    int K, int* __restrict__ error) {
+                    int K, int* __restrict__ error, long long wait_limit, int withheld_kb) {
+    // wait_limit: SM clocks after which a wait gives up. withheld_kb: -1, or (to try the
+    // giving-up path) the k-block whose bytes are announced to the barrier and never sent.
     grid_dependency_sync();
     constexpr int TC_STAGE_BYTES = (TC_BM + TC_BN) * TC_BK * 2;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -65,18 +67,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < k_blocks; ++kb) {
             const int s = kb % TC_STAGES;
             const uint32_t phase = (kb / TC_STAGES) & 1;
-            if (!mbar_wait(&empty_bar[s], phase ^ 1, error, 1)) break;
+            if (!mbar_wait(&empty_bar[s], phase ^ 1, error, 1, wait_limit)) break;
             unsigned char* a_tile = tiles + s * TC_STAGE_BYTES;
             unsigned char* b_tile = a_tile + TC_BM * TC_BK * 2;
             mbar_expect_tx(&full_bar[s], TC_STAGE_BYTES);
-            tma_load_2d(a_tile, &map_x, kb * TC_BK, m0, &full_bar[s]);
-            tma_load_2d(b_tile, &map_w, kb * TC_BK, n0, &full_bar[s]);
+            if (kb != withheld_kb) {
+                tma_load_2d(a_tile, &map_x, kb * TC_BK, m0, &full_bar[s]);
+                tma_load_2d(b_tile, &map_w, kb * TC_BK, n0, &full_bar[s]);
+            }
             issued = kb + 1;
         }
         // if the consumer gave up, still wait (bounded) for what was issued and not consumed
         if (*reinterpret_cast<volatile int*>(error) != 0) {
             for (int kb = issued > TC_STAGES ? issued - TC_STAGES : 0; kb < issued; ++kb)
-                mbar_wait(&full_bar[kb % TC_STAGES], (kb / TC_STAGES) & 1, error, 4);
+                mbar_wait(&full_bar[kb % TC_STAGES], (kb / TC_STAGES) & 1, error, 4, wait_limit);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
@@ -85,7 +89,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < k_blocks && ok; ++kb) {
             const int s = kb % TC_STAGES;
             const uint32_t phase = (kb / TC_STAGES) & 1;
-            ok = mbar_wait(&full_bar[s], phase, error, 2);
+            ok = mbar_wait(&full_bar[s], phase, error, 2, wait_limit);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned char* a_tile = tiles + s * TC_STAGE_BYTES;
@@ -104,7 +108,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     // ---- epilogue: all four warps, warp w owns accumulator lanes (rows) 32w .. 32w+31
     __syncwarp();
-    const bool ready = mbar_wait(&accum_bar, 0, error, 3);
+    const bool ready = mbar_wait(&accum_bar, 0, error, 3, wait_limit);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int m = m0 + warp * 32 + lane;
     // tcgen05.ld is warp-wide: take the decision for the whole warp
@@ -399,7 +403,8 @@ MB_EXPORT int mb_gemm_tcgen05_supports(int M, int N, int K) {
 
 template <bool OUT_F32, int BN, int STAGES>
 static int launch_tcgen05(const void* x, const void* w, const void* bias, void* out, int M, int N,
-                          int K, int* error, cudaStream_t s) {
+                          int K, int* error, cudaStream_t s, long long wait_limit = TC_WAIT_CYCLES,
+                          int withheld_kb = -1) {
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, x, M, K, TC_BM) || !make_map(&map_w, w, N, K, BN)) return MB_ERR_LAUNCH;
     const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024;
@@ -413,8 +418,23 @@ static int launch_tcgen05(const void* x, const void* w, const void* bias, void* 
     dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
     if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     MB_LAUNCH((gemm_tcgen05_kernel<OUT_F32, BN, STAGES>), grid, 128, smem, s, map_x, map_w,
-              (const __nv_bfloat16*)bias, out, M, N, K, error);
+              (const __nv_bfloat16*)bias, out, M, N, K, error, wait_limit, withheld_kb);
     return launch_status();
+}
+
+// The giving-up path of the bounded waits, run on purpose: the product as mb_gemm_tcgen05
+// computes it (128 x 128 tiles, bfloat16 out), except that the bytes of k-block 0 are
+// announced to their barrier and never sent, and every wait gives up after `wait_cycles` SM
+// clocks instead of about a second. Each block's MMA issuer runs out of patience, sets
+// `error`, the other roles see it or run out themselves, copies in flight are waited for,
+// tensor memory is freed, and the kernel returns: `out` is left as it was and the context
+// stays usable. For tests of that path only.
+MB_EXPORT int mb_gemm_tcgen05_withheld(const void* x, const void* w, void* out, int M, int N, int K,
+                                       int* error, long long wait_cycles, void* stream) {
+    if (!mb_gemm_tcgen05_supports(M, N, K) || wait_cycles <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return MB_ERR_ALIGNMENT;
+    return launch_tcgen05<false, 128, 3>(x, w, nullptr, out, M, N, K, error, (cudaStream_t)stream,
+                                         wait_cycles, 0);
 }
 
 // x: [M, K], w: [N, K], bias: [N] or null, all bfloat16; out: [M, N] bfloat16 (out_f32 = 0)

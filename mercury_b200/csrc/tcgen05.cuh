@@ -31,7 +31,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait for the phase with the given parity; false (and the error word set) if it
 // never came. try_wait itself suspends the thread for a while when the phase is not there
 // yet (a suspend-time hint changed nothing measurable); the clock is read only now and then.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error, int code,
+                                          long long limit = TC_WAIT_CYCLES) {
     const uint32_t addr = smem_u32(bar);
     long long start = 0;
     for (int round = 0;; ++round) {
@@ -50,7 +51,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
             if (done) return true;
         }
         if (round == 0) start = clock64();
-        else if (clock64() - start > TC_WAIT_CYCLES) break;
+        else if (clock64() - start > limit) break;
     }
     atomicExch(error, code);
     return false;

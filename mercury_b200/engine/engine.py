@@ -60,6 +60,8 @@ class _Flight:
     sampling: list[Request] = field(default_factory=list)
     handle: tuple[int, int] | None = None
     t_start: float = 0.0
+    prepare_s: float = 0.0
+    kernel_ms: dict | None = None
 
 
 class Engine:
@@ -74,6 +76,8 @@ class Engine:
                 max_step_tokens=cfg.max_batched_tokens, max_model_len=cfg.max_model_len, ops=ops,
                 cuda_graphs=cfg.cuda_graphs, poison_pages=cfg.debug_poison_pages)
         self.runner = runner
+        if cfg.time_kernels:
+            runner.time_kernels = True
         cfg.validate_against(runner.spec.max_positions)
         self.cache = runner.cache
         # a request skips the tokens of a cached prefix in every layer or in none, so one
@@ -256,7 +260,9 @@ class Engine:
             self.tap(sampling, logits)
         if sampling:
             handle = self.sampler.begin(logits, [(r.params, r.seed, len(r.out)) for r in sampling])
-        return _Flight(plan, sampling, handle, t_start)
+        kernel_ms = dict(self.runner.last_kernel_ms) if getattr(self.runner, "time_kernels", False) else None
+        return _Flight(plan, sampling, handle, t_start, getattr(self.runner, "last_prepare_s", 0.0),
+                       kernel_ms)
 
     def _complete(self, flight: _Flight) -> StepRecord:
         """Wait for the step's tokens and route them."""
@@ -276,7 +282,7 @@ class Engine:
             num_tokens=plan.num_tokens, sched_s=plan.sched_seconds,
             step_s=time.perf_counter() - flight.t_start, waiting=len(self.sched.waiting),
             running=len(self.sched.running), free_pages=min(self.cache.num_available()),
-            preempted=len(plan.preempted))
+            preempted=len(plan.preempted), prepare_s=flight.prepare_s, kernel_ms=flight.kernel_ms)
         self.metrics.add_step(record)
         return record
 

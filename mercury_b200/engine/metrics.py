@@ -18,6 +18,8 @@ class StepRecord:
     running: int
     free_pages: int
     preempted: int
+    prepare_s: float = 0.0            # host: pages, batch buffer, copy to the device
+    kernel_ms: dict | None = None     # per class of kernel call, when the runner times them
 
 
 def request_record(r) -> dict:
@@ -70,7 +72,13 @@ class EngineMetrics:
         step_s = [s.step_s for s in self.steps]
         sched_s = [s.sched_s for s in self.steps]
         total = sum(step_s) or 1e-9
+        kernels: dict[str, float] = {}
+        for s in self.steps:
+            for kind, ms in (s.kernel_ms or {}).items():
+                kernels[kind] = kernels.get(kind, 0.0) + ms
         return {**self.counters, "wall_seconds": sum(step_s),
+                "prepare_share": sum(s.prepare_s for s in self.steps) / total,
+                **({"kernel_ms": {k: round(v, 3) for k, v in sorted(kernels.items())}} if kernels else {}),
                 "mean_step_ms": 1e3 * total / max(1, len(step_s)),
                 "p50_step_ms": 1e3 * percentile(step_s, 0.5),
                 "p99_step_ms": 1e3 * percentile(step_s, 0.99),

@@ -11,6 +11,7 @@ pass takes prompt portions and decode tokens together and sampling is a separate
 
 from __future__ import annotations
 
+import time
 from pathlib import Path
 
 import torch
@@ -147,7 +148,10 @@ class ModelRunner:
         self.ctx = StepContext(ops, self.workspace, page_size, dtype)
         self.steps = 0
         self.max_pages = max_pages
-        self.use_graphs = cuda_graphs and self.device.type == "cuda" and self.model.capturable
+        # (the checked build of the kernels copies its limits from host memory before every
+        # attention call and is read back after every step: it runs without graphs)
+        self.use_graphs = (cuda_graphs and self.device.type == "cuda" and self.model.capturable
+                           and not getattr(ops, "checked", False))
         self._graphs: dict[int, tuple] = {}
         self.dependent_launch_buckets = 16   # largest batch bucket captured with dependent launch
         self.graph_replays = 0
@@ -155,6 +159,12 @@ class ModelRunner:
         self._shape_graphs: dict[tuple, tuple] = {}   # other steps, by the shape of the batch
         self._shape_seen: dict[tuple, int] = {}
         self.max_shape_graphs = 16
+        # opt-in: every step runs eagerly with CUDA events around each kernel-set call, and
+        # `last_kernel_ms` holds the step's milliseconds per class of call (a step so timed
+        # waits for the device; this is for looking at a step, not for serving)
+        self.time_kernels = False
+        self.last_prepare_s = 0.0          # host seconds the last step's preparation took
+        self.last_kernel_ms: dict[str, float] = {}
 
     # ------------------------------------------------------------------ sizes
 
@@ -205,6 +215,7 @@ class ModelRunner:
         """Provide pages for the entries' tokens and put the batch on the device. Token ids
         that an entry marks as `late` are taken on the device from `sampled`, the tokens the
         step before has sampled (and the host may not have read yet)."""
+        started = time.perf_counter()
         for e in entries:
             if not e.tokens:
                 raise ValueError(f"{e.seq.seq_id}: an entry needs at least one token")
@@ -224,6 +235,7 @@ class ModelRunner:
                 raise ValueError("an entry's token is to come from the step before, but its "
                                  "sampled tokens were not given")
             self.ops.patch_tokens(batch.token_ids, batch.token_from, sampled)
+        self.last_prepare_s = time.perf_counter() - started
         return batch
 
     def run(self, batch: StepBatch) -> torch.Tensor | None:
@@ -363,6 +375,17 @@ class ModelRunner:
         each entry's `want` (None if nothing is wanted). The tensor returned is a view of a
         buffer that the next step overwrites. `sampled` (device int32) supplies the token
         ids of entries marked `late`."""
+        timing = self.time_kernels and hasattr(self.ops, "begin_timing")
+        if timing:
+            self.ops.begin_timing()
+            try:
+                batch = self.prepare(entries, sampled)
+                logits = self.run(batch)
+            finally:
+                self.last_kernel_ms = self.ops.end_timing()
+            self.ops.check_errors()
+            self.finish(entries)
+            return logits
         if (self.use_graphs and len(entries) <= self.max_seqs
                 and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries)):
             return self._decode_with_graph(entries, sampled)

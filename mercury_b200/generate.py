@@ -58,6 +58,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--debug-invariants", action="store_true")
     p.add_argument("--debug-poison-pages", action="store_true",
                    help="fill cache pages with NaN whenever they change hands")
+    p.add_argument("--time-kernels", action="store_true",
+                   help="time every class of kernel call with CUDA events (steps run eagerly) "
+                        "and print the sums to stderr")
     p.add_argument("--seed", type=int, default=0)
     return p
 
@@ -92,7 +95,7 @@ def main(argv: list[str] | None = None) -> int:
         scan_limit=args.scan_limit, prefix_caching=not args.no_prefix_caching,
         cuda_graphs=not args.no_cuda_graphs, lookahead=not args.no_lookahead, cryptographic_hashes=args.cryptographic_hashes,
         debug_invariants=args.debug_invariants, debug_poison_pages=args.debug_poison_pages,
-        seed=args.seed)
+        time_kernels=args.time_kernels, seed=args.seed)
     if args.num_blocks < 0:
         from .engine.runner import kv_bytes_per_token_of
 
@@ -113,6 +116,9 @@ def main(argv: list[str] | None = None) -> int:
     outs = engine.generate(prompts, params, args.max_tokens)
     for prompt, out in zip(prompts, outs):
         print(json.dumps({"prompt_tokens": len(prompt), "output_ids": out}), flush=True)
+    if args.time_kernels:
+        print(json.dumps({"kernel_ms": engine.metrics.summary().get("kernel_ms", {})}),
+              file=sys.stderr, flush=True)
     return 0
 
 

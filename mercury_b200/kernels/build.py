@@ -6,6 +6,12 @@ well under a minute. The library lands next to this file (`_lib/`), or, when tha
 cannot be written, under the system's temporary folder; it is rebuilt when a source or a
 flag changes (the file name carries a hash of both). Progress goes to stderr, one line per
 source, because the first call of a fresh checkout has to wait for it.
+
+`build(bounds_check=True)` makes the checked variant (`-DMB_BOUNDS_CHECK`, see
+csrc/common.cuh): every index a kernel takes from the step's device buffers is compared
+with its limit and a bad one is recorded instead of used. It is a library of its own
+(another file name) and is loaded instead of the ordinary one when the environment has
+MERCURY_B200_BOUNDS_CHECK=1. It is the stand-in for a memory checker where none may run.
 """
 
 from __future__ import annotations
@@ -47,12 +53,20 @@ def _sources() -> list[Path]:
     return listed
 
 
-def _fingerprint() -> str:
+# the checked variant shares its status words between the sources: relocatable device code
+CHECK_FLAGS = ["-DMB_BOUNDS_CHECK", "-rdc=true"]
+
+
+def bounds_check_wanted() -> bool:
+    return os.environ.get("MERCURY_B200_BOUNDS_CHECK", "") not in ("", "0")
+
+
+def _fingerprint(bounds_check: bool = False) -> str:
     digest = hashlib.sha256()
-    for path in sorted(CSRC.glob("*.cu*")):
+    for path in sorted(CSRC.glob("*.cu*")) + sorted(CSRC.glob("*.h")):
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
-    digest.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    digest.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + (CHECK_FLAGS if bounds_check else [])).encode())
     return digest.hexdigest()[:16]
 
 
@@ -74,13 +88,15 @@ def _say(message: str) -> None:
     print(f"[mercury_b200] {message}", file=sys.stderr, flush=True)
 
 
-def library_path() -> Path:
-    return _writable_dir() / f"libmercury_b200_{_fingerprint()}.so"
+def library_path(bounds_check: bool = False) -> Path:
+    stem = "libmercury_b200_checked_" if bounds_check else "libmercury_b200_"
+    return _writable_dir() / f"{stem}{_fingerprint(bounds_check)}.so"
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
-    """Build the library if it is not there yet; returns its path."""
-    target = library_path()
+def build(force: bool = False, verbose: bool = True, bounds_check: bool = False) -> Path:
+    """Build the library (or its checked variant) if it is not there yet; returns its path."""
+    target = library_path(bounds_check)
+    extra = CHECK_FLAGS if bounds_check else []
     if target.exists() and not force:
         return target
     nvcc = _nvcc()
@@ -88,11 +104,12 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     work = Path(tempfile.mkdtemp(prefix="mercury_b200_build_", dir=str(out_dir)))
     started = time.time()
     if verbose:
-        _say(f"compiling {len(SOURCES)} CUDA sources for sm_100a with {nvcc} (first call only)")
+        _say(f"compiling {len(SOURCES)} CUDA sources for sm_100a with {nvcc} (first call only"
+             f"{', checked variant' if bounds_check else ''})")
 
     def compile_one(src: Path) -> Path:
         obj = work / (src.stem + ".o")
-        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         t0 = time.time()
         done = subprocess.run(cmd, capture_output=True, text=True)
         if done.returncode != 0:
@@ -113,7 +130,7 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     finally:
         shutil.rmtree(work, ignore_errors=True)
     for stale in out_dir.glob("libmercury_b200_*.so"):
-        if stale != target:
+        if stale != target and ("_checked_" in stale.name) == bounds_check:
             try:
                 stale.unlink()
             except OSError:

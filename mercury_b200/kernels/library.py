@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
-from .build import BuildError, build
+from .build import BuildError, bounds_check_wanted, build
 
 _LIB = None
 
@@ -58,6 +58,8 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mb_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                         c_int, c_void_p],
+    "mb_gemm_tcgen05_withheld": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                 c_longlong, c_void_p],
     "mb_gemm_tcgen05_persistent": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p],
     "mb_paged_attention_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -80,7 +82,7 @@ def load():
     if _LIB is not None:
         return _LIB
     try:
-        path = build()
+        path = build(bounds_check=bounds_check_wanted())
     except BuildError as err:
         raise KernelError(f"the CUDA kernels could not be built: {err}") from err
     lib = ctypes.CDLL(str(path))
@@ -90,6 +92,12 @@ def load():
         fn.restype = c_int
     lib.mb_gemm_tcgen05_supports.argtypes = [c_int, c_int, c_int]
     lib.mb_gemm_tcgen05_supports.restype = c_int
+    lib.mb_check_enabled.argtypes = []
+    lib.mb_check_enabled.restype = c_int
+    lib.mb_check_set_limits.argtypes = [c_int, c_int, c_void_p]
+    lib.mb_check_set_limits.restype = c_int
+    lib.mb_check_read.argtypes = [ctypes.POINTER(c_int), c_void_p]
+    lib.mb_check_read.restype = c_int
     lib.mb_set_dependent_launch.argtypes = [c_int]
     lib.mb_set_dependent_launch.restype = None
     lib.mb_gemm_skinny_supports.argtypes = [c_int, c_int, c_int]

@@ -7,6 +7,9 @@ This is the only kernel set the product has. It needs a CUDA device of compute c
 
 from __future__ import annotations
 
+import contextlib
+import functools
+
 import torch
 
 from . import library
@@ -25,6 +28,29 @@ def _flag(dtype: torch.dtype) -> int:
 
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+def _timed(kind: str):
+    """Marks a kernel-set method as one class of the step's time. While `begin_timing()` is
+    in force the outermost such call is bracketed by CUDA events and booked under `kind`;
+    otherwise the method runs as it is."""
+    def wrap(method):
+        @functools.wraps(method)
+        def run(self, *args, **kwargs):
+            if self._timing is None or self._timing_depth:
+                return method(self, *args, **kwargs)
+            label = self._timing_label or kind
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._timing_depth += 1
+            start.record()
+            try:
+                return method(self, *args, **kwargs)
+            finally:
+                stop.record()
+                self._timing_depth -= 1
+                self._timing.append((label, start, stop))
+        return run
+    return wrap
 
 
 class CudaOps:
@@ -76,6 +102,9 @@ class CudaOps:
         if major != 10:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}x")
         self.lib = library.load()
+        # the checked variant of the library (MERCURY_B200_BOUNDS_CHECK=1): indices are
+        # compared with their limits inside the kernels; see csrc/common.cuh
+        self.checked = bool(self.lib.mb_check_enabled())
         self.lib.mb_gemm_skinny_set_fed_min(self.fed_min_elements)
         # let each kernel be scheduled while its predecessor drains (see csrc/common.cuh)
         self.dependent_launch = bool(dependent_launch)     # True: on every launch, not only in graphs
@@ -99,6 +128,9 @@ class CudaOps:
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
         self._argmax_scratch: torch.Tensor | None = None
+        self._timing: list | None = None      # (kind, start event, stop event) while timing
+        self._timing_depth = 0
+        self._timing_label: str | None = None  # overrides the class of the calls inside `_as`
         self._pinned_stream: int | None = None
         self.launches = 0
         self.library_calls = 0
@@ -129,6 +161,29 @@ class CudaOps:
     def unpin_stream(self) -> None:
         self._pinned_stream = None
 
+    @contextlib.contextmanager
+    def _as(self, label: str):
+        """Calls made inside are booked under `label` instead of their own class."""
+        before, self._timing_label = self._timing_label, label
+        try:
+            yield
+        finally:
+            self._timing_label = before
+
+    def begin_timing(self) -> None:
+        """From now on bracket every kernel-set call with CUDA events (eager steps only: a
+        replayed graph makes no calls)."""
+        self._timing = []
+
+    def end_timing(self) -> dict[str, float]:
+        """Milliseconds per class of call since `begin_timing()`; waits for the device."""
+        events, self._timing = self._timing or [], None
+        torch.cuda.synchronize(self.device)
+        out: dict[str, float] = {}
+        for kind, start, stop in events:
+            out[kind] = out.get(kind, 0.0) + start.elapsed_time(stop)
+        return out
+
     def _scratch_for(self, floats: int) -> torch.Tensor:
         if self._scratch is None or self._scratch.numel() < floats:
             if self._scratch is not None:
@@ -154,6 +209,7 @@ class CudaOps:
 
     # ------------------------------------------------------------------ kernels
 
+    @_timed("embedding")
     def embed(self, token_ids, table, out):
         self._rows(out)
         check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
@@ -172,6 +228,7 @@ class CudaOps:
                                        token_ids.shape[0], self._stream()), "patch_tokens")
         self.launches += 1
 
+    @_timed("norm")
     def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
         count = h.shape[0] if rows is None else rows.shape[0]
         if delta is not None and delta.dtype != out.dtype:
@@ -188,9 +245,29 @@ class CudaOps:
             self._tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)
         return self._tc_error
 
+    def _check_limits(self, cache, tables=None) -> None:
+        """Checked build: tell the kernels that follow how many pages the pool of `cache`
+        has and how many rows the rotation tables have."""
+        if self.checked and cache is not None:
+            rows = tables[0].shape[0] if tables is not None else 0
+            check(self.lib.mb_check_set_limits(cache.k.shape[0], rows, self._stream()),
+                  "check limits")
+
     def check_errors(self) -> None:
         """Raise if a bounded wait inside a tcgen05 kernel ran out since the last check
-        (reads one word from the device, so it synchronises)."""
+        (reads one word from the device, so it synchronises). In the checked build also
+        raise if a kernel met an index beyond its limit."""
+        if self.checked:
+            import ctypes
+
+            word = (ctypes.c_int * 4)()
+            check(self.lib.mb_check_read(word, self._stream()), "check read")
+            if word[0]:
+                kind = {1: "a page number beyond the pool", 2: "a block-table column beyond the table",
+                        3: "a position beyond the rotation tables", 4: "a token id outside the vocabulary",
+                        5: "a sequence number beyond the batch"}.get(word[0], f"kind {word[0]}")
+                raise KernelError(f"bounds check: {kind}: {word[1]} (limit {word[2]}), "
+                                  f"{word[3]} bad indices in all; the accesses were skipped")
         if not self._tc_pending or self._tc_error is None:
             self._tc_pending = False
             return
@@ -228,6 +305,7 @@ class CudaOps:
         return (None, _ptr(pending.h), _ptr(pending.weight), _ptr(pending.rows), float(pending.eps),
                 None, 0, 0.0, 0)
 
+    @_timed("residual product")
     def linear_residual(self, x, weight, bias, h, ctx, name, then_norm=None):
         """h += x . weight^T (+ bias) in the float32 stream when the few-token kernel takes
         the shape (returns None); otherwise the product lands in the buffer `name` and is
@@ -264,6 +342,7 @@ class CudaOps:
         self.linear(x, weight, bias, out)
         return out
 
+    @_timed("product")
     def linear(self, x, weight, bias, out):
         pending = self._pending(x)
         m, k = x.shape
@@ -322,6 +401,7 @@ class CudaOps:
                 out.add_(bias.float())
         self.library_calls += 1
 
+    @_timed("gated product")
     def linear_swiglu(self, x, weight, out, ctx):
         """out = silu(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]: one kernel
         for few tokens, product then gate otherwise."""
@@ -359,33 +439,45 @@ class CudaOps:
         m, k = x.shape
         cos, sin = tables if tables is not None else (None, None)
         rot = 2 * cos.shape[1] if cos is not None else 0
+        self._check_limits(cache, tables)
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                 and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
                 and cache.k.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_qkv_supports(m, k, head_dim, rot)):
-            xp, hp, wp, _rows, eps, ssp, sst, sse, ssk = self._skinny_input(x)
-            check(self.lib.mb_gemm_skinny_qkv_rope(
-                xp, hp, wp, eps, ssp, sst, sse, ssk, _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
-                _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table),
-                cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), m, k, num_heads, num_kv_heads,
-                head_dim, cache.page_size, int(cache.write), self._stream()),
-                "qkv_rope_store (skinny)")
-            self.launches += 1
+            self._qkv_rope_fused(x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, cos, sin,
+                                 rot, batch, cache)
             return
         if self._pending(x) is not None:
             x = x.materialize()
-        self.linear(x, weight, bias, qkv)
+        with self._as("q/k/v product"):
+            self.linear(x, weight, bias, qkv)
         self.rope_cache_write(qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache)
 
+    @_timed("q/k/v + rotary + store")
+    def _qkv_rope_fused(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, cos, sin, rot,
+                        batch, cache):
+        m, k = x.shape
+        xp, hp, wp, _rows, eps, ssp, sst, sse, ssk = self._skinny_input(x)
+        check(self.lib.mb_gemm_skinny_qkv_rope(
+            xp, hp, wp, eps, ssp, sst, sse, ssk, _ptr(weight), _ptr(bias), _ptr(qkv), _ptr(cos), _ptr(sin), rot,
+            _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table),
+            cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), m, k, num_heads, num_kv_heads,
+            head_dim, cache.page_size, int(cache.write), self._stream()),
+            "qkv_rope_store (skinny)")
+        self.launches += 1
+
+    @_timed("gate")
     def swiglu(self, gate_up, out):
         check(self.lib.mb_swiglu(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],
                                  _flag(out.dtype), self._stream()), "swiglu")
         self.launches += 1
 
+    @_timed("rotary + store")
     def rope_cache_write(self, qkv, num_heads, num_kv_heads, head_dim, tables, batch, cache):
         cos, sin = tables if tables is not None else (None, None)
         rot = 2 * cos.shape[1] if cos is not None else 0
         store = int(cache is not None and cache.write)
+        self._check_limits(cache, tables)
         if cache is not None and cache.k.dtype != qkv.dtype:
             raise KernelError("rope_cache_write: pages and activations differ in dtype")
         check(self.lib.mb_rope_store(
@@ -448,12 +540,14 @@ class CudaOps:
             return max(1, self.prompt_splits)
         return 1
 
+    @_timed("attention")
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
                         window, out, kernel: str | None = None):
         """`kernel` forces "mma" or "simt"; by default bfloat16 with a head size the
         tensor-core kernel takes runs there, everything else on the CUDA cores."""
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
+        self._check_limits(cache)
         tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
             head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
         if kernel == "tcgen05" and not tc_ok:
@@ -511,9 +605,11 @@ class CudaOps:
                   "paged_attention")
         self.launches += 1 if splits == 1 else 2
 
+    @_timed("attention")
     def _decode_cluster(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
                         out, cluster, tables, raw):
         cos, sin = tables if tables is not None else (None, None)
+        self._check_limits(cache, tables)
         check(self.lib.mb_paged_attention_decode_cluster(
             _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
             cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
@@ -559,10 +655,12 @@ class CudaOps:
             self.paged_attention(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
                                  out)
             return
-        self.linear(x, weight, bias, qkv)
+        with self._as("q/k/v product"):
+            self.linear(x, weight, bias, qkv)
         self._decode_cluster(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
                              out, self._cluster_of(splits), tables, True)
 
+    @_timed("sampling")
     def argmax(self, logits, out):
         rows = logits.shape[0]
         if self._argmax_scratch is None or self._argmax_scratch.numel() < rows * 128:
@@ -574,6 +672,7 @@ class CudaOps:
                                  _ptr(self._argmax_scratch), self._stream()), "argmax")
         self.launches += 2 if logits.shape[1] >= 16384 else 1
 
+    @_timed("sampling")
     def sample(self, logits, temperature, top_p, u, out):
         check(self.lib.mb_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(out),
                                  logits.shape[0], logits.shape[1], self._stream()), "sample")

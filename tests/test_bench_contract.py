@@ -49,3 +49,30 @@ def test_the_reference_arm_answers_in_one_json_line_without_a_gpu():
     record = json.loads(lines[0])
     assert record["impl"] == "reference"
     assert "value" in record or isinstance(record.get("unavailable"), str)
+
+
+def test_both_arms_name_the_same_metric_and_config():
+    import bench
+
+    config = bench.bench_config("measured")
+    assert len(config) <= 20 and all(not isinstance(v, (list, dict)) for v in config.values())
+    assert config["layers"] == 24 and config["global_batch"] == 8 and config["seq_len"] == 2048
+    assert "batch 8" in bench.METRIC
+
+
+def test_class_costs_add_up_to_the_step():
+    """The per-class bytes of a decode step sum to the step's bytes (weights once, the cache
+    of the live requests), and the per-class flops of a prompt step to the step's flops."""
+    import bench
+
+    cfg = bench.QWEN25_05B
+    numbers = bench.model_numbers(cfg)
+    costs = bench.class_costs(cfg, 8, 2048, 2048)
+    decode = costs["decode"]
+    weights_and_cache = sum(decode[k][1] for k in ("q/k/v product", "attention", "residual product",
+                                                    "gated product", "product"))
+    norms = 2 * (24 * 2 * 896 + 896)
+    assert weights_and_cache + norms == numbers["weight_bytes"] + 8 * 2048 * numbers["kv_bytes_per_token"]
+    prefill = costs["prefill"]
+    flops = sum(prefill[k][1] for k in ("q/k/v product", "attention", "residual product", "gated product"))
+    assert flops == 2048 * numbers["gemm_flops_per_token"] + numbers["attn_flops"](2048)

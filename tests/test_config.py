@@ -101,3 +101,20 @@ def test_engine_config_checks():
         cfg.validate_against(4096)
     with pytest.raises(ValueError, match="positions"):
         EngineConfig(max_model_len=8192, num_blocks=4096).validate_against(2048)
+
+
+def test_autosize_blocks_takes_the_fraction_of_what_is_left(monkeypatch):
+    """mercury/config.py:164-185: (free - reserve) * fraction // (bytes per token * block)."""
+    import torch
+
+    from mercury_b200.config.engine_config import EngineConfig, autosize_blocks
+
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda index=0: (10 * 2 ** 30, 16 * 2 ** 30))
+    cfg = EngineConfig(block_size=16, gpu_memory_fraction=0.5)
+    per_token = 24 * 2 * 2 * 64 * 2
+    assert autosize_blocks(per_token, cfg, reserve_bytes=2 * 2 ** 30) == (4 * 2 ** 30) // (per_token * 16)
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda index=0: (2 ** 20, 16 * 2 ** 30))
+    import pytest
+
+    with pytest.raises(RuntimeError, match="no room for a cache"):
+        autosize_blocks(per_token, cfg, reserve_bytes=2 ** 30)

@@ -150,3 +150,34 @@ def test_a_name_in_use_is_refused():
     engine.run_until_idle()
     assert [e.kind for e in second] == ["error", "token", "token", "done"]
     assert engine.leaked_pages() == 0
+
+
+def test_a_sink_that_raises_loses_its_request_not_the_loop():
+    """mercury/engine.py:259-262: the request whose sink raised is aborted (its pages go
+    back, its done-event is not delivered to the broken sink), the others finish."""
+    from mercury_b200 import SamplingParams
+
+    engine = make_engine("A", True)
+    prompts = [random_tokens(n, 256, 90 + n) for n in (9, 21, 14)]
+    good = {0: [], 2: []}
+    seen = []
+
+    def bad_sink(event):
+        seen.append(event.kind)
+        if event.kind == "token" and len([k for k in seen if k == "token"]) == 2:
+            raise RuntimeError("the client went away")
+
+    def sink_for(i):
+        return lambda event: good[i].append(event.token if event.kind == "token" else event.finish_reason)
+
+    engine.submit("r0", prompts[0], 6, sink_for(0), SamplingParams(), arrival=0.0)
+    engine.submit("r1", prompts[1], 6, bad_sink, SamplingParams(), arrival=1.0)
+    engine.submit("r2", prompts[2], 6, sink_for(2), SamplingParams(), arrival=2.0)
+    engine.run_until_idle()
+    raw, _config, tensors = tiny_model("A")
+    for i in (0, 2):
+        assert good[i] == plain_generate(raw, tensors, prompts[i], 6) + ["length"]
+    assert seen.count("token") == 2, "no event may reach a sink after it raised"
+    assert engine.metrics.counters["aborted_requests"] == 1
+    assert engine.leaked_pages() == 0 and not engine.sched.has_work()
+    assert [r["finish_reason"] for r in engine.metrics.finished if r["rid"] == "r1"] == ["abort"]
