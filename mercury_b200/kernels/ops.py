@@ -130,6 +130,7 @@ class CudaOps:
         self._argmax_scratch: torch.Tensor | None = None
         self._timing: list | None = None      # (kind, start event, stop event) while timing
         self._timing_depth = 0
+        self._event_overhead_ms: float | None = None
         self._timing_label: str | None = None  # overrides the class of the calls inside `_as`
         self._pinned_stream: int | None = None
         self.launches = 0
@@ -176,12 +177,24 @@ class CudaOps:
         self._timing = []
 
     def end_timing(self) -> dict[str, float]:
-        """Milliseconds per class of call since `begin_timing()`; waits for the device."""
+        """Milliseconds per class of call since `begin_timing()`; waits for the device. What
+        a pair of events measures with nothing between them (a few microseconds) is taken
+        off every call."""
         events, self._timing = self._timing or [], None
+        if events and self._event_overhead_ms is None:
+            empty = []
+            for _ in range(20):
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                stop.record()
+                empty.append((start, stop))
+            torch.cuda.synchronize(self.device)
+            gaps = sorted(a.elapsed_time(b) for a, b in empty)
+            self._event_overhead_ms = gaps[len(gaps) // 2]
         torch.cuda.synchronize(self.device)
         out: dict[str, float] = {}
         for kind, start, stop in events:
-            out[kind] = out.get(kind, 0.0) + start.elapsed_time(stop)
+            out[kind] = out.get(kind, 0.0) + max(0.0, start.elapsed_time(stop) - self._event_overhead_ms)
         return out
 
     def _scratch_for(self, floats: int) -> torch.Tensor:

@@ -70,7 +70,7 @@ class GroupedQueryAttention(Mixer):
             ]
         if self.out_bias:
             specs.append(TensorSpec(p + "o_proj.bias", (h,)))
-        return specs
+        return specs + self.position.tensor_specs()      # a learned encoding owns tensors too
 
     def load(self, tensors, setup):
         p = self.prefix

@@ -36,6 +36,17 @@ class PartStand:
         self.ctx.batch = self.buffers.build(entries, self.page_size)
         return entries
 
+    def continue_with(self, entries, counts):
+        """The next `counts[i]` tokens of each sequence of `entries`, after the tokens it has
+        run so far were booked as computed."""
+        following = []
+        for e, n in zip(entries, counts):
+            self.cache.advance(e.seq, e.seq.num_computed + len(e.tokens))
+            assert self.cache.ensure(e.seq, e.seq.num_computed + n)
+            following.append(StepEntry(e.seq, [0] * n, []))
+        self.ctx.batch = self.buffers.build(following, self.page_size)
+        return following
+
     def layer_cache(self, kv_heads, head_dim, group=0):
         k = torch.zeros((self.num_pages, kv_heads, self.page_size, head_dim), dtype=self.dtype,
                         device=self.device)
