@@ -686,6 +686,11 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     float* land_ml = land_o + 16 * D;
     __shared__ float ml_red[4][16][2];
     __shared__ float ml_part[16][2];                                      // row maximum (log2 units), sum
+    // The block table of this block's key range, a window of it at a time: a table entry
+    // read from global memory inside the key loop puts a trip to L2 in front of every tile's
+    // copies (with 16 tiles per block that trip, not the copies, set the kernel's time).
+    constexpr int PAGE_WINDOW = 256;
+    __shared__ int page_s[PAGE_WINDOW];
 
     uint32_t split, num_splits;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
@@ -714,13 +719,30 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     }
     const int n_tiles = t_hi > t_lo ? t_hi - t_lo : 0;
 
-    // each thread copies half a key row of K and of V: one table lookup per tile
+    // tiles [window_lo, window_lo + window_tiles) have their table entries in page_s
+    // (pages of 2 or more tokens: at least 8 tiles, which covers the stages filled up front;
+    // pages larger than a tile share an entry between tiles, two entries are kept spare)
+    const int window_tiles = page_size >= MMA_BN ? PAGE_WINDOW - 2 : PAGE_WINDOW / (MMA_BN / page_size);
+    int window_lo = t_lo;
+    auto fill_window = [&](int first_tile) {
+        window_lo = first_tile;
+        const int base = (first_tile * MMA_BN) / page_size;
+        for (int e = tid; e < PAGE_WINDOW; e += 128) {
+            const int column = base + e;
+            page_s[e] = (column < max_pages && (int64_t)column * page_size < kv_len)
+                            ? table_page(table, seq, max_pages, column) : -1;
+        }
+    };
+    fill_window(t_lo);
+    __syncthreads();
+
+    // each thread copies half a key row of K and of V
     const int lj = tid >> 1, lc0 = (tid & 1) * (CH / 2);
     auto load_tile = [&](int stage, int kt) {
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
-            page = table_page(table, seq, max_pages, key / page_size);
+            page = page_s[key / page_size - (window_lo * MMA_BN) / page_size];
         const bool valid = page >= 0;
         const int64_t at =
             valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
@@ -881,6 +903,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         }
         if (it >= 1 && !resident) {
             const int next = it - 1 + STAGES;
+            if (next < n_tiles && t_lo + next >= window_lo + window_tiles) {
+                // the window has been used up: everyone is past the barrier above, so nobody
+                // reads it any more; the next stretch of the table takes its place
+                fill_window(t_lo + next);
+                __syncthreads();
+            }
             if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
             asm volatile("cp.async.commit_group;\n" ::);
         }
@@ -1261,7 +1289,9 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                 int raw, int store, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
-    if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
+    // (pages of one token would leave the kernel's window of the block table shorter than
+    // the tiles it fills up front)
+    if (page_size < 2 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
     if (q_row_stride % 8) return MB_ERR_ALIGNMENT;
     if (max_q_len * (n_q / n_kv) > 16 || n_kv > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return MB_ERR_UNSUPPORTED_SIZE;

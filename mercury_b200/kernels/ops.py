@@ -561,6 +561,21 @@ class CudaOps:
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
         self._check_limits(cache)
+        if kernel == "tc2":
+            if not (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tc2_supports(
+                    head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1])):
+                raise KernelError("the tensor-memory attention takes bfloat16, head sizes 64 and 128 "
+                                  "and pages of 8 to 128 tokens")
+            check(self.lib.mb_paged_attention_tc2(
+                _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), cache.k.shape[0],
+                _ptr(cache.table), cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
+                _ptr(out), tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads,
+                head_dim, cache.page_size, float(scale), int(window),
+                self.prompt_cluster or 1, _ptr(self._error_word()),
+                self._stream()), "paged_attention (tc2)")
+            self.launches += 1
+            self._tc_pending = True
+            return
         tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
             head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
         if kernel == "tcgen05" and not tc_ok:
@@ -588,7 +603,7 @@ class CudaOps:
             small = batch.max_q_len * group <= 16
             if small:
                 splits = self._splits(batch, num_kv_heads, group, 16, 64)
-                if self.decode_clusters and splits < 32 and kernel is None:
+                if self.decode_clusters and splits < 32 and kernel is None and cache.page_size >= 2:
                     cluster = self._cluster_of(splits)
                     self._decode_cluster(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
                                          window, out, cluster, None, False)
@@ -657,6 +672,7 @@ class CudaOps:
         fused = (self.decode_clusters and weight.dtype == torch.bfloat16
                  and x.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
                  and cache is not None and cache.write and cache.k.dtype == torch.bfloat16
+                 and cache.page_size >= 2
                  and qkv.dtype == torch.bfloat16 and batch.max_q_len * group <= 16
                  and self.lib.mb_attention_mma_supports(head_dim)
                  and self.lib.mb_attention_decode_raw_pays(head_dim)
