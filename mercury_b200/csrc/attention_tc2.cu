@@ -14,18 +14,18 @@
 //   MMA      (warp 5)  S(i) = Q K(i)^T into tensor memory (128 columns of float32); later
 //                      O += P(i) V(i) with P read FROM tensor memory (the A operand of the
 //                      MMA), V from shared memory as it lies in the pages
-//   softmax  (warps 0-3, one thread per row)  one row of 128 scores into registers, mask,
-//            maximum, 2^x, the row's probabilities packed to bfloat16 and written back over
-//            the first half of the row's scores. Nothing is exchanged between threads, and
-//            nothing goes through shared memory. The maximum that the probabilities and the
-//            output are relative to is only raised when a tile exceeds it by more than 2^8
-//            (the thread then rescales its row of O in tensor memory).
-// Head size 64: scores (128 columns) and output (64) take 256 columns of tensor memory and
-// 80 KB of shared memory, so two CTAs share an SM and one's softmax runs under the other's
-// MMAs. Head size 128: one CTA per SM; the scores are double-buffered (2 x 128 + 128
-// columns), S(i+1) is issued before P(i) V(i), and the softmax of tile i+1 finds its scores
-// waiting. Products issued by one thread run in order, which is what lets P(i) lie where
-// S(i + 1 or 2) will be written.
+//   softmax  (warps 0-3, one thread per row)  the row's 128 scores in two trips to tensor
+//            memory of 64 each: mask, 2^x relative to the maximum in use, the probabilities
+//            packed to bfloat16 into the tile's P columns, and the tile's own maximum on the
+//            side. Nothing is exchanged between threads and nothing goes through shared
+//            memory. The maximum that the probabilities and the output are relative to is
+//            only raised when a tile exceeds it by more than 2^8: the warp then rescales its
+//            rows of O in tensor memory and does the tile again (the scores are still there).
+// Head size 64: scores (128 columns), probabilities (64) and output (64) take the 256
+// columns of tensor memory that let two CTAs share an SM (80 KB of shared memory each), so
+// one's softmax runs under the other's MMAs. Head size 128: one CTA per SM; scores and
+// probabilities are double-buffered (2 x 128 + 2 x 64 + 128 columns), S(i+1) is issued
+// before P(i) V(i), and the softmax of tile i+1 finds its scores waiting.
 // Launched as thread-block clusters of 2 or 4 CTAs, the CTAs of a cluster share one row tile
 // and split its key tiles between them; each leaves its (maximum, sum, unnormalised output)
 // in its own shared memory and the first CTA of the cluster merges them through distributed
@@ -94,6 +94,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __shared__ uint64_t q_full, kv_full[TB_STAGES], kv_free[TB_STAGES], s_ready[2], p_ready[2], o_ready[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int page_ok[TB_STAGES][TB_KEYS];      // per key of a tile: 1 if its page was copied
+    // the pages of this CTA's key tiles, a window of them at a time (producer warp only): a
+    // table entry fetched from global memory when a stage comes free would put a trip to L2
+    // in front of every tile's copies
+    constexpr int PAGE_WINDOW = 256;
+    __shared__ int page_win[PAGE_WINDOW];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = n_q / n_kv;
@@ -152,8 +157,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = tmem_base_slot;                          // S_BUFS x 128 columns of scores
-    const uint32_t tmem_o = tmem_base_slot + S_BUFS * TB_KEYS;       // D columns of output
+    const uint32_t tmem_s = tmem_base_slot;                                    // S_BUFS x 128 columns of scores
+    const uint32_t tmem_p = tmem_base_slot + S_BUFS * TB_KEYS;                 // S_BUFS x 64 columns of probabilities
+    const uint32_t tmem_o = tmem_base_slot + S_BUFS * (TB_KEYS + TB_KEYS / 2); // D columns of output
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
@@ -166,22 +172,33 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // a copy brings `box` keys: a whole page, or 128 keys of a larger one
         const int box = page_size < TB_KEYS ? page_size : TB_KEYS;
         const int copies = TB_KEYS / box;                 // at most 16 (pages of 8)
+        const int win_tiles = PAGE_WINDOW / copies;
+        int win_lo = t_first;
+        auto fill_window = [&](int first_tile) {
+            win_lo = first_tile;
+            __syncwarp();
+            for (int e = lane; e < PAGE_WINDOW; e += 32) {
+                const int key0 = first_tile * TB_KEYS + e * box;
+                page_win[e] = key0 < kv_len ? table_page(table, seq, max_pages, key0 / page_size) : -1;
+            }
+            __syncwarp();
+        };
+        if (n_tiles > 0) fill_window(t_first);
         bool ok = true;
         for (int i = 0; i < n_tiles; ++i) {
             const int st = i % TB_STAGES, kt = t_first + i;
+            if (kt >= win_lo + win_tiles) fill_window(kt);
+            // lanes 0 .. copies-1 each take one page of the tile
+            int page = -1, row = 0;
+            if (lane < copies) {
+                const int key0 = kt * TB_KEYS + lane * box;
+                page = page_win[(kt - win_lo) * copies + lane];
+                if (page >= 0) row = (page * n_kv + kvh) * page_size + key0 % page_size;
+            }
             if (i >= TB_STAGES) {
                 ok = mbar_wait(&kv_free[st], (uint32_t)((i / TB_STAGES - 1) & 1), error, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-            }
-            // lanes 0 .. copies-1 each look one page up
-            int page = -1, row = 0;
-            if (lane < copies) {
-                const int key0 = kt * TB_KEYS + lane * box;
-                if (key0 < kv_len) {
-                    page = table_page(table, seq, max_pages, key0 / page_size);
-                    row = (page * n_kv + kvh) * page_size + key0 % page_size;
-                }
             }
             for (int k = lane; k < TB_KEYS; k += 32) {
                 const int pg = __shfl_sync(0xffffffffu, page, k / box);
@@ -225,30 +242,30 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             };
             if (ok) ok = issue_scores(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
-                // two score buffers: the scores of the next tile first; their buffer was read
-                // by the softmax of tile i - 1, which handed P(i - 1) over before this point,
-                // and P(i - 1) V(i - 1) was issued before this product
+                // two score buffers: the scores of the next tile go first, into the buffer the
+                // softmax of tile i - 1 has finished with (it handed P(i - 1) over before this
+                // point); one buffer: they go as soon as the softmax of tile i has read its own
                 if (S_BUFS == 2 && i + 1 < n_tiles) ok = issue_scores(i + 1);
                 if (!ok) break;
                 const int buf = i % S_BUFS;
                 ok = mbar_wait(&p_ready[buf], (uint32_t)((i / S_BUFS) & 1), error, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (S_BUFS == 1 && i + 1 < n_tiles) ok = issue_scores(i + 1);
+                if (!ok) break;
                 const int st = i % TB_STAGES;
                 const unsigned char* v_tile = kv_s + st * 2 * TILE_BYTES + TILE_BYTES;
-                const uint32_t tmem_p = tmem_s + (uint32_t)(buf * TB_KEYS);
+                const uint32_t p_at = tmem_p + (uint32_t)(buf * (TB_KEYS / 2));
 #pragma unroll
                 for (int k = 0; k < TB_KEYS / 16; ++k) {
 #pragma unroll
                     for (int s = 0; s < SUBS; ++s)
-                        umma_bf16_a_tmem(tmem_o + (uint32_t)(s * 64), tmem_p + (uint32_t)(8 * k),
+                        umma_bf16_a_tmem(tmem_o + (uint32_t)(s * 64), p_at + (uint32_t)(8 * k),
                                          tb_desc_mn(v_tile + s * SUB_BYTES) + (uint64_t)(k * (2048 >> 4)),
                                          idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&o_ready[i & 1]);       // O holds tiles 0 .. i
                 umma_commit(&kv_free[st]);
-                // one score buffer: the next scores overwrite P(i), behind the product that reads it
-                if (S_BUFS == 1 && i + 1 < n_tiles) ok = issue_scores(i + 1);
             }
         }
     } else {
@@ -271,82 +288,102 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t my_s = tmem_s + lane_addr + (uint32_t)(buf * TB_KEYS);
+            const uint32_t my_p = tmem_p + lane_addr + (uint32_t)(buf * (TB_KEYS / 2));
             const int key0 = kt * TB_KEYS;
             // does every key of the tile count for this row, and is every key real?
             const bool plain = row_ok && key0 + TB_KEYS - 1 <= pos && key0 + TB_KEYS <= kv_len &&
                                (window <= 0 || key0 > pos - window);
-            // 32 scores of the row at a time; a key that does not count becomes -inf
-            auto load_scores = [&](int c0, uint32_t (&sv)[32]) {
-                tmem_load_32(my_s + (uint32_t)c0, sv);
+            // 64 scores of the row per trip to tensor memory (two loads in flight); a key that
+            // does not count becomes -inf
+            auto load_scores = [&](int c0, uint32_t (&sa)[32], uint32_t (&sb)[32]) {
+                tmem_load_32_async(my_s + (uint32_t)c0, sa);
+                tmem_load_32_async(my_s + (uint32_t)(c0 + 32), sb);
+                tmem_wait_ld();
                 if (!plain) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int key = key0 + c0 + j;
-                        bool seen = row_ok && key <= pos && key < kv_len && page_ok[st][c0 + j];
-                        if (window > 0) seen = seen && key > pos - window;
-                        sv[j] = seen ? sv[j] : 0xff800000u;
+                        const int ka = key0 + c0 + j, kb = ka + 32;
+                        bool seen_a = row_ok && ka <= pos && ka < kv_len && page_ok[st][c0 + j];
+                        bool seen_b = row_ok && kb <= pos && kb < kv_len && page_ok[st][c0 + 32 + j];
+                        if (window > 0) {
+                            seen_a = seen_a && ka > pos - window;
+                            seen_b = seen_b && kb > pos - window;
+                        }
+                        sa[j] = seen_a ? sa[j] : 0xff800000u;
+                        sb[j] = seen_b ? sb[j] : 0xff800000u;
                     }
                 }
             };
-            // first pass: the row's maximum (the scores are read again below: a second trip
-            // to tensor memory is cheaper than 128 live registers)
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // The probabilities of the tile relative to `shift`, rounded to bfloat16, two to a
+            // column, into the tile's P columns; returns their sum and leaves the tile's
+            // maximum (log2 units) in `m_tile`. A row that has seen no key yet (m = -inf)
+            // gets zeros: (-inf) * scale2 - 0 = -inf, 2^-inf = 0.
+            auto emit = [&](float shift, float& m_tile) -> float {
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-            for (int c0 = 0; c0 < TB_KEYS; c0 += 32) {
-                uint32_t sv[32];
-                load_scores(c0, sv);
+                for (int h0 = 0; h0 < TB_KEYS; h0 += 64) {
+                    uint32_t sa[32], sb[32], packed[32];
+                    load_scores(h0, sa, sb);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(sv[j]));
-            }
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+                    for (int j = 0; j < 16; ++j) {
+                        const float a0 = __uint_as_float(sa[2 * j]), a1 = __uint_as_float(sa[2 * j + 1]);
+                        const float b0 = __uint_as_float(sb[2 * j]), b1 = __uint_as_float(sb[2 * j + 1]);
+                        mx[j & 3] = fmaxf(mx[j & 3], fmaxf(fmaxf(a0, a1), fmaxf(b0, b1)));
+                        const float p0 = tb_exp2(a0 * scale2 - shift), p1 = tb_exp2(a1 * scale2 - shift);
+                        const float p2 = tb_exp2(b0 * scale2 - shift), p3 = tb_exp2(b1 * scale2 - shift);
+                        sum[j & 3] += (p0 + p1) + (p2 + p3);
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+                        packed[j] = *reinterpret_cast<uint32_t*>(&lo);         // keys h0 + 2j, + 1
+                        packed[16 + j] = *reinterpret_cast<uint32_t*>(&hi);    // keys h0 + 32 + 2j, + 1
+                    }
+                    tmem_store_32(my_p + (uint32_t)(h0 / 2), packed);
+                }
+                m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+                return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            };
             if (i == 0) {
-                m = m_tile;
-            } else if (__any_sync(0xffffffffu, m_tile > m + TB_RAISE)) {
-                // some row of this warp outgrew its maximum: every row moves to its exact
-                // maximum and the warp rescales its rows of O, once P(i-1) V(i-1) is in
+                // the first tile: its maximum first (a pass over the scores alone)
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int h0 = 0; h0 < TB_KEYS; h0 += 64) {
+                    uint32_t sa[32], sb[32];
+                    load_scores(h0, sa, sb);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+                }
+                m = mx * scale2;
+            }
+            // One pass: the probabilities relative to the maximum in use, and the tile's own
+            // maximum beside them. Only when some row of the warp outgrew its maximum by more
+            // than 2^8 is the tile done again: every row moves to its exact maximum and the
+            // warp rescales its rows of O, once P(i-1) V(i-1) is in. Short of that a stale
+            // maximum changes nothing but the scale of intermediate values.
+            float m_tile;
+            float added = emit(m > -INFINITY ? m : 0.f, m_tile);
+            if (__any_sync(0xffffffffu, m_tile > m + TB_RAISE)) {
                 const float m_new = fmaxf(m, m_tile);
                 const float factor = m > -INFINITY ? tb_exp2(m - m_new) : 1.f;
                 m = m_new;
                 l *= factor;
-                ok = mbar_wait(&o_ready[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), error, 4);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (i > 0) {
+                    ok = mbar_wait(&o_ready[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), error, 4);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t ov[32];
-                    tmem_load_32(my_o + (uint32_t)c0, ov);
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t ov[32];
+                        tmem_load_32(my_o + (uint32_t)c0, ov);
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-                    tmem_store_32(my_o + (uint32_t)c0, ov);
-                }
-                tmem_wait_st();
-            }
-            // second pass: probabilities, rounded to bfloat16, two to a column, written over
-            // the first half of the row's scores (64 scores become 32 columns: a half is
-            // written only after both its score chunks were read); a row that has seen no key
-            // yet (m = -inf) gets zeros: (-inf) * scale2 - 0 = -inf, 2^-inf = 0
-            const float shift = m > -INFINITY ? m : 0.f;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int h0 = 0; h0 < TB_KEYS; h0 += 64) {
-                uint32_t packed[32];
-#pragma unroll
-                for (int part = 0; part < 2; ++part) {
-                    uint32_t sv[32];
-                    load_scores(h0 + part * 32, sv);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float p0 = tb_exp2(__uint_as_float(sv[2 * j]) * scale2 - shift);
-                        const float p1 = tb_exp2(__uint_as_float(sv[2 * j + 1]) * scale2 - shift);
-                        sum[j & 3] += p0 + p1;
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                        packed[part * 16 + j] = *reinterpret_cast<uint32_t*>(&h2);
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+                        tmem_store_32(my_o + (uint32_t)c0, ov);
                     }
                 }
-                tmem_store_32(my_s + (uint32_t)(h0 / 2), packed);
+                added = emit(m > -INFINITY ? m : 0.f, m_tile);
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            l += added;
             // a value row that was not copied, or lies beyond the sequence, must not reach the
             // MMA as it is (0 * NaN): each thread clears one key of the tile
             if (!page_ok[st][r]) {
