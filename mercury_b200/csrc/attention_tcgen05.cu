@@ -1,59 +1,62 @@
-// Paged attention of prompt portions on the fifth-generation tensor cores (bfloat16, head
-// size 64): scores and the probability-weighted values are tcgen05.mma products with their
-// accumulators in tensor memory; queries, keys and values arrive by TMA, keys and values
-// straight from the pages the block table names.
+// Paged attention of prompt portions on the fifth-generation tensor cores, head sizes 64
+// and 128 (bfloat16): scores and the probability-weighted values are tcgen05.mma products
+// with their accumulators in tensor memory; queries, keys and values arrive by TMA, keys and
+// values straight from the pages the block table names; the probabilities never leave
+// tensor memory.
 //
 // Same contract as the other attention kernels (ragged batch, causal by absolute position,
 // optional window; mercury/model/attention.py:77-101 is the reference's gather-and-SDPA
 // version). A CTA takes floor(128 / group) query tokens of one sequence and one KV head: the
 // (token, head of the group) pairs are the 128 rows of the MMA, one row per accumulator
-// lane and per softmax thread. Keys are walked in tiles of 64 and the three roles run a
-// tile or more apart:
-//   producer (warp 8)  TMA of the tile's key and value pages into a three-stage ring
-//   MMA      (warp 9)  S(i+1) = Q K(i+1)^T is issued before P(i) V(i), so the tensor cores
-//                      work on the next scores while the softmax of tile i runs; the scores
-//                      are double-buffered in tensor memory, and O += P(i) V(i) accumulates
-//                      in tensor memory over all tiles (2 x 64 + 64 columns)
+// lane. Keys are walked in tiles of 128, one CTA per SM:
+//   producers (warp 8 the keys and the queries, warp 10 the values)  TMA of the tile's
+//            pages into rings of four (head size 64) or two (128) stages; a head of 128
+//            features lies as two sub-tiles of 64, each 128-byte swizzled. A stage's keys are
+//            handed back as soon as the scores that read them are done, its values after
+//            P V. The block table is read a window of 256 entries at a time, so that no trip
+//            to global memory stands between a free stage and its copies.
+//   MMA      (warp 9)  S(i+1) = Q K(i+1)^T is issued before P(i) V(i): scores and
+//            probabilities are double-buffered in tensor memory (2 x 128 + 2 x 64 columns)
+//            beside the output (64 or 128 columns), and the softmax of tile i+1 finds its
+//            scores waiting. O += P(i) V(i) reads P FROM tensor memory (the A operand of the
+//            MMA) and V from shared memory as it lies in the pages.
 //   softmax  (warps 0-7, two threads per row: warps w and w + 4 share the rows of tensor-
-//            memory lane quarter w, 32 keys and 32 output columns each)  one tcgen05.ld of
-//            the scores, mask, running maximum (the two halves meet through shared memory),
-//            2^x, probabilities rounded to bfloat16 into a swizzled shared-memory tile
-//            (double-buffered). The maximum that the probabilities and the output are
-//            relative to is only raised when a tile exceeds it by more than 2^8 (the warp
-//            then rescales its rows of O in tensor memory); short of that a stale maximum
-//            changes nothing but the scale of intermediate values, and the per-tile pass
-//            over the output disappears
-// The walk over the key tiles of the last row tile is the critical path of a causal prompt
-// (every CTA is resident from the start). Launched as thread-block clusters of 2 or 4 CTAs,
-// the CTAs of a cluster share one row tile and split its key tiles between them; each
-// leaves its (maximum, sum, unnormalised output) in its own shared memory and the first CTA
-// of the cluster merges them through distributed shared memory, so the partial results
-// never touch global memory.
-// Two CTAs fit on an SM (97 KB of shared memory, 256 tensor-memory columns each). Every
-// mbarrier wait is bounded; a wait that runs out sets the error word and the CTA winds down
-// (frees its tensor memory, returns).
+//            memory lane quarter w, 64 keys and half of the output columns each)  one trip
+//            to tensor memory for the thread's 64 scores, mask, 2^x relative to the maximum
+//            in use, the probabilities packed to bfloat16 into the tile's P columns, and the
+//            maximum of the thread's keys on the side; the two threads of a row then compare
+//            notes on a named barrier of their own. Nothing goes through shared memory but
+//            that one number. The maximum that the probabilities and the output are relative
+//            to is only raised when a tile exceeds it by more than 2^8: the two warps then
+//            rescale their columns of O in tensor memory and do the tile again (its scores
+//            are still there). Rows of the MMA that are no rows of the problem (two of 128
+//            with seven heads to a group) are cleared once and run the same code as the
+//            others: a lane on a path of its own holds its whole warp back in every tile.
+// What sets the kernel's time is the softmax of the heaviest row tile (2^x runs at 16 a
+// cycle and SM), so the row tiles are launched heaviest first.
+// Launched as thread-block clusters of 2 or 4 CTAs, the CTAs of a cluster share one row tile
+// and split its key tiles between them; each leaves its (maximum, sum, unnormalised output)
+// in its own shared memory and the first CTA of the cluster merges them through distributed
+// shared memory. Every mbarrier wait is bounded; a wait that runs out sets the error word
+// and the CTA winds down (frees its tensor memory, returns).
 #include "tcgen05.cuh"
 
 namespace mb {
 
-constexpr int TA_D = 64;             // head size
-constexpr int TA_ROWS = 128;         // MMA M: query rows per CTA
-constexpr int TA_KEYS = 64;          // keys per tile
-constexpr int TA_STAGES = 3;         // key/value tiles in flight
-constexpr int TA_THREADS = 320;          // 8 softmax warps, producer, MMA issuer
-constexpr int TA_HALF = TA_KEYS / 2;     // keys (and output columns) per softmax thread
-constexpr int TA_TILE_BYTES = TA_KEYS * 128;   // one key (or value) tile in shared memory
+constexpr int TB_ROWS = 128;         // MMA M: query rows per CTA
+constexpr int TB_KEYS = 128;         // keys per tile
+constexpr int TB_THREADS = 352;      // 8 softmax warps, key producer, MMA issuer, value producer
+constexpr float TB_RAISE = 8.f;      // log2 of how far a tile may exceed the maximum in use
 
-__device__ __forceinline__ float ta_exp2(float x) {
+__device__ __forceinline__ float tb_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
 
-constexpr float TA_RAISE = 8.f;      // log2 of how far a tile may exceed the maximum in use
-
-// MN-major B operand (values as stored: [key][d], d contiguous, 128-byte swizzle).
-__device__ __forceinline__ uint64_t umma_desc_mn(const void* tile) {
+// MN-major B operand (values as stored: [key][64 features], features contiguous, 128-byte
+// swizzle; 8 keys are 1024 bytes).
+__device__ __forceinline__ uint64_t tb_desc_mn(const void* tile) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
     d |= (uint64_t)1 << 16;               // one 64-element block along N: offset unused
@@ -63,30 +66,56 @@ __device__ __forceinline__ uint64_t umma_desc_mn(const void* tile) {
     return d;
 }
 
-__global__ void __launch_bounds__(TA_THREADS, 2)
-attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
-                         const __grid_constant__ CUtensorMap map_k,
-                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ table,
-                         int max_pages, const int* __restrict__ q_start,
-                         const int* __restrict__ kv_len_of, __nv_bfloat16* __restrict__ out, int n_q,
-                         int n_kv, int page_size, float scale, int window, int tiles_per_seq,
-                         int* __restrict__ error) {
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (128 rows x 16 bfloat16, two to a column,
+// row = lane) is read from tensor memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(TB_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ table,
+                     int max_pages, const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
+                     __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size, float scale,
+                     int window, int tiles_per_seq, int* __restrict__ error) {
+    constexpr int SUBS = D / 64;                       // 64-feature sub-tiles of a head
+    constexpr int S_BUFS = 2;                          // score (and probability) buffers in tensor memory
+    constexpr int TB_STAGES = D == 64 ? 4 : 2;         // key/value tiles in flight
+    constexpr int SUB_BYTES = TB_KEYS * 128;           // one sub-tile: 128 rows x 128 bytes
+    constexpr int TILE_BYTES = SUBS * SUB_BYTES;       // one K (or V, or Q) tile
+    constexpr uint32_t TMEM_COLS = 512u;               // 2 x 128 scores, 2 x 64 probabilities, D output
     grid_dependency_sync();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base =
         reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;                              // 128 rows x 128 B
-    unsigned char* kv_s = q_s + TA_ROWS * 128;              // [stage][K tile, V tile]
-    unsigned char* p_s = kv_s + TA_STAGES * 2 * TA_TILE_BYTES;   // 2 x (128 rows x 128 B)
-    __shared__ uint64_t q_full, kv_full[TA_STAGES], kv_free[TA_STAGES], s_ready[2], p_ready[2],
-        o_ready[2], pair_met[4];
+    unsigned char* q_s = base;                              // [SUBS][128 rows][128 B]
+    unsigned char* kv_s = q_s + TILE_BYTES;                 // [stage][K tile, V tile]
+    __shared__ uint64_t q_full, k_full[TB_STAGES], k_free[TB_STAGES], v_full[TB_STAGES], v_free[TB_STAGES],
+        s_ready[2], p_ready[2], o_ready[2];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int page_ok[TA_STAGES][TA_KEYS];      // per key of a tile: 1 if its page was copied
-    __shared__ float row_xch[2][2][TA_ROWS];         // [tile parity][half][row]: maxima, then sums
+    // per tile in flight, one bit per copy (a page, or 128 keys of a larger one): was it there?
+    // (twice as many entries as stages: a stage's keys are handed back when its scores are
+    // done, which is when the softmax threads only begin to look at the entry)
+    __shared__ uint32_t copied[2 * TB_STAGES];
+    __shared__ float row_xch[3][2][TB_ROWS];         // [first tile, tile parity][half][row]: maxima, sums
+    // the pages of this CTA's key tiles, a window of them at a time (producer warp only): a
+    // table entry fetched from global memory when a stage comes free would put a trip to L2
+    // in front of every tile's copies
+    constexpr int PAGE_WINDOW = 256;
+    __shared__ int page_win[2][PAGE_WINDOW];         // one window for each of the two producers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = n_q / n_kv;
-    const int tok_per_tile = TA_ROWS / group;
+    const int tok_per_tile = TB_ROWS / group;
     const int seq = blockIdx.x / tiles_per_seq;
     const int tile = tiles_per_seq - 1 - (blockIdx.x - seq * tiles_per_seq);   // heavy tiles first
     const int kvh = blockIdx.y;
@@ -100,12 +129,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     if (tok_max > q_len - 1) tok_max = q_len - 1;
     const int p_min = first_pos + tok0, p_max = first_pos + tok_max;
     int t_lo = 0;
-    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / TA_KEYS;
+    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / TB_KEYS;
     // the key tiles of this row tile, cut evenly over the CTAs of the cluster
     uint32_t cl_rank, cl_size;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cl_size));
-    const int tiles_all = p_max / TA_KEYS + 1 - t_lo;
+    const int tiles_all = p_max / TB_KEYS + 1 - t_lo;
     const int tiles_per_cta = (tiles_all + (int)cl_size - 1) / (int)cl_size;
     const int t_first = t_lo + (int)cl_rank * tiles_per_cta;
     int n_tiles = t_lo + tiles_all - t_first;
@@ -114,119 +143,170 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        for (int i = 0; i < TA_STAGES; ++i) {
-            mbar_init(&kv_full[i], 1);
-            mbar_init(&kv_free[i], 1);
+        for (int i = 0; i < TB_STAGES; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_free[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_free[i], 1);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(&pair_met[i], 2);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_ready[i], 1);
-            mbar_init(&p_ready[i], 8);
+            mbar_init(&p_ready[i], 8);       // one arrival per softmax warp
+            // P V of tile i commits to o_ready[i & 1]: a wait for tile i finds that barrier
+            // either in the phase of tile i or just past it (tile i - 2 is known to be complete
+            // when the scores of tile i have arrived, tile i + 2 cannot start before P(i + 2)
+            // exists), so the parity of the wait is never ambiguous although most phases are
+            // never waited for
+            mbar_init(&o_ready[i], 1);
         }
-        // P V of tile i commits to o_ready[i & 1]: a wait for tile i finds that barrier either
-        // in the phase of tile i or just past it (tile i - 2 is known to be complete when the
-        // scores of tile i have arrived, tile i + 2 cannot start before P(i + 2) exists), so
-        // the parity of the wait is never ambiguous although most phases are never waited for
-        mbar_init(&o_ready[0], 1);
-        mbar_init(&o_ready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // The query rows beyond group * tok_per_tile (two of 128 with seven heads to a group) are
+    // no part of the TMA box: they are cleared once, so that their scores are zeros rather
+    // than whatever the memory held, and their threads can run the same code as every other
+    // row (a lane on a path of its own would hold its whole warp back in every tile).
+    for (int idx = threadIdx.x; idx < (TB_ROWS - group * tok_per_tile) * SUBS * 8; idx += TB_THREADS) {
+        const int row = group * tok_per_tile + idx / (SUBS * 8), piece = idx % (SUBS * 8);
+        *reinterpret_cast<uint4*>(q_s + (piece / 8) * SUB_BYTES + row * 128 + (piece % 8) * 16) =
+            make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&tmem_base_slot)),
-                     "r"(256u)
+                     "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = tmem_base_slot;                 // 2 x 64 columns of scores
-    const uint32_t tmem_o = tmem_base_slot + 2 * TA_KEYS;   // 64 columns of output
+    const uint32_t tmem_s = tmem_base_slot;                                    // S_BUFS x 128 columns of scores
+    const uint32_t tmem_p = tmem_base_slot + S_BUFS * TB_KEYS;                 // S_BUFS x 64 columns of probabilities
+    const uint32_t tmem_o = tmem_base_slot + S_BUFS * (TB_KEYS + TB_KEYS / 2); // D columns of output
 
-    if (warp == 8) {
-        // ---------------------------------------------------------------- producer
-        if (lane == 0 && n_tiles > 0) {
-            mbar_expect_tx(&q_full, (uint32_t)(group * tok_per_tile * 128));
-            tma_load_4d(q_s, &map_q, 0, 0, kvh, q_begin + tok0, &q_full);
+    // a copy brings `box` keys: a whole page, or 128 keys of a larger one
+    const int box = page_size < TB_KEYS ? page_size : TB_KEYS;
+    const int box_shift = 31 - __clz(box);
+    if (warp == 8 || warp == 10) {
+        // ------------------------------------------- producers: warp 8 the keys (and the
+        // queries), warp 10 the values. A stage's keys are free again as soon as the scores
+        // that read them are done, its values after P V; each warp issues its own copies
+        // (a copy costs its issuing thread some 60 cycles, 8 to 32 of them per tile).
+        const bool keys = warp == 8;
+        uint64_t* full = keys ? k_full : v_full;
+        uint64_t* freed = keys ? k_free : v_free;
+        const CUtensorMap* map = keys ? &map_k : &map_v;
+        int* window = page_win[keys ? 0 : 1];
+        if (keys && lane == 0 && n_tiles > 0) {
+            mbar_expect_tx(&q_full, (uint32_t)(group * tok_per_tile * D * 2));
+#pragma unroll
+            for (int s = 0; s < SUBS; ++s)
+                tma_load_4d(q_s + s * SUB_BYTES, &map_q, s * 64, 0, kvh, q_begin + tok0, &q_full);
         }
-        // a copy brings `box` keys: a whole page, or 64 keys of a larger one
-        const int box = page_size < TA_KEYS ? page_size : TA_KEYS;
-        const int copies = TA_KEYS / box;
+        const int copies = TB_KEYS / box;                 // at most 16 (pages of 8)
+        const int win_tiles = PAGE_WINDOW / copies;
+        int win_lo = t_first;
+        auto fill_window = [&](int first_tile) {
+            win_lo = first_tile;
+            __syncwarp();
+            for (int e = lane; e < PAGE_WINDOW; e += 32) {
+                const int key0 = first_tile * TB_KEYS + e * box;
+                window[e] = key0 < kv_len ? table_page(table, seq, max_pages, key0 / page_size) : -1;
+            }
+            __syncwarp();
+        };
+        if (n_tiles > 0) fill_window(t_first);
         bool ok = true;
         for (int i = 0; i < n_tiles; ++i) {
-            const int st = i % TA_STAGES, kt = t_first + i;
-            if (i >= TA_STAGES) {
-                ok = mbar_wait(&kv_free[st], (uint32_t)((i / TA_STAGES - 1) & 1), error, 1);
+            const int st = i % TB_STAGES, kt = t_first + i;
+            if (kt >= win_lo + win_tiles) fill_window(kt);
+            // lanes 0 .. copies-1 each take one page of the tile
+            int page = -1, row = 0;
+            if (lane < copies) {
+                const int key0 = kt * TB_KEYS + lane * box;
+                page = window[(kt - win_lo) * copies + lane];
+                if (page >= 0) row = (page * n_kv + kvh) * page_size + key0 % page_size;
+            }
+            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+            if (i >= TB_STAGES) {
+                ok = mbar_wait(&freed[st], (uint32_t)((i / TB_STAGES - 1) & 1), error, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            // lanes 0 .. copies-1 each look one page up
-            int page = -1, row = 0;
-            if (lane < copies) {
-                const int key0 = kt * TA_KEYS + lane * box;
-                if (key0 < kv_len) {
-                    page = table_page(table, seq, max_pages, key0 / page_size);
-                    row = (page * n_kv + kvh) * page_size + key0 % page_size;
-                }
+            if (lane == 0) {
+                if (keys) copied[i % (2 * TB_STAGES)] = valid;   // read by the softmax threads behind s_ready
+                mbar_expect_tx(&full[st], (uint32_t)(__popc(valid) * box * D * 2));
             }
-            for (int k = lane; k < TA_KEYS; k += 32) {
-                const int pg = __shfl_sync(0xffffffffu, page, k / box);
-                page_ok[st][k] = pg >= 0 && kt * TA_KEYS + k < kv_len;
-            }
-            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-            __syncwarp();
-            if (lane == 0) mbar_expect_tx(&kv_full[st], (uint32_t)(__popc(valid) * 2 * box * 128));
             __syncwarp();
             if (page >= 0) {
-                unsigned char* k_dst = kv_s + st * 2 * TA_TILE_BYTES + lane * box * 128;
-                tma_load_2d(k_dst, &map_k, 0, row, &kv_full[st]);
-                tma_load_2d(k_dst + TA_TILE_BYTES, &map_v, 0, row, &kv_full[st]);
+                unsigned char* dst = kv_s + st * 2 * TILE_BYTES + (keys ? 0 : TILE_BYTES) + lane * box * 128;
+#pragma unroll
+                for (int s = 0; s < SUBS; ++s) tma_load_2d(dst + s * SUB_BYTES, map, s * 64, row, &full[st]);
             }
         }
     } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(TA_ROWS, TA_KEYS);
-            const uint32_t idesc_o = umma_idesc(TA_ROWS, TA_D) | (1u << 16);   // B is MN-major
-            const uint64_t qd = umma_desc(q_s);
+            const uint32_t idesc_s = umma_idesc(TB_ROWS, TB_KEYS);
+            const uint32_t idesc_o = umma_idesc(TB_ROWS, 64) | (1u << 16);   // B is MN-major
             bool ok = n_tiles > 0 && mbar_wait(&q_full, 0, error, 2);
-            // S(i) = Q K(i)^T into score buffer i & 1
+            // S(i) = Q K(i)^T into score buffer i % S_BUFS
             auto issue_scores = [&](int i) -> bool {
-                const int st = i % TA_STAGES;
-                if (!mbar_wait(&kv_full[st], (uint32_t)((i / TA_STAGES) & 1), error, 2)) return false;
+                const int st = i % TB_STAGES;
+                if (!mbar_wait(&k_full[st], (uint32_t)((i / TB_STAGES) & 1), error, 2)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t kd = umma_desc(kv_s + st * 2 * TA_TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < TA_D / 16; ++k)
-                    umma_bf16(tmem_s + (uint32_t)((i & 1) * TA_KEYS), qd + (uint64_t)(2 * k),
-                              kd + (uint64_t)(2 * k), idesc_s, k > 0);
-                umma_commit(&s_ready[i & 1]);
+                for (int s = 0; s < SUBS; ++s) {
+                    const uint64_t qd = umma_desc(q_s + s * SUB_BYTES);
+                    const uint64_t kd = umma_desc(kv_s + st * 2 * TILE_BYTES + s * SUB_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_s + (uint32_t)((i % S_BUFS) * TB_KEYS), qd + (uint64_t)(2 * k),
+                                  kd + (uint64_t)(2 * k), idesc_s, (s > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&s_ready[i % S_BUFS]);
+                umma_commit(&k_free[st]);          // the keys are free once these scores are done
                 return true;
             };
             if (ok) ok = issue_scores(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
-                // the scores of the next tile first: their buffer was read by the softmax of
-                // tile i - 1, which handed P(i - 1) over before this point
-                if (i + 1 < n_tiles) ok = issue_scores(i + 1);
+                // two score buffers: the scores of the next tile go first, into the buffer the
+                // softmax of tile i - 1 has finished with (it handed P(i - 1) over before this
+                // point); one buffer: they go as soon as the softmax of tile i has read its own
+                if (S_BUFS == 2 && i + 1 < n_tiles) ok = issue_scores(i + 1);
                 if (!ok) break;
-                ok = mbar_wait(&p_ready[i & 1], (uint32_t)((i >> 1) & 1), error, 5);
+                const int buf = i % S_BUFS;
+                ok = mbar_wait(&p_ready[buf], (uint32_t)((i / S_BUFS) & 1), error, 5);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int st = i % TA_STAGES;
-                const uint64_t vd = umma_desc_mn(kv_s + st * 2 * TA_TILE_BYTES + TA_TILE_BYTES);
-                const uint64_t pd = umma_desc(p_s + (i & 1) * (TA_ROWS * 128));
+                if (S_BUFS == 1 && i + 1 < n_tiles) ok = issue_scores(i + 1);
+                if (!ok) break;
+                const int st = i % TB_STAGES;
+                ok = mbar_wait(&v_full[st], (uint32_t)((i / TB_STAGES) & 1), error, 2);
+                if (!ok) break;
+                const unsigned char* v_tile = kv_s + st * 2 * TILE_BYTES + TILE_BYTES;
+                const uint32_t p_at = tmem_p + (uint32_t)(buf * (TB_KEYS / 2));
 #pragma unroll
-                for (int k = 0; k < TA_KEYS / 16; ++k)
-                    umma_bf16(tmem_o, pd + (uint64_t)(2 * k), vd + (uint64_t)(k * (2048 >> 4)),
-                              idesc_o, i > 0 || k > 0);
+                for (int k = 0; k < TB_KEYS / 16; ++k) {
+#pragma unroll
+                    for (int s = 0; s < SUBS; ++s)
+                        umma_bf16_a_tmem(tmem_o + (uint32_t)(s * 64), p_at + (uint32_t)(8 * k),
+                                         tb_desc_mn(v_tile + s * SUB_BYTES) + (uint64_t)(k * (2048 >> 4)),
+                                         idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit(&o_ready[i & 1]);       // O holds tiles 0 .. i
-                umma_commit(&kv_free[st]);
+                umma_commit(&v_free[st]);
             }
         }
     } else {
         // ------------------------------------------------------- softmax: two threads per row
+        // Warps w and w + 4 share the rows of tensor-memory lane quarter w: each takes 64 of a
+        // tile's 128 keys and half of the output columns. The two meet once per tile on a
+        // named barrier of their own (64 threads), to agree on the row's maximum; the meeting
+        // is a plain barrier, so a warp whose bounded wait ran out still goes through every
+        // tile's meetings (and does nothing else), or its partner would wait for ever.
         const int quarter = warp & 3, half = warp >> 2;
         const int r = quarter * 32 + lane;
         const int tok = tok0 + r / group;
@@ -234,156 +314,200 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool row_ok = r < group * tok_per_tile && tok < q_len;
         const int pos = first_pos + tok;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const uint32_t col0 = (uint32_t)(half * TA_HALF);
+        const int c_half = half * (TB_KEYS / 2);            // first key of a tile that is this thread's
         const float scale2 = scale * 1.4426950408889634f;
-        // the two warps of a lane quarter meet on an mbarrier of their own (a bounded wait,
-        // like every other wait of this kernel); `meetings` counts them for the parity
-        int meetings = 0;
-        auto pair_sync = [&]() -> bool {
-            __syncwarp();
-            if (lane == 0)
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&pair_met[quarter])) : "memory");
-            bool met = mbar_wait(&pair_met[quarter], (uint32_t)(meetings & 1), error, 6);
-            ++meetings;
-            return __all_sync(0xffffffffu, met);
-        };
+        auto meet = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
         // m: the maximum that O and l are relative to (log2 units); l: this thread's keys only
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        const uint32_t my_o = tmem_o + lane_addr + col0;
+        const uint32_t my_o = tmem_o + lane_addr + (uint32_t)(half * (D / 2));
         for (int i = 0; i < n_tiles; ++i) {
-            const int st = i % TA_STAGES, kt = t_first + i;
-            ok = mbar_wait(&s_ready[i & 1], (uint32_t)((i >> 1) & 1), error, 3);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t sv[TA_HALF];
-            tmem_load_32(tmem_s + lane_addr + (uint32_t)((i & 1) * TA_KEYS) + col0, sv);
-            const int key0 = kt * TA_KEYS;
-            // does every key of the tile count for this row, and is every key real?
-            const bool plain = row_ok && key0 + TA_KEYS - 1 <= pos && key0 + TA_KEYS <= kv_len &&
-                               (window <= 0 || key0 > pos - window);
-            if (!plain) {
-                // a key that does not count becomes -inf in place
-#pragma unroll
-                for (int j = 0; j < TA_HALF; ++j) {
-                    const int key = key0 + (int)col0 + j;
-                    bool seen = row_ok && key <= pos && key < kv_len && page_ok[st][col0 + j];
-                    if (window > 0) seen = seen && key > pos - window;
-                    sv[j] = seen ? sv[j] : 0xff800000u;
-                }
+            const int st = i % TB_STAGES, kt = t_first + i, buf = i % S_BUFS;
+            if (ok) {
+                ok = mbar_wait(&s_ready[buf], (uint32_t)((i / S_BUFS) & 1), error, 3);
+                ok = __all_sync(0xffffffffu, ok);
             }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (!ok) {
+                if (i == 0) meet();
+                meet();
+                continue;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t my_s = tmem_s + lane_addr + (uint32_t)(buf * TB_KEYS + c_half);
+            const uint32_t my_p = tmem_p + lane_addr + (uint32_t)(buf * (TB_KEYS / 2) + c_half / 2);
+            const int key0 = kt * TB_KEYS + c_half;
+            // does every key of the tile count for this row, and is every key real? (A row
+            // that is no row of the problem takes the same path: its numbers are finite and
+            // go nowhere.)
+            const bool plain = kt * TB_KEYS + TB_KEYS - 1 <= pos && (kt + 1) * TB_KEYS <= kv_len &&
+                               (window <= 0 || kt * TB_KEYS > pos - window);
+            const uint32_t landed = copied[i % (2 * TB_STAGES)];   // which pages of the tile were there
+            // this thread's 64 scores of the row in one trip to tensor memory (two loads in
+            // flight); a key that does not count becomes -inf
+            auto load_scores = [&](uint32_t (&sa)[32], uint32_t (&sb)[32]) {
+                tmem_load_32_async(my_s, sa);
+                tmem_load_32_async(my_s + 32u, sb);
+                tmem_wait_ld();
+                if (!plain) {
 #pragma unroll
-            for (int j = 0; j < TA_HALF; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(sv[j]));
-            const float part = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
-            row_xch[i & 1][half][r] = part;
-            ok = pair_sync();
-            if (!ok) break;
-            const float m_tile = fmaxf(part, row_xch[i & 1][half ^ 1][r]);
+                    for (int j = 0; j < 32; ++j) {
+                        const int ka = key0 + j, kb = ka + 32;
+                        bool seen_a = row_ok && ka <= pos && ka < kv_len && ((landed >> ((c_half + j) >> box_shift)) & 1u);
+                        bool seen_b = row_ok && kb <= pos && kb < kv_len && ((landed >> ((c_half + 32 + j) >> box_shift)) & 1u);
+                        if (window > 0) {
+                            seen_a = seen_a && ka > pos - window;
+                            seen_b = seen_b && kb > pos - window;
+                        }
+                        sa[j] = seen_a ? sa[j] : 0xff800000u;
+                        sb[j] = seen_b ? sb[j] : 0xff800000u;
+                    }
+                }
+            };
+            // The probabilities of this thread's keys relative to `shift`, rounded to bfloat16,
+            // two to a column, into the tile's P columns; returns their sum and leaves their
+            // maximum (log2 units) in `m_mine`. A row that has seen no key yet (m = -inf)
+            // gets zeros: (-inf) * scale2 - 0 = -inf, 2^-inf = 0.
+            auto emit = [&](float shift, float& m_mine) -> float {
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t sa[32], sb[32], packed[32];
+                load_scores(sa, sb);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float a0 = __uint_as_float(sa[2 * j]), a1 = __uint_as_float(sa[2 * j + 1]);
+                    const float b0 = __uint_as_float(sb[2 * j]), b1 = __uint_as_float(sb[2 * j + 1]);
+                    mx[j & 3] = fmaxf(mx[j & 3], fmaxf(fmaxf(a0, a1), fmaxf(b0, b1)));
+                    const float p0 = tb_exp2(a0 * scale2 - shift), p1 = tb_exp2(a1 * scale2 - shift);
+                    const float p2 = tb_exp2(b0 * scale2 - shift), p3 = tb_exp2(b1 * scale2 - shift);
+                    sum[j & 3] += (p0 + p1) + (p2 + p3);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+                    packed[j] = *reinterpret_cast<uint32_t*>(&lo);         // keys 2j, 2j + 1 of this half
+                    packed[16 + j] = *reinterpret_cast<uint32_t*>(&hi);    // keys 32 + 2j, 32 + 2j + 1
+                }
+                tmem_store_32(my_p, packed);
+                m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+                return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            };
             if (i == 0) {
-                m = m_tile;
-            } else if (__any_sync(0xffffffffu, m_tile > m + TA_RAISE)) {
-                // some row of this warp outgrew its maximum: every row moves to its exact
-                // maximum and the warp rescales its rows of O, once P(i-1) V(i-1) is in
+                // the first tile: the row's maximum first (a pass over the scores alone)
+                uint32_t sa[32], sb[32];
+                load_scores(sa, sb);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+                row_xch[2][half][r] = mx * scale2;
+                meet();
+                m = fmaxf(mx * scale2, row_xch[2][half ^ 1][r]);
+            }
+            // One pass: the probabilities relative to the maximum in use, and the maximum of
+            // this thread's keys beside them; the two threads of a row then compare notes. Only
+            // when some row of the warp outgrew its maximum by more than 2^8 is the tile done
+            // again (by both warps of the quarter: they see the same rows and the same
+            // maxima): every row moves to its exact maximum and the warps rescale their
+            // columns of O, once P(i-1) V(i-1) is in. Short of that a stale maximum changes
+            // nothing but the scale of intermediate values.
+            float m_mine;
+            float added = emit(m > -INFINITY ? m : 0.f, m_mine);
+            row_xch[i & 1][half][r] = m_mine;
+            meet();
+            const float m_tile = fmaxf(m_mine, row_xch[i & 1][half ^ 1][r]);
+            if (__any_sync(0xffffffffu, m_tile > m + TB_RAISE)) {
                 const float m_new = fmaxf(m, m_tile);
-                const float factor = m > -INFINITY ? ta_exp2(m - m_new) : 1.f;
+                const float factor = m > -INFINITY ? tb_exp2(m - m_new) : 1.f;
                 m = m_new;
                 l *= factor;
-                ok = mbar_wait(&o_ready[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), error, 4);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t ov[TA_HALF];
-                tmem_load_32(my_o, ov);
+                if (i > 0) {
+                    ok = mbar_wait(&o_ready[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), error, 4);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) continue;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D / 2; c0 += 32) {
+                        uint32_t ov[32];
+                        tmem_load_32(my_o + (uint32_t)c0, ov);
 #pragma unroll
-                for (int c = 0; c < TA_HALF; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-                tmem_store_32(my_o, ov);
-                tmem_wait_st();
-            }
-            // probabilities, rounded to bfloat16, into the swizzled P tile; a row that has
-            // seen no key yet (m = -inf) gets zeros: (-inf) * scale2 - 0 = -inf, 2^-inf = 0
-            const float shift = m > -INFINITY ? m : 0.f;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            unsigned char* prow = p_s + (i & 1) * (TA_ROWS * 128) + r * 128;
-#pragma unroll
-            for (int c = 0; c < TA_HALF / 8; ++c) {
-                uint4 packed;
-                uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ta_exp2(__uint_as_float(sv[c * 8 + 2 * e]) * scale2 - shift);
-                    const float p1 = ta_exp2(__uint_as_float(sv[c * 8 + 2 * e + 1]) * scale2 - shift);
-                    sum[e] += p0 + p1;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                    pw[e] = *reinterpret_cast<uint32_t*>(&h2);
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+                        tmem_store_32(my_o + (uint32_t)c0, ov);
+                    }
                 }
-                const int chunk = half * (TA_HALF / 8) + c;
-                *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) * 16)) = packed;
+                added = emit(m > -INFINITY ? m : 0.f, m_mine);
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            l += added;
             // a value row that was not copied, or lies beyond the sequence, must not reach the
-            // MMA as it is (0 * NaN): the first 64 threads each clear one key of the tile
-            if (half == 0 && r < TA_KEYS && !page_ok[st][r]) {
-                unsigned char* v_row = kv_s + st * 2 * TA_TILE_BYTES + TA_TILE_BYTES + r * 128;
-                const uint4 zero = make_uint4(0, 0, 0, 0);
+            // MMA as it is (0 * NaN): the threads of the first half each clear one key of the
+            // tile, once the tile's copies have landed (a copy brings whole pages, rows beyond
+            // the sequence included)
+            if (half == 0 && !(((landed >> (r >> box_shift)) & 1u) && kt * TB_KEYS + r < kv_len)) {
+                mbar_wait(&v_full[st], (uint32_t)((i / TB_STAGES) & 1), error, 3);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(v_row + c * 16) = zero;
+                for (int s = 0; s < SUBS; ++s) {
+                    unsigned char* v_row = kv_s + st * 2 * TILE_BYTES + TILE_BYTES + s * SUB_BYTES + r * 128;
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(v_row + c * 16) = zero;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_wait_st();
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0)
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[i & 1])) : "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_ready[buf])) : "memory");
         }
         // the output: all tiles are in once the last P V has been committed
-        float o[TA_HALF];
-#pragma unroll
-        for (int c = 0; c < TA_HALF; ++c) o[c] = 0.f;
         if (ok && n_tiles > 0) {
             ok = mbar_wait(&o_ready[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), error, 4);
             ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t ov[TA_HALF];
-                tmem_load_32(my_o, ov);
-#pragma unroll
-                for (int c = 0; c < TA_HALF; ++c) o[c] = __uint_as_float(ov[c]);
-            }
+            if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         // the row's sum: both halves
-        if (ok) {
-            row_xch[n_tiles & 1][half][r] = l;
-            ok = pair_sync();
-            l += row_xch[n_tiles & 1][half ^ 1][r];
-        }
+        row_xch[2][half][r] = l;
+        meet();
+        l += row_xch[2][half ^ 1][r];
         if (cl_size == 1) {
-            if (ok && row_ok) {
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                __nv_bfloat16* dst =
-                    out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * TA_D + col0;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + half * (D / 2);
+#pragma unroll 1
+            for (int c0 = 0; c0 < D / 2; c0 += 32) {
+                uint32_t ov[32];
 #pragma unroll
-                for (int c = 0; c < TA_HALF; c += 8) {
-                    uint4 q;
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
+                for (int c = 0; c < 32; ++c) ov[c] = 0u;
+                if (ok && n_tiles > 0) tmem_load_32(my_o + (uint32_t)c0, ov);    // the whole warp
+                if (ok && row_ok) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        h2[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
-                    *reinterpret_cast<uint4*>(dst + c) = q;
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 q;
+                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            h2[e] = __floats2bfloat162_rn(__uint_as_float(ov[c + 2 * e]) * inv,
+                                                          __uint_as_float(ov[c + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = q;
+                    }
                 }
             }
         } else {
             // this CTA's share of the keys, for the merge below: the key/value ring is free
             // (every tile loaded was consumed); four columns of a row lie together and the
             // rows of a column group follow each other, so that a warp writes whole lines
-            float4* merge_o = reinterpret_cast<float4*>(kv_s);              // [16 groups][128 rows]
-            float* merge_ml = reinterpret_cast<float*>(merge_o + (TA_D / 4) * TA_ROWS);   // [m, l][128]
+            float4* merge_o = reinterpret_cast<float4*>(kv_s);                          // [D / 4][128 rows]
+            float* merge_ml = reinterpret_cast<float*>(merge_o + (D / 4) * TB_ROWS);    // [m, l][128]
+#pragma unroll 1
+            for (int c0 = 0; c0 < D / 2; c0 += 32) {
+                uint32_t ov[32];
 #pragma unroll
-            for (int c = 0; c < TA_HALF; c += 4)
-                merge_o[(((int)col0 + c) / 4) * TA_ROWS + r] = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                for (int c = 0; c < 32; ++c) ov[c] = 0u;
+                if (ok && n_tiles > 0) tmem_load_32(my_o + (uint32_t)c0, ov);
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    merge_o[((half * (D / 2) + c0 + c) / 4) * TB_ROWS + r] =
+                        make_float4(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]),
+                                    __uint_as_float(ov[c + 2]), __uint_as_float(ov[c + 3]));
+            }
             if (half == 0) {
-                merge_ml[r] = m;
-                merge_ml[TA_ROWS + r] = l;
+                merge_ml[r] = ok ? m : -INFINITY;
+                merge_ml[TB_ROWS + r] = ok ? l : 0.f;
             }
         }
     }
@@ -397,9 +521,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             const int r = quarter * 32 + lane;
             const int tok = tok0 + r / group, hg = r % group;
             const bool row_ok = r < group * tok_per_tile && tok < q_len;
-            const int col0 = half * TA_HALF;
+            const int col0 = half * (D / 2);
             const uint32_t local_o = smem_u32(kv_s);
-            const uint32_t local_ml = local_o + TA_D * TA_ROWS * 4;
+            const uint32_t local_ml = local_o + D * TB_ROWS * 4;
             uint32_t remote_o[4];
             float weight[4], l_of[4];
             float m_all = -INFINITY, l_all = 0.f;
@@ -413,22 +537,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_o[k]) : "r"(local_o), "r"(k));
                     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_ml) : "r"(local_ml), "r"(k));
                     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(weight[k]) : "r"(remote_ml + 4 * r) : "memory");
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l_of[k]) : "r"(remote_ml + 4 * (TA_ROWS + r)) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l_of[k]) : "r"(remote_ml + 4 * (TB_ROWS + r)) : "memory");
                 }
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k) m_all = fmaxf(m_all, weight[k]);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                weight[k] = weight[k] > -INFINITY ? ta_exp2(weight[k] - m_all) : 0.f;
+                weight[k] = weight[k] > -INFINITY ? tb_exp2(weight[k] - m_all) : 0.f;
                 l_all += l_of[k] * weight[k];
             }
             if (row_ok) {
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-                __nv_bfloat16* dst =
-                    out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * TA_D + col0;
-#pragma unroll
-                for (int c = 0; c < TA_HALF; c += 8) {
+                __nv_bfloat16* dst = out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D;
+#pragma unroll 1
+                for (int c = col0; c < col0 + D / 2; c += 8) {
                     // all loads of these eight columns first, then the sums
                     float4 part[4][2];
 #pragma unroll
@@ -437,8 +560,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                         for (int g4 = 0; g4 < 2; ++g4) {
                             part[k][g4] = make_float4(0.f, 0.f, 0.f, 0.f);
                             if (weight[k] != 0.f) {    // a CTA without keys for this row is skipped
-                                const uint32_t at =
-                                    remote_o[k] + 16u * (uint32_t)(((col0 + c) / 4 + g4) * TA_ROWS + r);
+                                const uint32_t at = remote_o[k] + 16u * (uint32_t)((c / 4 + g4) * TB_ROWS + r);
                                 asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
                                              : "=f"(part[k][g4].x), "=f"(part[k][g4].y),
                                                "=f"(part[k][g4].z), "=f"(part[k][g4].w)
@@ -477,7 +599,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot),
-                     "r"(256u)
+                     "r"(TMEM_COLS)
                      : "memory");
     }
 }
@@ -486,61 +608,57 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 
 using namespace mb;
 
-// Whether the tensor-memory attention takes this problem: bfloat16, head size 64, pages of 8
-// to 128 tokens, groups of at most 128 query heads per KV head, row strides that TMA accepts.
+// Whether the tensor-memory attention takes this problem: bfloat16, head size 64 or 128,
+// pages of 8 to 128 tokens, groups of at most 128 query heads per KV head, row strides that
+// TMA accepts.
 MB_EXPORT int mb_attention_tcgen05_supports(int d, int page_size, int n_q, int n_kv, int q_row_stride) {
-    if (d != TA_D || n_kv <= 0 || n_q % n_kv) return 0;
+    if ((d != 64 && d != 128) || n_kv <= 0 || n_q % n_kv) return 0;
     const int group = n_q / n_kv;
-    if (group > TA_ROWS) return 0;
+    if (group > TB_ROWS) return 0;
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return 0;
     return q_row_stride % 8 == 0;
 }
 
-// qkv: [tokens, q_row_stride] bfloat16 with the rotated queries first; k_pages / v_pages:
-// [num_pages, n_kv, page_size, 64]; out: [tokens, n_q * 64]. `error` as for mb_gemm_tcgen05
-// (codes 1 producer, 2 and 5 MMA issuer, 3, 4 and 6 softmax). `cluster` (1, 2 or 4) is the
-// number of CTAs that share a row tile and split its keys.
-MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, const void* k_pages,
-                                         const void* v_pages, int num_pages, const int* table,
-                                         int max_pages, const int* q_start, const int* kv_len,
-                                         void* out, int tokens, int num_seqs, int max_q_len, int n_q,
-                                         int n_kv, int d, int page_size, float scale, int window,
-                                         int cluster, int* error, void* stream) {
-    if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
-    if (!mb_attention_tcgen05_supports(d, page_size, n_q, n_kv, q_row_stride)) return MB_ERR_UNSUPPORTED_SIZE;
-    if (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) return MB_ERR_ALIGNMENT;
+template <int D>
+static int launch_attention_tcgen05(const void* qkv, int q_row_stride, const void* k_pages, const void* v_pages,
+                      int num_pages, const int* table, int max_pages, const int* q_start,
+                      const int* kv_len, void* out, int tokens, int num_seqs, int max_q_len, int n_q,
+                      int n_kv, int page_size, float scale, int window, int cluster, int* error,
+                      cudaStream_t stream) {
     const int group = n_q / n_kv;
-    const int tok_per_tile = TA_ROWS / group;
+    const int tok_per_tile = TB_ROWS / group;
     CUtensorMap map_q, map_k, map_v;
     {
-        // queries: [D, group, n_kv, tokens]
-        cuuint64_t dims[4] = {(cuuint64_t)TA_D, (cuuint64_t)group, (cuuint64_t)n_kv, (cuuint64_t)tokens};
-        cuuint64_t strides[3] = {(cuuint64_t)TA_D * 2, (cuuint64_t)group * TA_D * 2, (cuuint64_t)q_row_stride * 2};
-        cuuint32_t box[4] = {(cuuint32_t)TA_D, (cuuint32_t)group, 1u, (cuuint32_t)tok_per_tile};
+        // queries: [D, group, n_kv, tokens], copied 64 features at a time
+        cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)group, (cuuint64_t)n_kv, (cuuint64_t)tokens};
+        cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)group * D * 2, (cuuint64_t)q_row_stride * 2};
+        cuuint32_t box[4] = {64u, (cuuint32_t)group, 1u, (cuuint32_t)tok_per_tile};
         if (!make_map_nd(&map_q, qkv, 4, dims, strides, box)) return MB_ERR_LAUNCH;
     }
     {
         const cuuint64_t rows = (cuuint64_t)num_pages * n_kv * page_size;
-        cuuint64_t dims[2] = {(cuuint64_t)TA_D, rows};
-        cuuint64_t strides[1] = {(cuuint64_t)TA_D * 2};
-        cuuint32_t box[2] = {(cuuint32_t)TA_D, (cuuint32_t)(page_size < TA_KEYS ? page_size : TA_KEYS)};
+        cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+        cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+        cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < TB_KEYS ? page_size : TB_KEYS)};
         if (!make_map_nd(&map_k, k_pages, 2, dims, strides, box) ||
             !make_map_nd(&map_v, v_pages, 2, dims, strides, box))
             return MB_ERR_LAUNCH;
     }
-    const size_t smem = (size_t)(TA_ROWS + TA_STAGES * 2 * TA_KEYS + 2 * TA_ROWS) * 128 + 1024;
+    // queries, four (head size 64) or two (128) stages of keys and values, and room to round
+    // the start up to 1024 bytes
+    constexpr int stages = D == 64 ? 4 : 2;
+    const size_t smem = (size_t)(1 + 2 * stages) * (D / 64) * TB_KEYS * 128 + 1024;
     static bool raised = false;
     if (!raised) {
-        if (cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = true;
     }
     const int tiles_per_seq = (max_q_len + tok_per_tile - 1) / tok_per_tile;
-    if (n_kv > 65535 || (cluster != 1 && cluster != 2 && cluster != 4)) return MB_ERR_UNSUPPORTED_SIZE;
     // the CTAs of a cluster lie along z and share (row tile, KV head)
     dim3 grid(num_seqs * tiles_per_seq, n_kv, cluster);
-    cudaLaunchConfig_t config = launch_config(grid, TA_THREADS, smem, (cudaStream_t)stream);
+    cudaLaunchConfig_t config = launch_config(grid, TB_THREADS, smem, stream);
     cudaLaunchAttribute attrs[2];
     int num_attrs = 0;
     if (config.numAttrs) attrs[num_attrs++] = config.attrs[0];
@@ -553,8 +671,32 @@ MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, cons
     }
     config.attrs = attrs;
     config.numAttrs = num_attrs;
-    cudaLaunchKernelEx(&config, attention_tcgen05_kernel, map_q, map_k, map_v, table, max_pages, q_start,
+    cudaLaunchKernelEx(&config, attention_tcgen05_kernel<D>, map_q, map_k, map_v, table, max_pages, q_start,
                        kv_len, (__nv_bfloat16*)out, n_q, n_kv, page_size, scale, window, tiles_per_seq,
                        error);
     return launch_status();
+}
+
+// qkv: [tokens, q_row_stride] bfloat16 with the rotated queries first; k_pages / v_pages:
+// [num_pages, n_kv, page_size, d]; out: [tokens, n_q * d]. `error` as for mb_gemm_tcgen05
+// (codes 1 producer, 2 and 5 MMA issuer, 3 and 4 softmax). `cluster` (1, 2 or 4) is the
+// number of CTAs that share a row tile and split its keys.
+MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, const void* k_pages,
+                                     const void* v_pages, int num_pages, const int* table,
+                                     int max_pages, const int* q_start, const int* kv_len, void* out,
+                                     int tokens, int num_seqs, int max_q_len, int n_q, int n_kv, int d,
+                                     int page_size, float scale, int window, int cluster, int* error,
+                                     void* stream) {
+    if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
+    if (!mb_attention_tcgen05_supports(d, page_size, n_q, n_kv, q_row_stride)) return MB_ERR_UNSUPPORTED_SIZE;
+    if (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) return MB_ERR_ALIGNMENT;
+    if (n_kv > 65535 || (cluster != 1 && cluster != 2 && cluster != 4)) return MB_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64)
+        return launch_attention_tcgen05<64>(qkv, q_row_stride, k_pages, v_pages, num_pages, table, max_pages, q_start,
+                              kv_len, out, tokens, num_seqs, max_q_len, n_q, n_kv, page_size, scale,
+                              window, cluster, error, s);
+    return launch_attention_tcgen05<128>(qkv, q_row_stride, k_pages, v_pages, num_pages, table, max_pages, q_start,
+                           kv_len, out, tokens, num_seqs, max_q_len, n_q, n_kv, page_size, scale, window,
+                           cluster, error, s);
 }

@@ -65,9 +65,6 @@ _SIGNATURES = {
     "mb_paged_attention_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
-    "mb_paged_attention_tc2": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
     "mb_paged_attention_decode_cluster": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
@@ -109,8 +106,6 @@ def load():
     lib.mb_gemm_skinny_qkv_supports.restype = c_int
     lib.mb_attention_tcgen05_supports.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mb_attention_tcgen05_supports.restype = c_int
-    lib.mb_attention_tc2_supports.argtypes = [c_int, c_int, c_int, c_int, c_int]
-    lib.mb_attention_tc2_supports.restype = c_int
     lib.mb_attention_mma_supports.argtypes = [c_int]
     lib.mb_attention_mma_supports.restype = c_int
     lib.mb_attention_decode_raw_pays.argtypes = [c_int]

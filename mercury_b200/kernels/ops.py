@@ -76,8 +76,8 @@ class CudaOps:
         # ... and from this many on, weights come by TMA (gemm_skinny.cu: skinny_fed_kernel);
         # only those launches have a wait that can give up and so an error word to look at
         self.fed_min_elements = 12 * 1024 * 1024
-        # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head size 64, the
-        # mma.sync kernels for everything else; "mma": the mma.sync kernels only
+        # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head sizes 64 and
+        # 128, the mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
@@ -529,19 +529,14 @@ class CudaOps:
         return max(1, -(-self.graph_blocks_per_sm_large * self.sm_count // rows))
 
     def _prompt_cluster(self, batch, num_kv_heads, group) -> int:
-        """CTAs per row tile of the tensor-memory attention. While every CTA of a causal
-        prompt is resident from the start (two per SM), the walk over the keys of the last
-        row tile sets the kernel's time; then two CTAs share a row tile and split its keys
-        (merged through distributed shared memory). Measured on B200 with 14 heads over 2 KV
-        heads: 1024 tokens 27.8 -> 23.5 us, 2048 tokens 51 -> 46 us; at 4096 tokens and more
-        the CTAs already come in waves and the split only adds its merge (117 -> 120 us), and
-        four CTAs per row tile were slower than two at every length."""
+        """CTAs per row tile of the tensor-memory attention: the CTAs of a cluster share a
+        row tile and split its keys (merged through distributed shared memory). Measured on
+        B200 the split never paid with one CTA per SM and the heaviest row tiles scheduled
+        first (14 heads over 2 KV heads of 64, 2048 tokens: 36 us alone, 61 us in pairs; 12
+        over 2 of 128: 36 against 60 us), so it is used only when asked for."""
         if self.prompt_cluster is not None:
             return self.prompt_cluster
-        tokens_per_tile = max(1, 128 // group)
-        ctas = batch.num_seqs * -(-batch.max_q_len // tokens_per_tile) * num_kv_heads
-        key_tiles = -(-batch.max_kv_len // 64)
-        return 2 if key_tiles >= 8 and ctas <= 2 * self.sm_count else 1
+        return 1
 
     def _prompt_splits(self, batch, num_kv_heads, group) -> int:
         """Key ranges per row tile of a prompt portion. Cutting the keys (and merging the
@@ -561,26 +556,11 @@ class CudaOps:
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
         self._check_limits(cache)
-        if kernel == "tc2":
-            if not (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tc2_supports(
-                    head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1])):
-                raise KernelError("the tensor-memory attention takes bfloat16, head sizes 64 and 128 "
-                                  "and pages of 8 to 128 tokens")
-            check(self.lib.mb_paged_attention_tc2(
-                _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), cache.k.shape[0],
-                _ptr(cache.table), cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len),
-                _ptr(out), tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads,
-                head_dim, cache.page_size, float(scale), int(window),
-                self.prompt_cluster or 1, _ptr(self._error_word()),
-                self._stream()), "paged_attention (tc2)")
-            self.launches += 1
-            self._tc_pending = True
-            return
         tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
             head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
         if kernel == "tcgen05" and not tc_ok:
-            raise KernelError("the tensor-memory attention takes bfloat16, head size 64 and pages "
-                              "of 8 to 128 tokens")
+            raise KernelError("the tensor-memory attention takes bfloat16, head sizes 64 and 128 and "
+                              "pages of 8 to 128 tokens")
         # prompt portions (at least one full tile of rows) go to the tensor-memory kernel
         if tc_ok and (kernel == "tcgen05" or (kernel is None and self.attention == "auto"
                                               and batch.max_q_len * group >= 128)):

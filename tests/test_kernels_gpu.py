@@ -582,7 +582,7 @@ ATTENTION_CASES = [
 def attention_close(got, want, dtype, kernel):
     """The tensor-core kernels round the probabilities to bfloat16 before P.V and the result
     once more: two roundings of 2^-8, against one for the CUDA-core kernel."""
-    if kernel in ("mma", "tcgen05", "tc2", "clusters"):
+    if kernel in ("mma", "tcgen05", "clusters"):
         err = float((got.double() - want.double()).abs().max()) / float(want.abs().max())
         assert err <= 2 * 2.0 ** -8, f"attention (mma): relative error {err:.3e}"
     else:
@@ -591,8 +591,8 @@ def attention_close(got, want, dtype, kernel):
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
                                           ("mma", torch.bfloat16), ("tcgen05", torch.bfloat16),
-                                          ("tc2", torch.bfloat16), ("clusters", torch.bfloat16)],
-                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05", "bf16-tc2", "bf16-clusters"])
+                                          ("clusters", torch.bfloat16)],
+                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05", "bf16-clusters"])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("case", range(len(ATTENTION_CASES)), ids=lambda i: f"case{i}")
 def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
@@ -605,15 +605,13 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     if kernel == "tcgen05" and not ops.lib.mb_attention_tcgen05_supports(
             d, page, n_q, n_kv, (n_q + 2 * n_kv) * d):
         pytest.skip("left to the other attention kernels")
-    if kernel == "tc2" and not ops.lib.mb_attention_tc2_supports(d, page, n_q, n_kv, (n_q + 2 * n_kv) * d):
-        pytest.skip("left to the other attention kernels")
     if kernel == "clusters" and not (ops.lib.mb_attention_mma_supports(d)
                                      and max(q_lens) * (n_q // n_kv) <= 16):
         pytest.skip("the cluster kernel is for decode-like batches of head size 64 or 128")
     # for the tensor-memory kernel the split is the number of CTAs that share a row tile, for
     # the decode clusters the number of blocks of a (sequence, KV head)
     clusters = (None,)
-    if kernel in ("tcgen05", "tc2"):
+    if kernel == "tcgen05":
         clusters = (1,) if splits == 1 else (2, 4)
     elif kernel == "clusters":
         clusters = (1,) if splits == 1 else (2, 4, 8)
