@@ -942,26 +942,57 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             mma_bf16(s[1], qf[ks], b[2], b[3]);
         }
         float m_new[2] = {m[0], m[1]};
+        // Every key of this warp's 16 is seen by every row when the newest of them is no later
+        // than the earliest position of the step, real, and inside every row's window (rows
+        // beyond the step's are zeros and go nowhere): then nothing is masked one by one.
+        const int key_lo = kt * MMA_BN + warp * 16;
+        const bool plain = key_lo + 15 <= first_pos && key_lo + 15 < kv_len &&
+                           (window <= 0 || key_lo > p_max - window);
+        if (plain) {
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+            for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int key = kt * MMA_BN + warp * 16 + nt * 8 + 2 * t4 + (e & 1);
-                bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
-                if (window > 0) seen = seen && key > pos[h] - window;
-                s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
-                m_new[h] = fmaxf(m_new[h], s[nt][e]);
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= scale2;
+                    m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int key = key_lo + nt * 8 + 2 * t4 + (e & 1);
+                    bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                    if (window > 0) seen = seen && key > pos[h] - window;
+                    s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
+                    m_new[h] = fmaxf(m_new[h], s[nt][e]);
+                }
             }
         }
-        float corr[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-            corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
-            m[h] = m_new[h];
-            l[h] *= corr[h];
+        }
+        // the running sums and the output move to a new maximum only when some row of the
+        // warp has one (after the first tiles that is rare)
+        if (__any_sync(0xffffffffu, m_new[0] > m[0] || m_new[1] > m[1])) {
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
+                m[h] = m_new[h];
+                l[h] *= corr[h];
+            }
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -972,13 +1003,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
                 s[nt][e] = p;
                 l[h] += p;
             }
-        }
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[0];
-            o[i][2] *= corr[1];
-            o[i][3] *= corr[1];
         }
         uint32_t a[4];
         a[0] = pack_bf16(s[0][0], s[0][1]);
