@@ -13,7 +13,7 @@
 // pages into a two-stage, XOR-swizzled shared-memory ring. Scores, the running maximum and
 // sum, and the output accumulate in float32; probabilities are rounded to bfloat16 for the
 // P.V product (the usual flash-attention arrangement).
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace mb {
 
@@ -652,15 +652,23 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // area would cost the second block per SM) every block keeps its result, and after a cluster
 // barrier each block reads its rows from all the others' memories; a second barrier keeps
 // the memories alive meanwhile. Nothing goes through global memory, and there is no ticket.
-template <int D>
+// FED: the key and value tiles come by TMA (one copy per page, 128-byte swizzle, which is the
+// layout the fragments are read in) issued by lanes of warp 0 and awaited on one mbarrier per
+// stage, instead of 16 bytes per thread and instruction. For blocks that walk many tiles
+// (large batches) the per-thread copies were the limit: issuing a tile's 8 cp.async took a
+// thread 780 of the 2080 cycles a tile took. Head size 64, pages of 8 tokens or more.
+template <int D, bool FED>
 __global__ void __launch_bounds__(128)
-attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
+                                const __grid_constant__ CUtensorMap map_v,
+                                const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                                 const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages,
                                 const int* __restrict__ table, int max_pages,
                                 const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
                                 __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size,
                                 float scale, int window, const float* __restrict__ cos_t,
-                                const float* __restrict__ sin_t, int raw, int store) {
+                                const float* __restrict__ sin_t, int raw, int store,
+                                int* __restrict__ error) {
     // raw: q, k and v in `qkv` are the projection as it came out of the product (bias added,
     // not rotated, nothing stored): this kernel rotates the queries as it loads them, and the
     // block whose key range holds this step's positions rotates the new keys, writes them and
@@ -673,7 +681,11 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     __shared__ __align__(16) __nv_bfloat16 new_k[16][D]; // this step's keys, rotated
     __shared__ __align__(16) __nv_bfloat16 new_v[16][D];
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][D]
+    // (TMA's swizzle goes by the address: the tiles then start on a 1024-byte boundary)
+    unsigned char* smem_base = FED ? reinterpret_cast<unsigned char*>(
+                                         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                                   : smem_raw;
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_base);     // [16][D]
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
     __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
     float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][D], after the loop
@@ -691,6 +703,10 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     // copies (with 16 tiles per block that trip, not the copies, set the kernel's time).
     constexpr int PAGE_WINDOW = 256;
     __shared__ int page_s[PAGE_WINDOW];
+    __shared__ uint64_t tile_full[STAGES];       // FED: a stage's copies have landed
+    __shared__ uint32_t tile_pages[STAGES][4];   // FED: which of the stage's pages were there, by issuing warp
+    __shared__ int fed_error;                    // FED: a wait gave up (never read by the host:
+                                                 // the block then leaves its rows unwritten)
 
     uint32_t split, num_splits;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
@@ -734,11 +750,44 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
         }
     };
     fill_window(t_lo);
+    if (FED && tid == 0) {
+        for (int st = 0; st < STAGES; ++st) mbar_init(&tile_full[st], 4);   // one arrival per warp
+        fed_error = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
 
     // each thread copies half a key row of K and of V
     const int lj = tid >> 1, lc0 = (tid & 1) * (CH / 2);
+    // FED: a copy brings `box` keys (a page, or 64 keys of a larger one)
+    const int box = page_size < MMA_BN ? page_size : MMA_BN;
+    const int box_shift = 31 - __clz(box);
     auto load_tile = [&](int stage, int kt) {
+        if (FED) {
+            // the tile's copies are dealt out over the four warps (a copy costs its thread
+            // some 60 cycles): warp w takes every fourth of them, one lane each, and
+            // announces its own bytes; the stage is full when all four have and all landed
+            const int copies = MMA_BN / box;
+            const int copy = warp + 4 * lane;
+            int page = -1, row = 0;
+            if (copy < copies) {
+                const int key0 = kt * MMA_BN + copy * box;
+                if (key0 < kv_len) page = page_s[key0 / page_size - (window_lo * MMA_BN) / page_size];
+                if (page >= 0) row = (page * n_kv + kvh) * page_size + key0 % page_size;
+            }
+            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+            if (lane == 0) {
+                tile_pages[stage][warp] = valid;
+                mbar_expect_tx(&tile_full[stage], (uint32_t)(__popc(valid) * 2 * box * 128));
+            }
+            __syncwarp();
+            if (page >= 0) {
+                tma_load_2d(k_s + (stage * MMA_BN + copy * box) * D, &map_k, 0, row, &tile_full[stage]);
+                tma_load_2d(v_s + (stage * MMA_BN + copy * box) * D, &map_v, 0, row, &tile_full[stage]);
+            }
+            return;
+        }
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
@@ -875,7 +924,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
 
     // raw, and no more tiles than stages: every tile was asked for before the wait and none
     // is refilled, so one wait and the barrier below stand for the per-tile ones
-    const bool resident = raw && n_tiles <= STAGES;
+    const bool resident = !FED && raw && n_tiles <= STAGES;
     if (resident) asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
     uint32_t qf[D / 16][4];
@@ -893,7 +942,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = t_lo + it;
         const int stage = it % STAGES;
-        if (!resident) {
+        if (FED) {
+            // (bounded like every mbarrier wait of this library; a wait that gives up sets
+            // the error word and the block goes on with whatever the stage holds)
+            mbar_wait(&tile_full[stage], (uint32_t)((it / STAGES) & 1), error ? error : &fed_error, 8);
+            __syncthreads();   // the stage of tile it-1 is free
+        } else if (!resident) {
             if (kt >= t_new && !raw) {
                 asm volatile("cp.async.wait_group 0;\n" ::);
             } else {
@@ -930,6 +984,22 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
             __syncthreads();
         }
 
+        if (FED) {
+            // A copy brings whole pages and nothing for a page that is not there: value rows
+            // beyond the sequence or of a missing page are cleared before P V meets them
+            // (0 x NaN). Every warp clears among the 16 rows it reads itself.
+            const int row = warp * 16 + (lane >> 1), key = kt * MMA_BN + row;
+            // copy c of the tile was issued by lane c / 4 of warp c % 4
+            const int c_of = row >> box_shift;
+            const bool there = key < kv_len && ((tile_pages[stage][c_of & 3] >> (c_of >> 2)) & 1u);
+            if (!there) {
+                const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < CH / 2; ++c)
+                    *reinterpret_cast<uint4*>(vt_s + row * D + ((lane & 1) * (CH / 2) + c) * 8) = zero;
+            }
+            __syncwarp();
+        }
         // this warp's 16 keys of the tile
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -1193,20 +1263,33 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int D>
+template <int D, bool FED>
 int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
                                     const void* v_pages, const int* table, int max_pages,
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
                                     int page_size, float scale, int window, int num_seqs, int cluster,
                                     const float* cos_t, const float* sin_t, int raw, int store,
-                                    cudaStream_t s) {
+                                    int num_pages, int* error, cudaStream_t s) {
     constexpr int STAGES = D == 64 ? 5 : 3;
+    CUtensorMap map_k, map_v;
+    memset(&map_k, 0, sizeof(map_k));
+    memset(&map_v, 0, sizeof(map_v));
+    if (FED) {
+        const cuuint64_t rows = (cuuint64_t)num_pages * n_kv * page_size;
+        cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+        cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+        cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < MMA_BN ? page_size : MMA_BN)};
+        if (!make_map_nd(&map_k, k_pages, 2, dims, strides, box) ||
+            !make_map_nd(&map_v, v_pages, 2, dims, strides, box))
+            return MB_ERR_LAUNCH;
+    }
     // queries and key/value stages; with head size 64 also the landing area of the merge
+    // (FED: and room to start the tiles on a 1024-byte boundary)
     const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16) +
-                        (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0);
+                        (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D>,
+        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = true;
@@ -1225,9 +1308,10 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     config.attrs = attrs;
     config.numAttrs = num_attrs;
-    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D>, (const bf*)qkv, q_row_stride,
-                       (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start, kv_len, (bf*)out,
-                       n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store);
+    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED>, map_k, map_v, (const bf*)qkv,
+                       q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start,
+                       kv_len, (bf*)out, n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store,
+                       error);
     return launch_status();
 }
 
@@ -1310,7 +1394,12 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                 int tokens, int num_seqs, int max_q_len, int n_q,
                                                 int n_kv, int d, int page_size, float scale, int window,
                                                 int cluster, const float* cos_t, const float* sin_t,
-                                                int raw, int store, void* stream) {
+                                                int raw, int store, int num_pages, int* error,
+                                                void* stream) {
+    // num_pages > 0 (with the pages' count) and `error` (a zeroed word on the device) select
+    // the TMA-fed form for head size 64 and pages of 8 to 64 tokens: for blocks that walk many
+    // key tiles each (large batches). 0: the copies are 16 bytes per thread, as the small
+    // batches want them, whose tiles are all in flight before the kernel in front is done.
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     // (pages of one token would leave the kernel's window of the block table shorter than
@@ -1323,13 +1412,21 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
     // reads another layer's cache must find this step's keys in the pages
     if (raw && !store) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64 && num_pages > 0 && error != nullptr && page_size >= 8 && page_size <= MMA_BN &&
+        (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0)
+        return launch_attention_decode_cluster<64, true>(qkv, q_row_stride, k_pages, v_pages, table,
+                                                         max_pages, q_start, kv_len, out, n_q, n_kv,
+                                                         page_size, scale, window, num_seqs, cluster,
+                                                         cos_t, sin_t, raw, store, num_pages, error, s);
     if (d == 64)
-        return launch_attention_decode_cluster<64>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
-                                                   q_start, kv_len, out, n_q, n_kv, page_size, scale,
-                                                   window, num_seqs, cluster, cos_t, sin_t, raw, store, s);
-    return launch_attention_decode_cluster<128>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
-                                                q_start, kv_len, out, n_q, n_kv, page_size, scale, window,
-                                                num_seqs, cluster, cos_t, sin_t, raw, store, s);
+        return launch_attention_decode_cluster<64, false>(qkv, q_row_stride, k_pages, v_pages, table,
+                                                          max_pages, q_start, kv_len, out, n_q, n_kv,
+                                                          page_size, scale, window, num_seqs, cluster,
+                                                          cos_t, sin_t, raw, store, 0, nullptr, s);
+    return launch_attention_decode_cluster<128, false>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                                       q_start, kv_len, out, n_q, n_kv, page_size, scale,
+                                                       window, num_seqs, cluster, cos_t, sin_t, raw, store,
+                                                       0, nullptr, s);
 }
 
 // Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.

@@ -68,7 +68,7 @@ _SIGNATURES = {
     "mb_paged_attention_decode_cluster": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
-                                          c_void_p, c_int, c_int, c_void_p],
+                                          c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_gemm_skinny_set_slices": [c_int, c_int],
     "mb_patch_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],

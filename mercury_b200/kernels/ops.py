@@ -117,6 +117,7 @@ class CudaOps:
         # pairs, at most `graph_max_ranges_small` ranges each (a range then still holds three
         # or more 64-key tiles); about `graph_blocks_per_sm_large` per SM beyond that.
         self.graph_small_rows = 16
+        self.decode_long_ranges: bool | None = None   # override of the choice of `_long_ranges`
         self.graph_max_ranges_small = 12
         self.graph_blocks_per_sm_small = 1
         self.graph_blocks_per_sm_large = 2
@@ -291,7 +292,8 @@ class CudaOps:
             role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue or the softmax",
                     4: "the producer's drain or the wait for the output", 5: "the MMA issuer (P)",
                     6: "the meeting of a row's two softmax threads",
-                    7: "a weight ring of a few-token product"}.get(code, f"code {code}")
+                    7: "a weight ring of a few-token product",
+                    8: "the key tiles of the decode attention"}.get(code, f"code {code}")
             raise KernelError(f"a kernel gave up waiting in {role}; its output is invalid")
 
     # -- inputs that may still be an unevaluated norm (parts/norm.py: PendingNorm)
@@ -618,13 +620,26 @@ class CudaOps:
                         out, cluster, tables, raw):
         cos, sin = tables if tables is not None else (None, None)
         self._check_limits(cache, tables)
+        # blocks that walk many key tiles each (a large batch) get their tiles by TMA
+        fed = self._long_ranges(batch, num_kv_heads)
+        if fed:
+            self._tc_pending = True
         check(self.lib.mb_paged_attention_decode_cluster(
             _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
             cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
             qkv.shape[0], batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim,
             cache.page_size, float(scale), int(window), cluster, _ptr(cos), _ptr(sin), int(raw),
-            int(cache.write), self._stream()), "paged_attention (decode clusters)")
+            int(cache.write), cache.k.shape[0] if fed else 0, _ptr(self._error_word()) if fed else None,
+            self._stream()), "paged_attention (decode clusters)")
         self.launches += 1
+
+    def _long_ranges(self, batch, num_kv_heads) -> bool:
+        """Whether the blocks of the cluster decode kernel will walk many key tiles each:
+        the batch alone brings more (sequence, KV head) pairs than `graph_small_rows`, so
+        that few key ranges per pair fill the device."""
+        if self.decode_long_ranges is not None:
+            return bool(self.decode_long_ranges)
+        return batch.num_seqs * num_kv_heads > 2 * self.graph_small_rows
 
     @staticmethod
     def _cluster_of(splits: int) -> int:

@@ -582,7 +582,7 @@ ATTENTION_CASES = [
 def attention_close(got, want, dtype, kernel):
     """The tensor-core kernels round the probabilities to bfloat16 before P.V and the result
     once more: two roundings of 2^-8, against one for the CUDA-core kernel."""
-    if kernel in ("mma", "tcgen05", "clusters"):
+    if kernel in ("mma", "tcgen05", "clusters", "clusters-tma"):
         err = float((got.double() - want.double()).abs().max()) / float(want.abs().max())
         assert err <= 2 * 2.0 ** -8, f"attention (mma): relative error {err:.3e}"
     else:
@@ -591,8 +591,8 @@ def attention_close(got, want, dtype, kernel):
 
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
                                           ("mma", torch.bfloat16), ("tcgen05", torch.bfloat16),
-                                          ("clusters", torch.bfloat16)],
-                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05", "bf16-clusters"])
+                                          ("clusters", torch.bfloat16), ("clusters-tma", torch.bfloat16)],
+                         ids=["f32", "bf16", "bf16-mma", "bf16-tcgen05", "bf16-clusters", "bf16-clusters-tma"])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("case", range(len(ATTENTION_CASES)), ids=lambda i: f"case{i}")
 def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
@@ -605,15 +605,19 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     if kernel == "tcgen05" and not ops.lib.mb_attention_tcgen05_supports(
             d, page, n_q, n_kv, (n_q + 2 * n_kv) * d):
         pytest.skip("left to the other attention kernels")
-    if kernel == "clusters" and not (ops.lib.mb_attention_mma_supports(d)
-                                     and max(q_lens) * (n_q // n_kv) <= 16):
+    if kernel in ("clusters", "clusters-tma") and not (ops.lib.mb_attention_mma_supports(d)
+                                                       and max(q_lens) * (n_q // n_kv) <= 16):
         pytest.skip("the cluster kernel is for decode-like batches of head size 64 or 128")
+    if kernel == "clusters-tma":
+        if d != 64 or not 8 <= page <= 64:
+            pytest.skip("the TMA-fed form is for head size 64 and pages of 8 to 64 tokens")
+        ops.decode_long_ranges = True      # the form that large batches take
     # for the tensor-memory kernel the split is the number of CTAs that share a row tile, for
     # the decode clusters the number of blocks of a (sequence, KV head)
     clusters = (None,)
     if kernel == "tcgen05":
         clusters = (1,) if splits == 1 else (2, 4)
-    elif kernel == "clusters":
+    elif kernel in ("clusters", "clusters-tma"):
         clusters = (1,) if splits == 1 else (2, 4, 8)
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 5
     drop = [max(0, kv - q - window + 1) for q, kv in zip(q_lens, kv_lens)] if window else None
@@ -640,11 +644,11 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
     twin.paged_attention(qkv_twin, n_q, n_kv, d, batch, cache_twin, d ** -0.5, window, want)
     for cluster in clusters:
         ops.prompt_cluster = cluster
-        if kernel == "clusters":
+        if kernel in ("clusters", "clusters-tma"):
             ops.decode_splits = cluster
         got = torch.zeros_like(want)
         ops.paged_attention(qkv, n_q, n_kv, d, batch, cache, d ** -0.5, window, got,
-                            kernel=None if kernel == "clusters" else kernel)
+                            kernel=None if kernel in ("clusters", "clusters-tma") else kernel)
         ops.check_errors()
         assert torch.isfinite(got[live]).all(), "attention read a poisoned slot"
         attention_close(got[live], want[live], dtype, kernel)
