@@ -229,8 +229,15 @@ __device__ __forceinline__ void store_partial(float* red, const float (&acc)[NT]
 // EPI: 0 = bfloat16 out, 1 = float32 out, 2 = swiglu (bfloat16 out; the row tiles of a
 // block alternate gate / up, and `half_n` is the width of the result), 3 = added into the
 // float32 rows of `out`.
+// Threads a block of this kernel may have: eight tokens per block leave room for 1024 (the
+// gated form is built for three blocks of 448 per SM); sixteen tokens per block keep twice
+// the activation fragments and sums in registers and get half the threads.
+constexpr int skinny_max_threads(int NT, int EPI, bool NORM) {
+    return NT == 2 ? 512 : (NORM ? 512 : (EPI == 2 ? 448 : 1024));
+}
+
 template <int NT, int EPI, bool NORM>
-__global__ void __launch_bounds__(NORM ? 512 : (EPI == 2 ? 448 : 1024), (EPI == 2 && !NORM) ? 3 : 1)
+__global__ void __launch_bounds__(skinny_max_threads(NT, EPI, NORM), (NT == 1 && EPI == 2 && !NORM) ? 3 : 1)
 skinny_gemm_kernel(SkinnyInput in_all,
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ bias, void* __restrict__ out_all,
@@ -757,11 +764,18 @@ MB_EXPORT int mb_gemm_skinny_set_slices(int plain, int qkv) {
     return MB_OK;
 }
 
-// At most 16 tokens: beyond that the activations no longer come cheaply through L1 and the
-// library product (or a tensor-core tile kernel) is the better tool.
+// At most 16 tokens: a block takes 8 or 16 of them and uses its weight fragments for each.
+// (32 tokens per block, and 33 to 64 tokens as two groups of blocks that both stream the
+// matrix, were built and measured at the 0.5B widths: a decode step of 32 sequences took 1.49 ms
+// against 1.18 ms with the library product and separate norm and gate kernels, one of 64
+// took 2.33 against 1.40. Each warp's MMAs then repeat per token tile while the weights no
+// longer bound the time, so beyond 16 tokens the library product is the better tool.)
 MB_EXPORT int mb_gemm_skinny_supports(int T, int N, int K) {
     return T >= 1 && T <= 16 && K > 0 && K % 32 == 0 && N > 0 && N % 16 == 0;
 }
+
+// Tokens per block in units of eight for a product of T tokens.
+static int skinny_nt(int T) { return T <= 8 ? 1 : 2; }
 
 #define MB_SK_NT_SWITCH(NTV, ...)                            \
     if (NTV <= 1) { constexpr int NT = 1; __VA_ARGS__ }        \
@@ -885,31 +899,30 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
     cudaStream_t s = (cudaStream_t)stream;
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
     // large matrices: weights by TMA (`error` as for mb_gemm_tcgen05, code 7; null: never)
-    if (g_fed_min_elements > 0 && (long long)N * K >= g_fed_min_elements) {
+    if (g_fed_min_elements > 0 && (long long)N * K >= g_fed_min_elements && T <= 16) {
         const int rc_fed = launch_fed(in, w, bias, out, mode, T, N, K, 0, next_w, next_x, next_ss, error, s);
         if (rc_fed != MB_ERR_UNSUPPORTED_SIZE) return rc_fed;
     }
-    const int nt = (T + 7) / 8;
+    const int nt = skinny_nt(T);
     const int tiles = N / 16;
     // (blocks if K were not shared: one per row tile once a tile has 8 warps or more)
     const int slices = norm_w ? 1 : pick_slices(tiles, K / 32, g_slices_plain);
-    const int ksplit = pick_ksplit(tiles * slices, (K / 32 + slices - 1) / slices, norm_w ? 16 : 32);
+    const int ksplit = pick_ksplit(tiles * slices, (K / 32 + slices - 1) / slices,
+                                   (nt == 2 || norm_w) ? 16 : 32);
     const int rowt = ksplit >= 8 ? 1 : 8 / ksplit;
     const int blocks = (tiles + rowt - 1) / rowt;
     const int threads = rowt * ksplit * 32;
     const int half_n = 0;
     int rc = MB_OK;
-    // eight tokens per block; further tokens go to further blocks along z (measured on B200:
-    // sixteen tokens in one block need more registers than a 1024-thread block has, and the
-    // spills made the sixteen-token step 1.7 times the eight-token step)
-    const int groups = nt;
-    {
-        constexpr int NT = 1;
+    // 8 or 16 tokens per block (a block of 16 has fewer threads, see skinny_max_threads:
+    // sixteen tokens in a 1024-thread block spilled)
+    const int groups = (T + 8 * nt - 1) / (8 * nt);
+    MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * (ksplit + slices - 1) * 16 * 8 * NT * sizeof(float);
         if (mode == 0) MB_SK_LAUNCH_GEMM(0);
         else if (mode == 1) MB_SK_LAUNCH_GEMM(1);
         else MB_SK_LAUNCH_GEMM(3);
-    }
+    })
     return rc != MB_OK ? rc : launch_status();
 }
 
@@ -922,12 +935,12 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
     const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
-    if (g_fed_min_elements > 0 && 2ll * width * K >= (g_fed_min_elements > g_fed_min_gated || g_fed_min_elements < 1024 ? g_fed_min_elements : g_fed_min_gated)) {
+    if (T <= 16 && g_fed_min_elements > 0 && 2ll * width * K >= (g_fed_min_elements > g_fed_min_gated || g_fed_min_elements < 1024 ? g_fed_min_elements : g_fed_min_gated)) {
         const int rc_fed = launch_fed(in, w, nullptr, out, 0, T, 2 * width, K, width / 16, nullptr, nullptr,
                                       nullptr, error, s);
         if (rc_fed != MB_ERR_UNSUPPORTED_SIZE) return rc_fed;
     }
-    const int nt = (T + 7) / 8;
+    const int nt = skinny_nt(T);
     const int pairs = width / 16;
     // (at most 14 warps: the gated kernel is built for three blocks of 448 threads per SM, so
     // that all its blocks are resident beside the blocks of the kernel in front)
@@ -944,12 +957,11 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     float* next_ss = nullptr;
     const int slices = 1;
     int rc = MB_OK;
-    const int groups = nt;
-    {
-        constexpr int NT = 1;
+    const int groups = (T + 8 * nt - 1) / (8 * nt);
+    MB_SK_NT_SWITCH(nt, {
         const size_t smem = (size_t)rowt * ksplit * 16 * 8 * NT * sizeof(float);
         MB_SK_LAUNCH_GEMM(2);
-    }
+    })
     return rc != MB_OK ? rc : launch_status();
 }
 
