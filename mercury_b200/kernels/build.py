@@ -27,7 +27,7 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
-SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_simt.cu", "attention_mma.cu", "attention_tcgen05.cu", "sampling.cu"]
+SOURCES = ["elementwise.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_pair.cu", "attention_simt.cu", "attention_mma.cu", "attention_tcgen05.cu", "sampling.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
               "-fvisibility=hidden", "--expt-relaxed-constexpr"]

@@ -62,6 +62,10 @@ _SIGNATURES = {
                                  c_longlong, c_void_p],
     "mb_gemm_tcgen05_persistent": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p],
+    "mb_gemm_pair_supports": [c_int, c_int, c_int],
+    "mb_gemm_pair_tiles": [c_int, c_int],
+    "mb_gemm_pair": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                     c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "mb_paged_attention_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],

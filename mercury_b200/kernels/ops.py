@@ -76,6 +76,11 @@ class CudaOps:
         # ... and from this many on, weights come by TMA (gemm_skinny.cu: skinny_fed_kernel);
         # only those launches have a wait that can give up and so an error word to look at
         self.fed_min_elements = 12 * 1024 * 1024
+        # The gated product of a prompt step runs on pairs of SMs (gemm_pair.cu) from this K
+        # on; below it the one-CTA persistent kernel is level or ahead (measured on B200 at
+        # 2048 tokens: K 896, 34 us one CTA against 35 us pairs; K 1536, 91 against 86; at 4096
+        # tokens, K 3584 and 2 x 18944 rows, 1515 against 1028)
+        self.pair_min_k = 1024
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head sizes 64 and
         # 128, the mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
@@ -437,9 +442,16 @@ class CudaOps:
         if (self.gemm in ("tcgen05", "auto") and x.dtype == torch.bfloat16
                 and weight.dtype == torch.bfloat16 and m >= 256 and width % 8 == 0
                 and self.lib.mb_gemm_tcgen05_supports(m, width, k)):
-            check(self.lib.mb_gemm_tcgen05_persistent(_ptr(x), _ptr(weight), None, _ptr(out), 2, m,
-                                                      width, k, _ptr(self._error_word()),
-                                                      self._stream()), "linear_swiglu (tcgen05)")
+            if k >= self.pair_min_k and self.lib.mb_gemm_pair_supports(m, width, k):
+                # pairs of SMs sharing one 256-row MMA: a CTA loads a third less per output
+                check(self.lib.mb_gemm_pair(_ptr(x), _ptr(weight), None, _ptr(out), 2, m, width, k,
+                                            None, 0, 0.0, 0, None, None, None, None,
+                                            _ptr(self._error_word()), self._stream()),
+                      "linear_swiglu (tcgen05 pairs)")
+            else:
+                check(self.lib.mb_gemm_tcgen05_persistent(_ptr(x), _ptr(weight), None, _ptr(out), 2, m,
+                                                          width, k, _ptr(self._error_word()),
+                                                          self._stream()), "linear_swiglu (tcgen05)")
             self.launches += 1
             self._tc_pending = True
             return

@@ -197,6 +197,94 @@ def test_tcgen05_persistent_plain_product(twin, m, n, k, mode, out_dtype):
     close(got, want, out_dtype, terms=k)
 
 
+@pytest.mark.parametrize("m", [256, 300, 2048, 2049])
+@pytest.mark.parametrize("k", [896, 1536, 3584])
+@pytest.mark.parametrize("width", [4864, 200], ids=["w4864", "w200"])
+@pytest.mark.parametrize("scaled", [False, True], ids=["plain", "row-scaled"])
+def test_pair_gated_product(m, k, width, scaled):
+    """The product on pairs of SMs (one 256-row MMA per two CTAs) with the SiLU gate in its
+    epilogue, called directly: full and ragged row tiles (the odd CTA of the last pair may own
+    no row at all), widths that are no multiple of the tile, three lengths of the sum, and
+    with the rows scaled by 1/rms from sums of squares that come in pieces."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 71)
+    w = rand((2 * width, k), torch.bfloat16, 72, 0.05)
+    got = torch.zeros((m, width), dtype=torch.bfloat16, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pieces = torch.rand((m, 5), generator=torch.Generator().manual_seed(3)).cuda() * 300 + 20 if scaled else None
+    rc = lib.mb_gemm_pair(x.data_ptr(), w.data_ptr(), None, got.data_ptr(), 2, m, width, k,
+                          pieces.data_ptr() if scaled else None, 5 if scaled else 0, 1e-5, 640,
+                          None, None, None, None, error.data_ptr(),
+                          torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert int(error.item()) == 0, "a bounded wait in the kernel ran out"
+    scale = torch.rsqrt(pieces.double().sum(1) / 640 + 1e-5)[:, None] if scaled else 1.0
+    gate = (x.double() @ w[:width].double().T) * scale
+    up = (x.double() @ w[width:].double().T) * scale
+    want = gate * torch.sigmoid(gate) * up
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert err <= 3 * 2.0 ** -8, err
+    loose = (got.double() - want).abs() <= 2.0 ** -6 * want.abs() + 2e-3 * want.abs().max()
+    assert bool(loose.all())
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 1152, 896), (300, 896, 4864), (2049, 200, 1536), (2048, 4608, 320),
+                                   (129, 264, 64), (4096, 896, 896)])
+def test_pair_plain_product(twin, m, n, k):
+    """The same kernel's plain mode (bias, bfloat16 out): tiles of 128 and of 256 columns."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 73)
+    w = rand((n, k), torch.bfloat16, 74, 0.1)
+    bias = rand((n,), torch.bfloat16, 75)
+    got = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.mb_gemm_pair(x.data_ptr(), w.data_ptr(), bias.data_ptr(), got.data_ptr(), 0, m, n, k,
+                          None, 0, 0.0, 0, None, None, None, None, error.data_ptr(),
+                          torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and int(error.item()) == 0
+    want = torch.empty_like(got)
+    twin.linear(x, w, bias, want)
+    close(got, want, torch.bfloat16, terms=k)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 896, 896), (300, 896, 4864), (2049, 200, 1536), (2048, 4608, 320),
+                                   (129, 264, 64)])
+@pytest.mark.parametrize("next_norm", [False, True], ids=["add", "add+next-norm"])
+def test_pair_residual_product(m, n, k, next_norm):
+    """The same kernel adding into the float32 stream, and leaving what the product after the
+    next norm takes: the stream times that norm's weight in bfloat16, and the rows' sums of
+    squares in pieces that add up."""
+    from mercury_b200.kernels import library
+
+    lib = library.load()
+    x = rand((m, k), torch.bfloat16, 76)
+    w = rand((n, k), torch.bfloat16, 77, 0.1)
+    h = rand((m, n), torch.float32, 78)
+    h0 = h.clone()
+    norm_w = rand((n,), torch.bfloat16, 79) if next_norm else None
+    pieces = lib.mb_gemm_pair_tiles(m, n)
+    next_x = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    next_ss = torch.full((m, pieces), float("nan"), device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.mb_gemm_pair(x.data_ptr(), w.data_ptr(), None, None, 3, m, n, k, None, 0, 0.0, 0,
+                          h.data_ptr(), norm_w.data_ptr() if next_norm else None,
+                          next_x.data_ptr() if next_norm else None,
+                          next_ss.data_ptr() if next_norm else None, error.data_ptr(),
+                          torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and int(error.item()) == 0
+    want = h0.double() + x.double() @ w.double().T
+    assert float((h.double() - want).abs().max() / want.abs().max()) <= 2 * k ** 0.5 * 2.0 ** -24
+    if next_norm:
+        scaled = want * norm_w.double()
+        assert float((next_x.double() - scaled).abs().max() / scaled.abs().max()) <= 2.0 ** -8
+        sums = (want * want).sum(1)
+        assert float((next_ss.double().sum(1) - sums).abs().max() / sums.max()) <= 1e-5
+
+
 def test_tcgen05_refuses_an_odd_k():
     from mercury_b200.kernels import library
 
