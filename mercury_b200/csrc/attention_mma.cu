@@ -738,14 +738,17 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // tiles [window_lo, window_lo + window_tiles) have their table entries in page_s
     // (pages of 2 or more tokens: at least 8 tiles, which covers the stages filled up front;
     // pages larger than a tile share an entry between tiles, two entries are kept spare)
-    const int window_tiles = page_size >= MMA_BN ? PAGE_WINDOW - 2 : PAGE_WINDOW / (MMA_BN / page_size);
+    // (a page holds a power of two of tokens: shifts and masks, since an integer division
+    // costs a thread some hundred cycles and the tile loop had four of them per tile)
+    const int page_shift = 31 - __clz(page_size), page_mask = page_size - 1;
+    const int window_tiles = page_size >= MMA_BN ? PAGE_WINDOW - 2 : PAGE_WINDOW >> (6 - page_shift);
     int window_lo = t_lo;
     auto fill_window = [&](int first_tile) {
         window_lo = first_tile;
-        const int base = (first_tile * MMA_BN) / page_size;
+        const int base = (first_tile * MMA_BN) >> page_shift;
         for (int e = tid; e < PAGE_WINDOW; e += 128) {
             const int column = base + e;
-            page_s[e] = (column < max_pages && (int64_t)column * page_size < kv_len)
+            page_s[e] = (column < max_pages && ((int64_t)column << page_shift) < kv_len)
                             ? table_page(table, seq, max_pages, column) : -1;
         }
     };
@@ -768,33 +771,33 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             // the tile's copies are dealt out over the four warps (a copy costs its thread
             // some 60 cycles): warp w takes every fourth of them, one lane each, and
             // announces its own bytes; the stage is full when all four have and all landed
-            const int copies = MMA_BN / box;
+            const int copies = MMA_BN >> box_shift;
             const int copy = warp + 4 * lane;
             int page = -1, row = 0;
             if (copy < copies) {
-                const int key0 = kt * MMA_BN + copy * box;
-                if (key0 < kv_len) page = page_s[key0 / page_size - (window_lo * MMA_BN) / page_size];
-                if (page >= 0) row = (page * n_kv + kvh) * page_size + key0 % page_size;
+                const int key0 = kt * MMA_BN + (copy << box_shift);
+                if (key0 < kv_len) page = page_s[(key0 >> page_shift) - ((window_lo * MMA_BN) >> page_shift)];
+                if (page >= 0) row = (((page * n_kv + kvh)) << page_shift) + (key0 & page_mask);
             }
             const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
             if (lane == 0) {
                 tile_pages[stage][warp] = valid;
-                mbar_expect_tx(&tile_full[stage], (uint32_t)(__popc(valid) * 2 * box * 128));
+                mbar_expect_tx(&tile_full[stage], (uint32_t)(__popc(valid) << (box_shift + 8)));
             }
             __syncwarp();
             if (page >= 0) {
-                tma_load_2d(k_s + (stage * MMA_BN + copy * box) * D, &map_k, 0, row, &tile_full[stage]);
-                tma_load_2d(v_s + (stage * MMA_BN + copy * box) * D, &map_v, 0, row, &tile_full[stage]);
+                tma_load_2d(k_s + (stage * MMA_BN + (copy << box_shift)) * D, &map_k, 0, row, &tile_full[stage]);
+                tma_load_2d(v_s + (stage * MMA_BN + (copy << box_shift)) * D, &map_v, 0, row, &tile_full[stage]);
             }
             return;
         }
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
-            page = page_s[key / page_size - (window_lo * MMA_BN) / page_size];
+            page = page_s[(key >> page_shift) - ((window_lo * MMA_BN) >> page_shift)];
         const bool valid = page >= 0;
         const int64_t at =
-            valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D : 0;
+            valid ? ((((int64_t)page * n_kv + kvh) << page_shift) + (key & page_mask)) * D : 0;
         __nv_bfloat16* kd = k_s + (stage * MMA_BN + lj) * D;
         __nv_bfloat16* vd = v_s + (stage * MMA_BN + lj) * D;
 #pragma unroll
@@ -825,7 +828,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         new_c = new_idx - new_tok * HC;
         const int key = first_pos + new_tok, kt = key / MMA_BN;
         new_mine = kt >= t_lo && kt < t_hi;
-        if (new_mine && store) new_page = table_page(table, seq, max_pages, key / page_size);
+        if (new_mine && store) new_page = table_page(table, seq, max_pages, key >> page_shift);
     }
     grid_dependency_sync();
 
@@ -897,7 +900,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             if (store) {
                 const int page = new_page;
                 if (page >= 0) {
-                    const int64_t at = (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D;
+                    const int64_t at = ((((int64_t)page * n_kv + kvh) << page_shift) + (key & page_mask)) * D;
                     *reinterpret_cast<uint4*>(k_pages_out + at + c * 8) = klo;
                     *reinterpret_cast<uint4*>(k_pages_out + at + D / 2 + c * 8) = khi;
                     *reinterpret_cast<uint4*>(v_pages_out + at + c * 8) = vlo;
@@ -955,7 +958,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             }
             __syncthreads();   // tile `it` has landed for everyone; the stage of tile it-1 is free
         }
-        if (it >= 1 && !resident) {
+        auto refill = [&]() {
             const int next = it - 1 + STAGES;
             if (next < n_tiles && t_lo + next >= window_lo + window_tiles) {
                 // the window has been used up: everyone is past the barrier above, so nobody
@@ -965,7 +968,8 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             }
             if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
             asm volatile("cp.async.commit_group;\n" ::);
-        }
+        };
+        if (!FED && it >= 1 && !resident) refill();
         __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
         __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
         if (raw && kt >= t_new) {
@@ -1011,6 +1015,9 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             mma_bf16(s[0], qf[ks], b[0], b[1]);
             mma_bf16(s[1], qf[ks], b[2], b[3]);
         }
+        // FED: the next tile's copies are issued here, under the MMAs just issued (their
+        // issue is some hundred cycles of one lane per warp and the scores are not needed yet)
+        if (FED && it >= 1) refill();
         float m_new[2] = {m[0], m[1]};
         // Every key of this warp's 16 is seen by every row when the newest of them is no later
         // than the earliest position of the step, real, and inside every row's window (rows
