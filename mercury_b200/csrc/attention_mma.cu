@@ -658,7 +658,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // (large batches) the per-thread copies were the limit: issuing a tile's 8 cp.async took a
 // thread 780 of the 2080 cycles a tile took. Head size 64, pages of 8 tokens or more.
 template <int D, bool FED>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(FED ? 160 : 128)
 attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
                                 const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
@@ -675,7 +675,8 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // the new values into the pages (if `store`) and into its own tiles. The product in front
     // then needs no block per head, and every tile of the pages can be copied before the wait.
     constexpr int CH = D / 8;
-    constexpr int STAGES = D == 64 ? 5 : 3;
+    // (FED: one stage per warp, see the tile loop)
+    constexpr int STAGES = FED ? 4 : (D == 64 ? 5 : 3);
     __nv_bfloat16* k_pages_out = const_cast<__nv_bfloat16*>(k_pages);
     __nv_bfloat16* v_pages_out = const_cast<__nv_bfloat16*>(v_pages);
     __shared__ __align__(16) __nv_bfloat16 new_k[16][D]; // this step's keys, rotated
@@ -703,8 +704,11 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // copies (with 16 tiles per block that trip, not the copies, set the kernel's time).
     constexpr int PAGE_WINDOW = 256;
     __shared__ int page_s[PAGE_WINDOW];
-    __shared__ uint64_t tile_full[STAGES];       // FED: a stage's copies have landed
-    __shared__ uint32_t tile_pages[STAGES][4];   // FED: which of the stage's pages were there, by issuing warp
+    // FED: the four stages are eight half stages of 32 keys, two per consumer warp
+    constexpr int HALF = MMA_BN / 2, HSTAGES = 2 * STAGES;
+    __shared__ uint64_t tile_full[HSTAGES];      // FED: a half stage's copies have landed
+    __shared__ uint64_t tile_free[HSTAGES];      // FED: its warp has read it
+    __shared__ uint32_t tile_pages[HSTAGES];     // FED: which of its pages were there
     __shared__ int fed_error;                    // FED: a wait gave up (never read by the host:
                                                  // the block then leaves its rows unwritten)
 
@@ -746,51 +750,39 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     auto fill_window = [&](int first_tile) {
         window_lo = first_tile;
         const int base = (first_tile * MMA_BN) >> page_shift;
-        for (int e = tid; e < PAGE_WINDOW; e += 128) {
+        // (FED: by the threads that load neither queries nor new keys, so that all three
+        // trips to L2 are under way at once)
+        for (int e = FED ? tid - 96 : tid; e < PAGE_WINDOW; e += (FED ? 64 : 128)) {
+            if (e < 0) continue;
             const int column = base + e;
             page_s[e] = (column < max_pages && ((int64_t)column << page_shift) < kv_len)
                             ? table_page(table, seq, max_pages, column) : -1;
         }
     };
+    // FED: this form is never launched ahead of the kernel in front (large batches are not
+    // captured with dependent launch), so nothing is gained by putting work before the wait:
+    // it waits first, and then queries, new keys and the block table are fetched side by side
+    // by different warps, with one barrier of the block before the loop instead of two.
+    if (FED) grid_dependency_sync();
     fill_window(t_lo);
     if (FED && tid == 0) {
-        for (int st = 0; st < STAGES; ++st) mbar_init(&tile_full[st], 4);   // one arrival per warp
+        for (int st = 0; st < HSTAGES; ++st) {
+            mbar_init(&tile_full[st], 1);   // the arrival that announces the bytes
+            mbar_init(&tile_free[st], 1);   // lane 0 of the warp that read it
+        }
         fed_error = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
+    if (!FED) __syncthreads();
 
     // each thread copies half a key row of K and of V
     const int lj = tid >> 1, lc0 = (tid & 1) * (CH / 2);
     // FED: a copy brings `box` keys (a page, or 64 keys of a larger one)
-    const int box = page_size < MMA_BN ? page_size : MMA_BN;
+    const int box = FED ? (page_size < HALF ? page_size : HALF) : (page_size < MMA_BN ? page_size : MMA_BN);
     const int box_shift = 31 - __clz(box);
     auto load_tile = [&](int stage, int kt) {
-        if (FED) {
-            // the tile's copies are dealt out over the four warps (a copy costs its thread
-            // some 60 cycles): warp w takes every fourth of them, one lane each, and
-            // announces its own bytes; the stage is full when all four have and all landed
-            const int copies = MMA_BN >> box_shift;
-            const int copy = warp + 4 * lane;
-            int page = -1, row = 0;
-            if (copy < copies) {
-                const int key0 = kt * MMA_BN + (copy << box_shift);
-                if (key0 < kv_len) page = page_s[(key0 >> page_shift) - ((window_lo * MMA_BN) >> page_shift)];
-                if (page >= 0) row = (((page * n_kv + kvh)) << page_shift) + (key0 & page_mask);
-            }
-            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-            if (lane == 0) {
-                tile_pages[stage][warp] = valid;
-                mbar_expect_tx(&tile_full[stage], (uint32_t)(__popc(valid) << (box_shift + 8)));
-            }
-            __syncwarp();
-            if (page >= 0) {
-                tma_load_2d(k_s + (stage * MMA_BN + (copy << box_shift)) * D, &map_k, 0, row, &tile_full[stage]);
-                tma_load_2d(v_s + (stage * MMA_BN + (copy << box_shift)) * D, &map_v, 0, row, &tile_full[stage]);
-            }
-            return;
-        }
+        if (FED) return;     // (the producer warp's copies: fetch_half below)
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
@@ -808,12 +800,55 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         }
     };
 
+    // FED: the producer warp's copies of a round of half tiles (32 keys each; half tile h of the
+    // block belongs to consumer warp h % 4, whose two half stages alternate, and round r is
+    // the half tiles 4 r .. 4 r + 3). One lane per page (or half page) and half tile: a copy
+    // costs its warp some hundred cycles however many lanes issue it, so a round goes out in
+    // one instruction per tensor. `reuse`: wait until each stage's warp has read what was there.
+    const int keys_end = kv_len < t_hi * MMA_BN ? kv_len : t_hi * MMA_BN;
+    const int n_half = FED && keys_end > t_lo * MMA_BN ? (keys_end - t_lo * MMA_BN + HALF - 1) / HALF : 0;
+    auto fetch_round = [&](int r, bool reuse) -> bool {
+        const int copies_shift = 5 - box_shift;              // copies per half tile: 1, 2 or 4
+        const int w = lane >> copies_shift, piece = lane & ((1 << copies_shift) - 1);
+        const int h = 4 * r + w;
+        const bool active = w < 4 && h < n_half;
+        const int hs = (w & 3) + 4 * (r & 1);
+        bool ok = true;
+        if (active && reuse)
+            ok = mbar_wait(&tile_free[hs], (uint32_t)(((r >> 1) - 1) & 1), error ? error : &fed_error, 8);
+        if (!__all_sync(0xffffffffu, ok)) return false;
+        int page = -1, row = 0;
+        if (active) {
+            const int key0 = t_lo * MMA_BN + h * HALF + (piece << box_shift);
+            if (key0 < kv_len) {
+                const int column = key0 >> page_shift;
+                const int e = column - ((window_lo * MMA_BN) >> page_shift);
+                // (beyond the window of the table in shared memory: from the table itself)
+                page = e < PAGE_WINDOW ? page_s[e]
+                                       : (column < max_pages ? table_page(table, seq, max_pages, column) : -1);
+            }
+            if (page >= 0) row = ((page * n_kv + kvh) << page_shift) + (key0 & page_mask);
+        }
+        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+        if (active && piece == 0) {
+            const unsigned mine = (valid >> (w << copies_shift)) & ((1u << (1 << copies_shift)) - 1u);
+            tile_pages[hs] = mine;
+            mbar_expect_tx(&tile_full[hs], (uint32_t)(__popc(mine) << (box_shift + 8)));
+        }
+        __syncwarp();
+        if (page >= 0) {
+            tma_load_2d(k_s + (hs * HALF + (piece << box_shift)) * D, &map_k, 0, row, &tile_full[hs]);
+            tma_load_2d(v_s + (hs * HALF + (piece << box_shift)) * D, &map_v, 0, row, &tile_full[hs]);
+        }
+        return true;
+    };
+
     // ---- before the wait: the first STAGES tiles, one copy group each (an empty group for a
     // tile that is not there or holds keys of this step)
 #pragma unroll
     for (int st = 0; st < STAGES; ++st) {
         const int kt = t_lo + st;
-        if (kt < t_hi && (kt < t_new || raw)) load_tile(st, kt);
+        if (!FED && kt < t_hi && (kt < t_new || raw)) load_tile(st, kt);
         asm volatile("cp.async.commit_group;\n" ::);
     }
     // raw: which piece of this step's keys and values this thread will turn and store (threads
@@ -823,14 +858,14 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     const int new_idx = (tid + 128 - (16 * HC) % 128) % 128;
     int new_tok = 0, new_c = 0, new_page = -1;
     bool new_mine = false;
-    if (raw && new_idx < q_len * HC) {
+    if (raw && tid < 128 && new_idx < q_len * HC) {
         new_tok = new_idx / HC;
         new_c = new_idx - new_tok * HC;
         const int key = first_pos + new_tok, kt = key / MMA_BN;
         new_mine = kt >= t_lo && kt < t_hi;
         if (new_mine && store) new_page = table_page(table, seq, max_pages, key >> page_shift);
     }
-    grid_dependency_sync();
+    if (!FED) grid_dependency_sync();
 
     // ---- after it: the queries, and the tiles of the first STAGES that had to wait
     if (!raw) {
@@ -846,7 +881,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
 #pragma unroll
         for (int st = 0; st < STAGES; ++st) {
             const int kt = t_lo + st;
-            if (kt < t_hi && kt >= t_new) load_tile(st, kt);
+            if (!FED && kt < t_hi && kt >= t_new) load_tile(st, kt);
         }
     } else {
         // (the angles are read beside the values they turn: the same trip to L2)
@@ -911,18 +946,32 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     }
     asm volatile("cp.async.commit_group;\n" ::);
 
-    int pos[2];
-    bool row_ok[2];
+    // The products run transposed: S^T = K Q^T and O^T = V^T P^T, keys (or the head's
+    // dimensions) along the 16 rows of an MMA and the step's query rows along its 8 columns.
+    // A decode step of a group of up to 8 query heads then needs one column tile where the
+    // untransposed form spent a 16-row tile on 7 rows, and mma.sync is the scarce unit here:
+    // an m16n8k16 issues about every 40 cycles per scheduler on this GPU, so a 64-key tile cost
+    // a warp some 700 cycles of MMAs alone. A thread holds, of a 16 x 8 piece, rows g and g + 8
+    // (keys) and columns 2 t4 and 2 t4 + 1 (query rows).
+    const bool two = rows > 8;               // a second column tile of query rows
+    int pos[2][2];
+    bool row_ok[2][2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = g + h * 8;
-        row_ok[h] = r < rows;
-        pos[h] = first_pos + r / group;
+    for (int nr = 0; nr < 2; ++nr) {
+#pragma unroll
+        for (int z = 0; z < 2; ++z) {
+            const int r = nr * 8 + 2 * t4 + z;
+            row_ok[nr][z] = r < rows;
+            pos[nr][z] = first_pos + r / group;
+        }
     }
-    float o[D / 8][4];
+    float o[D / 16][2][4];                   // O^T: [dimension tile][row tile]
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    for (int i = 0; i < D / 16; ++i) {
+#pragma unroll
+        for (int nr = 0; nr < 2; ++nr) o[i][nr][0] = o[i][nr][1] = o[i][nr][2] = o[i][nr][3] = 0.f;
+    }
+    float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     const float scale2 = scale * 1.4426950408889634f;
 
     // raw, and no more tiles than stages: every tile was asked for before the wait and none
@@ -930,27 +979,273 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     const bool resident = !FED && raw && n_tiles <= STAGES;
     if (resident) asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
-    uint32_t qf[D / 16][4];
+    if (FED && warp == 4) {
+        // the first two rounds (the block table and the barriers are there now)
+        fetch_round(0, false);
+        if (n_half > 4) fetch_round(1, false);
+    }
+    uint32_t qf[D / 16][4];                  // Q as the B operand: [0], [1] rows 0..7, [2], [3] rows 8..15
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
-        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int c = ks * 2 + (lane >> 4);
+        const int r = (lane & 7) + (lane >> 4) * 8;
+        const int c = ks * 2 + ((lane >> 3) & 1);
         ldmatrix_x4(qf[ks], q_s + r * D + ((c ^ (r & 7)) * 8));
+    }
+
+    // scores of the 16 keys from row `j0` of a tile on
+    auto unit_scores = [&](const __nv_bfloat16* kt_s, int j0, float (&sc)[2][4]) {
+#pragma unroll
+        for (int nr = 0; nr < 2; ++nr) sc[nr][0] = sc[nr][1] = sc[nr][2] = sc[nr][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t a[4];
+            const int j = j0 + (lane & 15);
+            const int c = ks * 2 + (lane >> 4);
+            ldmatrix_x4(a, kt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(sc[0], a, qf[ks][0], qf[ks][1]);
+            if (two) mma_bf16(sc[1], a, qf[ks][2], qf[ks][3]);
+        }
+    };
+    // scale and mask the unit's scores (keys from `key_lo` on) and raise `top` to their maxima.
+    // Every key of the 16 is seen by every row when the newest of them is no later than the
+    // earliest position of the step, real, and inside every row's window (rows beyond the
+    // step's are zeros and go nowhere): then nothing is masked one by one.
+    auto unit_mask = [&](float (&sc)[2][4], int key_lo, float (&top)[2][2]) {
+        const bool plain = key_lo + 15 <= first_pos && key_lo + 15 < kv_len &&
+                           (window <= 0 || key_lo > p_max - window);
+#pragma unroll
+        for (int nr = 0; nr < 2; ++nr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int z = e & 1;
+                bool seen = true;
+                if (!plain) {
+                    const int key = key_lo + g + (e >> 1) * 8;
+                    seen = row_ok[nr][z] && key <= pos[nr][z] && key < kv_len;
+                    if (window > 0) seen = seen && key > pos[nr][z] - window;
+                }
+                sc[nr][e] = seen ? sc[nr][e] * scale2 : -INFINITY;
+                top[nr][z] = fmaxf(top[nr][z], sc[nr][e]);
+            }
+        }
+    };
+    // the maxima of a row over the keys of all lanes that hold it (lanes of one t4)
+    auto across_keys_max = [&](float (&top)[2][2]) {
+#pragma unroll
+        for (int nr = 0; nr < 2; ++nr) {
+#pragma unroll
+            for (int z = 0; z < 2; ++z) {
+                top[nr][z] = fmaxf(top[nr][z], __shfl_xor_sync(0xffffffffu, top[nr][z], 4));
+                top[nr][z] = fmaxf(top[nr][z], __shfl_xor_sync(0xffffffffu, top[nr][z], 8));
+                top[nr][z] = fmaxf(top[nr][z], __shfl_xor_sync(0xffffffffu, top[nr][z], 16));
+            }
+        }
+    };
+    // probabilities on the rows' maxima, their sums, and O^T += V^T P^T for the unit
+    auto unit_values = [&](float (&sc)[2][4], const __nv_bfloat16* vt_s, int j0) {
+        uint32_t pt[2][2];
+#pragma unroll
+        for (int nr = 0; nr < 2; ++nr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int z = e & 1;
+                const float p = m[nr][z] > -INFINITY ? fast_exp2(sc[nr][e] - m[nr][z]) : 0.f;
+                sc[nr][e] = p;
+                l[nr][z] += p;
+            }
+            // P^T as the B operand: the 8 x 8 pieces [keys][rows] turned into [rows][keys]
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t piece = pack_bf16(sc[nr][2 * half], sc[nr][2 * half + 1]);
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(pt[nr][half]) : "r"(piece));
+            }
+        }
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2) {
+            uint32_t a[4];
+            const int j = j0 + (lane & 7) + (lane >> 4) * 8;
+            const int c = d2 * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4_trans(a, vt_s + j * D + ((c ^ (j & 7)) * 8));
+            mma_bf16(o[d2][0], a, pt[0][0], pt[0][1]);
+            if (two) mma_bf16(o[d2][1], a, pt[1][0], pt[1][1]);
+        }
+    };
+
+    if (resident) {
+        // Every tile is in shared memory. The warps then share the keys by runs instead of
+        // every warp taking a quarter of every tile: a warp takes n_tiles consecutive units
+        // of 16 keys, computes all its scores, goes through the softmax once and then through
+        // P V, so that its MMAs are independent chains and nothing is rescaled.
+        if (t_new < t_hi) {
+            // this step's keys and values take their rows of their tiles (the copies left zeros)
+            for (int idx = tid; idx < q_len * CH; idx += 128) {
+                const int tok = idx / CH, c = idx - tok * CH;
+                const int key = first_pos + tok, kt = key / MMA_BN;
+                if (kt < t_lo || kt >= t_hi) continue;
+                const int row = key % MMA_BN;
+                const int sw = (c ^ (row & 7)) * 8;
+                *reinterpret_cast<uint4*>(k_s + ((kt - t_lo) * MMA_BN + row) * D + sw) =
+                    *reinterpret_cast<const uint4*>(&new_k[tok][c * 8]);
+                *reinterpret_cast<uint4*>(v_s + ((kt - t_lo) * MMA_BN + row) * D + sw) =
+                    *reinterpret_cast<const uint4*>(&new_v[tok][c * 8]);
+            }
+            __syncthreads();
+        }
+        constexpr int UPW = STAGES;          // units per warp: n_tiles of them, at most STAGES
+        const int u_lo = warp * n_tiles;
+        float sc[UPW][2][4];
+#pragma unroll
+        for (int u = 0; u < UPW; ++u) {
+#pragma unroll
+            for (int nr = 0; nr < 2; ++nr) sc[u][nr][0] = sc[u][nr][1] = sc[u][nr][2] = sc[u][nr][3] = 0.f;
+        }
+        // (slice of the head by slice, all units in each: consecutive MMAs are independent)
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t a[UPW][4];
+#pragma unroll
+            for (int u = 0; u < UPW; ++u) {
+                if (u < n_tiles) {
+                    const int unit = u_lo + u;
+                    const int j = (unit & 3) * 16 + (lane & 15);
+                    const int c = ks * 2 + (lane >> 4);
+                    ldmatrix_x4(a[u], k_s + (unit >> 2) * MMA_BN * D + j * D + ((c ^ (j & 7)) * 8));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UPW; ++u) {
+                if (u < n_tiles) {
+                    mma_bf16(sc[u][0], a[u], qf[ks][0], qf[ks][1]);
+                    if (two) mma_bf16(sc[u][1], a[u], qf[ks][2], qf[ks][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UPW; ++u) {
+            if (u < n_tiles)
+                unit_mask(sc[u], (t_lo + ((u_lo + u) >> 2)) * MMA_BN + ((u_lo + u) & 3) * 16, m);
+        }
+        across_keys_max(m);
+#pragma unroll
+        for (int u = 0; u < UPW; ++u) {
+            if (u < n_tiles) {
+                const int unit = u_lo + u;
+                unit_values(sc[u], v_s + (unit >> 2) * MMA_BN * D, (unit & 3) * 16);
+            }
+        }
+    }
+
+    if (FED && warp == 4) {
+        // ---- the producer warp: a round's half tiles go into their half stages as soon as the
+        // warps that own the stages have read what was there (two rounds earlier)
+        for (int r = 2; 4 * r < n_half; ++r)
+            if (!fetch_round(r, true)) break;
+    } else if (FED) {
+        // ---- Many tiles per block: every consumer warp walks half tiles of its own (warp w
+        // takes the block's half tiles w, w + 4, ...) through two half stages of its own. It
+        // waits for its half tile, goes through the two units of 16 keys side by side and hands
+        // the half stage back to the producer warp, so that no barrier of the block stands in
+        // the loop, the copies are nobody's detour, and while a warp waits the others work.
+        for (int h = warp; h < n_half; h += 4) {
+            const int hs = warp + 4 * ((h >> 2) & 1);
+            const int key_base = t_lo * MMA_BN + h * HALF;
+            // (bounded like every mbarrier wait of this library; a wait that gives up sets
+            // the error word and the warp goes on with whatever the stage holds)
+            mbar_wait(&tile_full[hs], (uint32_t)((h >> 3) & 1), error ? error : &fed_error, 8);
+            __nv_bfloat16* kt_s = k_s + hs * HALF * D;
+            __nv_bfloat16* vt_s = v_s + hs * HALF * D;
+            if (raw && key_base + HALF > first_pos) {
+                // this step's keys and values take their rows of the half tile
+                for (int idx = lane; idx < q_len * CH; idx += 32) {
+                    const int tok = idx / CH, c = idx - tok * CH;
+                    const int row = first_pos + tok - key_base;
+                    if (row < 0 || row >= HALF) continue;
+                    const int sw = (c ^ (row & 7)) * 8;
+                    *reinterpret_cast<uint4*>(kt_s + row * D + sw) =
+                        *reinterpret_cast<const uint4*>(&new_k[tok][c * 8]);
+                    *reinterpret_cast<uint4*>(vt_s + row * D + sw) =
+                        *reinterpret_cast<const uint4*>(&new_v[tok][c * 8]);
+                }
+            }
+            // A copy brings whole pages and nothing for a page that is not there: value rows
+            // beyond the sequence or of a missing page are cleared before P V meets them
+            // (0 x NaN).
+            if (key_base + HALF > kv_len || tile_pages[hs] != (1u << (HALF >> box_shift)) - 1u) {
+                const int key = key_base + lane;
+                const bool there = key < kv_len && ((tile_pages[hs] >> (lane >> box_shift)) & 1u);
+                if (!there) {
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(vt_s + lane * D + c * 8) = zero;
+                }
+            }
+            __syncwarp();
+            float sc[2][2][4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int nr = 0; nr < 2; ++nr) sc[u][nr][0] = sc[u][nr][1] = sc[u][nr][2] = sc[u][nr][3] = 0.f;
+            }
+            // (slice of the head by slice, both units in each: consecutive MMAs are independent)
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t a[2][4];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int j = u * 16 + (lane & 15);
+                    const int c = ks * 2 + (lane >> 4);
+                    ldmatrix_x4(a[u], kt_s + j * D + ((c ^ (j & 7)) * 8));
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    mma_bf16(sc[u][0], a[u], qf[ks][0], qf[ks][1]);
+                    if (two) mma_bf16(sc[u][1], a[u], qf[ks][2], qf[ks][3]);
+                }
+            }
+            float m_new[2][2] = {{m[0][0], m[0][1]}, {m[1][0], m[1][1]}};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) unit_mask(sc[u], key_base + u * 16, m_new);
+            across_keys_max(m_new);
+            // the running sums and the output move to a new maximum only when some row has one
+            if (__any_sync(0xffffffffu, m_new[0][0] > m[0][0] || m_new[0][1] > m[0][1] ||
+                                            m_new[1][0] > m[1][0] || m_new[1][1] > m[1][1])) {
+#pragma unroll
+                for (int nr = 0; nr < 2; ++nr) {
+                    float corr[2];
+#pragma unroll
+                    for (int z = 0; z < 2; ++z) {
+                        corr[z] = m_new[nr][z] > -INFINITY ? fast_exp2(m[nr][z] - m_new[nr][z]) : 1.f;
+                        m[nr][z] = m_new[nr][z];
+                        l[nr][z] *= corr[z];
+                    }
+#pragma unroll
+                    for (int i = 0; i < D / 16; ++i) {
+                        o[i][nr][0] *= corr[0];
+                        o[i][nr][1] *= corr[1];
+                        o[i][nr][2] *= corr[0];
+                        o[i][nr][3] *= corr[1];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) unit_values(sc[u], vt_s, u * 16);
+            // the half tile has been read (its fragments are in registers and used) and the
+            // rows this warp wrote are ordered before the copy that will overwrite them
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tile_free[hs])) : "memory");
+        }
     }
 
     // Copy groups in the order they were committed: tiles 0 .. STAGES-1, the late group, then
     // one refill per iteration from the second on. A tile of this step's keys may sit in the
     // late group: it waits for everything; any other tile is older than the newest
     // STAGES - 2 groups when its turn comes.
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = 0; it < n_tiles && !resident && !FED; ++it) {
         const int kt = t_lo + it;
         const int stage = it % STAGES;
-        if (FED) {
-            // (bounded like every mbarrier wait of this library; a wait that gives up sets
-            // the error word and the block goes on with whatever the stage holds)
-            mbar_wait(&tile_full[stage], (uint32_t)((it / STAGES) & 1), error ? error : &fed_error, 8);
-            __syncthreads();   // the stage of tile it-1 is free
-        } else if (!resident) {
+        {
             if (kt >= t_new && !raw) {
                 asm volatile("cp.async.wait_group 0;\n" ::);
             } else {
@@ -969,7 +1264,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             if (next < n_tiles) load_tile((it - 1) % STAGES, t_lo + next);
             asm volatile("cp.async.commit_group;\n" ::);
         };
-        if (!FED && it >= 1 && !resident) refill();
+        if (it >= 1) refill();
         __nv_bfloat16* kt_s = k_s + stage * MMA_BN * D;
         __nv_bfloat16* vt_s = v_s + stage * MMA_BN * D;
         if (raw && kt >= t_new) {
@@ -988,140 +1283,69 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             __syncthreads();
         }
 
-        if (FED) {
-            // A copy brings whole pages and nothing for a page that is not there: value rows
-            // beyond the sequence or of a missing page are cleared before P V meets them
-            // (0 x NaN). Every warp clears among the 16 rows it reads itself.
-            const int row = warp * 16 + (lane >> 1), key = kt * MMA_BN + row;
-            // copy c of the tile was issued by lane c / 4 of warp c % 4
-            const int c_of = row >> box_shift;
-            const bool there = key < kv_len && ((tile_pages[stage][c_of & 3] >> (c_of >> 2)) & 1u);
-            if (!there) {
-                const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int c = 0; c < CH / 2; ++c)
-                    *reinterpret_cast<uint4*>(vt_s + row * D + ((lane & 1) * (CH / 2) + c) * 8) = zero;
-            }
-            __syncwarp();
-        }
         // this warp's 16 keys of the tile
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            uint32_t b[4];
-            const int j = warp * 16 + (lane & 7) + (lane >> 4) * 8;
-            const int c = ks * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4(b, kt_s + j * D + ((c ^ (j & 7)) * 8));
-            mma_bf16(s[0], qf[ks], b[0], b[1]);
-            mma_bf16(s[1], qf[ks], b[2], b[3]);
-        }
-        // FED: the next tile's copies are issued here, under the MMAs just issued (their
-        // issue is some hundred cycles of one lane per warp and the scores are not needed yet)
-        if (FED && it >= 1) refill();
-        float m_new[2] = {m[0], m[1]};
-        // Every key of this warp's 16 is seen by every row when the newest of them is no later
-        // than the earliest position of the step, real, and inside every row's window (rows
-        // beyond the step's are zeros and go nowhere): then nothing is masked one by one.
-        const int key_lo = kt * MMA_BN + warp * 16;
-        const bool plain = key_lo + 15 <= first_pos && key_lo + 15 < kv_len &&
-                           (window <= 0 || key_lo > p_max - window);
-        if (plain) {
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[nt][e] *= scale2;
-                    m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int h = e >> 1;
-                    const int key = key_lo + nt * 8 + 2 * t4 + (e & 1);
-                    bool seen = row_ok[h] && key <= pos[h] && key < kv_len;
-                    if (window > 0) seen = seen && key > pos[h] - window;
-                    s[nt][e] = seen ? s[nt][e] * scale2 : -INFINITY;
-                    m_new[h] = fmaxf(m_new[h], s[nt][e]);
-                }
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
-            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-        }
+        float sc[2][4];
+        unit_scores(kt_s, warp * 16, sc);
+        float m_new[2][2] = {{m[0][0], m[0][1]}, {m[1][0], m[1][1]}};
+        unit_mask(sc, kt * MMA_BN + warp * 16, m_new);
+        across_keys_max(m_new);
         // the running sums and the output move to a new maximum only when some row of the
         // warp has one (after the first tiles that is rare)
-        if (__any_sync(0xffffffffu, m_new[0] > m[0] || m_new[1] > m[1])) {
-            float corr[2];
+        if (__any_sync(0xffffffffu, m_new[0][0] > m[0][0] || m_new[0][1] > m[0][1] ||
+                                        m_new[1][0] > m[1][0] || m_new[1][1] > m[1][1])) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                corr[h] = m_new[h] > -INFINITY ? fast_exp2(m[h] - m_new[h]) : 1.f;
-                m[h] = m_new[h];
-                l[h] *= corr[h];
-            }
+            for (int nr = 0; nr < 2; ++nr) {
+                float corr[2];
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) {
-                o[i][0] *= corr[0];
-                o[i][1] *= corr[0];
-                o[i][2] *= corr[1];
-                o[i][3] *= corr[1];
-            }
-        }
+                for (int z = 0; z < 2; ++z) {
+                    corr[z] = m_new[nr][z] > -INFINITY ? fast_exp2(m[nr][z] - m_new[nr][z]) : 1.f;
+                    m[nr][z] = m_new[nr][z];
+                    l[nr][z] *= corr[z];
+                }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const float p = m[h] > -INFINITY ? fast_exp2(s[nt][e] - m[h]) : 0.f;
-                s[nt][e] = p;
-                l[h] += p;
+                for (int i = 0; i < D / 16; ++i) {
+                    o[i][nr][0] *= corr[0];
+                    o[i][nr][1] *= corr[1];
+                    o[i][nr][2] *= corr[0];
+                    o[i][nr][3] *= corr[1];
+                }
             }
         }
-        uint32_t a[4];
-        a[0] = pack_bf16(s[0][0], s[0][1]);
-        a[1] = pack_bf16(s[0][2], s[0][3]);
-        a[2] = pack_bf16(s[1][0], s[1][1]);
-        a[3] = pack_bf16(s[1][2], s[1][3]);
-#pragma unroll
-        for (int d2 = 0; d2 < D / 16; ++d2) {
-            uint32_t b[4];
-            const int j = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-            const int c = d2 * 2 + (lane >> 4);
-            ldmatrix_x4_trans(b, vt_s + j * D + ((c ^ (j & 7)) * 8));
-            mma_bf16(o[2 * d2], a, b[0], b[1]);
-            mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
-        }
+        unit_values(sc, vt_s, warp * 16);
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();   // every warp is done with the key tiles: their memory becomes o_red
 
     // ---- merge the four warps (each saw a quarter of the keys)
+    if (!FED || warp < 4) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-        if (t4 == 0) {
-            ml_red[warp][g + h * 8][0] = m[h];
-            ml_red[warp][g + h * 8][1] = l[h];
+    for (int nr = 0; nr < 2; ++nr) {
+#pragma unroll
+        for (int z = 0; z < 2; ++z) {
+            l[nr][z] += __shfl_xor_sync(0xffffffffu, l[nr][z], 4);
+            l[nr][z] += __shfl_xor_sync(0xffffffffu, l[nr][z], 8);
+            l[nr][z] += __shfl_xor_sync(0xffffffffu, l[nr][z], 16);
+            if (g == 0) {
+                ml_red[warp][nr * 8 + 2 * t4 + z][0] = m[nr][z];
+                ml_red[warp][nr * 8 + 2 * t4 + z][1] = l[nr][z];
+            }
         }
     }
     // (each warp's output goes in as it is, on its own maximum; the weights that bring the
     // four onto the common maximum are applied where they are summed)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = g + h * 8;
+    for (int nr = 0; nr < 2; ++nr) {
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<float2*>(o_red + (warp * 16 + r) * D + i * 8 + 2 * t4) =
-                make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        for (int i = 0; i < D / 16; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o_red[(warp * 16 + nr * 8 + 2 * t4 + (e & 1)) * D + i * 16 + g + (e >> 1) * 8] = o[i][nr][e];
+        }
+    }
     }
     __syncthreads();
     // 128 threads: thread -> (row = tid / 8, 8 threads across D)
-    {
+    if (!FED || tid < 128) {
         const int r = tid >> 3;
         const int tok = r / group, hg = r - tok * group;
         float big = -INFINITY, sum = 0.f;
@@ -1192,7 +1416,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
         const int r_first = (int)split * per_block;
-        for (int e = tid; e < per_block * D; e += 128) {
+        for (int e = tid; e < per_block * D && tid < 128; e += 128) {
             const int r_local = e / D, c = e % D;
             const int r = r_first + r_local;
             if (r >= rows) continue;
@@ -1277,7 +1501,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                                     int page_size, float scale, int window, int num_seqs, int cluster,
                                     const float* cos_t, const float* sin_t, int raw, int store,
                                     int num_pages, int* error, cudaStream_t s) {
-    constexpr int STAGES = D == 64 ? 5 : 3;
+    constexpr int STAGES = FED ? 4 : (D == 64 ? 5 : 3);
     CUtensorMap map_k, map_v;
     memset(&map_k, 0, sizeof(map_k));
     memset(&map_v, 0, sizeof(map_v));
@@ -1285,7 +1509,8 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
         const cuuint64_t rows = (cuuint64_t)num_pages * n_kv * page_size;
         cuuint64_t dims[2] = {(cuuint64_t)D, rows};
         cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-        cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < MMA_BN ? page_size : MMA_BN)};
+        // (a copy brings a page, or 32 keys of a larger one: the kernel's half tiles)
+        cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < MMA_BN / 2 ? page_size : MMA_BN / 2)};
         if (!make_map_nd(&map_k, k_pages, 2, dims, strides, box) ||
             !make_map_nd(&map_v, v_pages, 2, dims, strides, box))
             return MB_ERR_LAUNCH;
@@ -1302,7 +1527,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
         raised = true;
     }
     typedef __nv_bfloat16 bf;
-    cudaLaunchConfig_t config = launch_config(dim3(num_seqs, n_kv, cluster), 128, smem, s);
+    cudaLaunchConfig_t config = launch_config(dim3(num_seqs, n_kv, cluster), FED ? 160 : 128, smem, s);
     cudaLaunchAttribute attrs[2];
     int num_attrs = 0;
     if (config.numAttrs) attrs[num_attrs++] = config.attrs[0];
