@@ -657,7 +657,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // stage, instead of 16 bytes per thread and instruction. For blocks that walk many tiles
 // (large batches) the per-thread copies were the limit: issuing a tile's 8 cp.async took a
 // thread 780 of the 2080 cycles a tile took. Head size 64, pages of 8 tokens or more.
-template <int D, bool FED>
+// TWO: the step's query rows (tokens x heads of the group) are more than 8 and take a second
+// column tile of the transposed products.
+template <int D, bool FED, bool TWO>
 __global__ void __launch_bounds__(FED ? 160 : 128)
 attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
@@ -689,8 +691,11 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_base);     // [16][D]
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
     __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
-    float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][D], after the loop
-    float* o_part = o_red + 4 * 16 * D;                                   // [16][D], this block's result
+    // (rows of D + 4 floats: the warps write their pieces of O^T column by column, and with
+    // this stride the 32 lanes of a store fall into 32 banks)
+    constexpr int OR = D + 4;
+    float* o_red = reinterpret_cast<float*>(k_s);                         // [4][16][OR], after the loop
+    float* o_part = o_red + 4 * 16 * OR;                                  // [16][D], this block's result
     // where the other blocks leave their results for this block's rows (head size 64 only):
     // [range][row of this block][D], then [range][row of this block][maximum, sum]; no
     // other use, since a block that is done early writes here while this one still runs
@@ -953,7 +958,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // an m16n8k16 issues about every 40 cycles per scheduler on this GPU, so a 64-key tile cost
     // a warp some 700 cycles of MMAs alone. A thread holds, of a 16 x 8 piece, rows g and g + 8
     // (keys) and columns 2 t4 and 2 t4 + 1 (query rows).
-    const bool two = rows > 8;               // a second column tile of query rows
+    constexpr bool two = TWO;                // a second column tile of query rows
     int pos[2][2];
     bool row_ok[2][2];
 #pragma unroll
@@ -1015,6 +1020,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                            (window <= 0 || key_lo > p_max - window);
 #pragma unroll
         for (int nr = 0; nr < 2; ++nr) {
+            if (nr == 1 && !two) continue;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int z = e & 1;
@@ -1033,6 +1039,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     auto across_keys_max = [&](float (&top)[2][2]) {
 #pragma unroll
         for (int nr = 0; nr < 2; ++nr) {
+            if (nr == 1 && !two) continue;
 #pragma unroll
             for (int z = 0; z < 2; ++z) {
                 top[nr][z] = fmaxf(top[nr][z], __shfl_xor_sync(0xffffffffu, top[nr][z], 4));
@@ -1046,6 +1053,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         uint32_t pt[2][2];
 #pragma unroll
         for (int nr = 0; nr < 2; ++nr) {
+            if (nr == 1 && !two) continue;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int z = e & 1;
@@ -1339,7 +1347,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         for (int i = 0; i < D / 16; ++i) {
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                o_red[(warp * 16 + nr * 8 + 2 * t4 + (e & 1)) * D + i * 16 + g + (e >> 1) * 8] = o[i][nr][e];
+                o_red[(warp * 16 + nr * 8 + 2 * t4 + (e & 1)) * OR + i * 16 + g + (e >> 1) * 8] = o[i][nr][e];
         }
     }
     }
@@ -1374,7 +1382,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                     for (int w = 0; w < 4; ++w) {
-                        const float4 u = *reinterpret_cast<const float4*>(o_red + (w * 16 + r) * D + 4 * c4);
+                        const float4 u = *reinterpret_cast<const float4*>(o_red + (w * 16 + r) * OR + 4 * c4);
                         v.x += wgt[w] * u.x;
                         v.y += wgt[w] * u.y;
                         v.z += wgt[w] * u.z;
@@ -1390,8 +1398,8 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             }
         } else {
             for (int c = (tid & 7); c < D; c += 8) {
-                const float v = wgt[0] * o_red[(0 * 16 + r) * D + c] + wgt[1] * o_red[(1 * 16 + r) * D + c] +
-                                wgt[2] * o_red[(2 * 16 + r) * D + c] + wgt[3] * o_red[(3 * 16 + r) * D + c];
+                const float v = wgt[0] * o_red[(0 * 16 + r) * OR + c] + wgt[1] * o_red[(1 * 16 + r) * OR + c] +
+                                wgt[2] * o_red[(2 * 16 + r) * OR + c] + wgt[3] * o_red[(3 * 16 + r) * OR + c];
                 if (num_splits == 1) {
                     if (r < rows)
                         out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
@@ -1494,7 +1502,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int D, bool FED>
+template <int D, bool FED, bool TWO>
 int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
                                     const void* v_pages, const int* table, int max_pages,
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
@@ -1521,7 +1529,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                         (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED>,
+        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED, TWO>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = true;
@@ -1540,7 +1548,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     config.attrs = attrs;
     config.numAttrs = num_attrs;
-    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED>, map_k, map_v, (const bf*)qkv,
+    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO>, map_k, map_v, (const bf*)qkv,
                        q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start,
                        kv_len, (bf*)out, n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store,
                        error);
@@ -1644,21 +1652,19 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
     // reads another layer's cache must find this step's keys in the pages
     if (raw && !store) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (d == 64 && num_pages > 0 && error != nullptr && page_size >= 8 && page_size <= MMA_BN &&
-        (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0)
-        return launch_attention_decode_cluster<64, true>(qkv, q_row_stride, k_pages, v_pages, table,
-                                                         max_pages, q_start, kv_len, out, n_q, n_kv,
-                                                         page_size, scale, window, num_seqs, cluster,
-                                                         cos_t, sin_t, raw, store, num_pages, error, s);
-    if (d == 64)
-        return launch_attention_decode_cluster<64, false>(qkv, q_row_stride, k_pages, v_pages, table,
-                                                          max_pages, q_start, kv_len, out, n_q, n_kv,
-                                                          page_size, scale, window, num_seqs, cluster,
-                                                          cos_t, sin_t, raw, store, 0, nullptr, s);
-    return launch_attention_decode_cluster<128, false>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
-                                                       q_start, kv_len, out, n_q, n_kv, page_size, scale,
-                                                       window, num_seqs, cluster, cos_t, sin_t, raw, store,
-                                                       0, nullptr, s);
+    const bool fed = d == 64 && num_pages > 0 && error != nullptr && page_size >= 8 &&
+                     page_size <= MMA_BN && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    // (the longest portion bounds every sequence's rows: one column tile of 8 rows, or two)
+    const bool two = max_q_len * (n_q / n_kv) > 8;
+#define MB_DC_LAUNCH(D_, FED_, TWO_)                                                                  \
+    launch_attention_decode_cluster<D_, FED_, TWO_>(qkv, q_row_stride, k_pages, v_pages, table, max_pages, \
+                                                    q_start, kv_len, out, n_q, n_kv, page_size, scale, \
+                                                    window, num_seqs, cluster, cos_t, sin_t, raw, store, \
+                                                    FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
+    if (fed) return two ? MB_DC_LAUNCH(64, true, true) : MB_DC_LAUNCH(64, true, false);
+    if (d == 64) return two ? MB_DC_LAUNCH(64, false, true) : MB_DC_LAUNCH(64, false, false);
+    return two ? MB_DC_LAUNCH(128, false, true) : MB_DC_LAUNCH(128, false, false);
+#undef MB_DC_LAUNCH
 }
 
 // Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.
