@@ -483,22 +483,67 @@ def run_part(args) -> dict:
     _entry, config = config_from_dict(raw)
     vocab = raw["vocab_size"]
     if args.only == "products":
+        from types import SimpleNamespace
+
         from mercury_b200.kernels.ops import CudaOps
+
+        def replayed(fn, calls=10):
+            """Microseconds per call of fn, `calls` of them replayed from a CUDA graph: the
+            device's time without the host's share (a product of a few microseconds is
+            launched more slowly than it runs)."""
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(calls):
+                    fn()
+            graph.replay()
+            return timed(torch, graph.replay, max(args.steps, 3)) / calls * 1e3
 
         out = {}
         for name, (m, n, k) in {"qkv": (2048, 1152, 896), "o": (2048, 896, 896),
-                                "gate_up": (2048, 9728, 896), "down": (2048, 896, 4864)}.items():
+                                "gate_up": (2048, 9728, 896), "down": (2048, 896, 4864),
+                                "qkv_7b": (2048, 4608, 3584), "down_7b": (2048, 3584, 18944)}.items():
             x = torch.randn(m, k).bfloat16().cuda()
             w = torch.randn(n, k).bfloat16().cuda()
             y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
             for gemm in ("library", "tcgen05"):
                 ops = CudaOps("cuda", gemm=gemm)
-                for _ in range(3):
-                    ops.linear(x, w, None, y)
-                ms = timed(torch, lambda: ops.linear(x, w, None, y), args.steps)
+                us = replayed(lambda: ops.linear(x, w, None, y))
                 ops.check_errors()
-                out[f"{name}_{gemm}_us"] = round(ms * 1e3, 1)
-                out[f"{name}_{gemm}_tflops"] = round(2 * m * n * k / ms / 1e9, 1)
+                out[f"{name}_{gemm}_us"] = round(us, 1)
+                out[f"{name}_{gemm}_tflops"] = round(2 * m * n * k / us / 1e6, 1)
+            ops = CudaOps("cuda")
+            error = torch.zeros(1, dtype=torch.int32, device="cuda")
+            stream = torch.cuda.current_stream
+
+            def pairs():
+                assert ops.lib.mb_gemm_pair(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 0, m, n, k,
+                                            None, 0, 0.0, 0, None, None, None, None, error.data_ptr(),
+                                            stream().cuda_stream) == 0
+            us = replayed(pairs)
+            assert int(error.item()) == 0
+            out[f"{name}_pairs_us"] = round(us, 1)
+            out[f"{name}_pairs_tflops"] = round(2 * m * n * k / us / 1e6, 1)
+        # the gated product: gate/up with the SiLU gate in the epilogue, one CTA per tile against
+        # pairs of CTAs, and the library's product followed by the gate kernel
+        for name, (m, width, k) in {"gated_0.5b": (2048, 4864, 896), "gated_1.5b": (2048, 8960, 1536),
+                                    "gated_7b": (2048, 18944, 3584)}.items():
+            x = torch.randn(m, k).bfloat16().cuda()
+            w = (torch.randn(2 * width, k) * 0.05).bfloat16().cuda()
+            y = torch.empty(m, width, dtype=torch.bfloat16, device="cuda")
+            both = torch.empty(m, 2 * width, dtype=torch.bfloat16, device="cuda")
+            ctx = SimpleNamespace(buffer=lambda *_a, **_k: both)
+            for label, gemm, min_k in (("one_cta", "auto", 1 << 30), ("pairs", "auto", 0),
+                                       ("library_and_gate", "library", 0)):
+                ops = CudaOps("cuda", gemm=gemm)
+                ops.pair_min_k = min_k
+                ops.gated_max_elements = 1 << 40
+                us = replayed(lambda: ops.linear_swiglu(x, w, y, ctx))
+                ops.check_errors()
+                out[f"{name}_{label}_us"] = round(us, 1)
+                out[f"{name}_{label}_tflops"] = round(4 * m * width * k / us / 1e6, 1)
         return out
     tensors = random_tensors(config, SEED, torch.bfloat16)
     batch = args.batch

@@ -659,7 +659,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // thread 780 of the 2080 cycles a tile took. Head size 64, pages of 8 tokens or more.
 // TWO: the step's query rows (tokens x heads of the group) are more than 8 and take a second
 // column tile of the transposed products.
-template <int D, bool FED, bool TWO>
+// STG: stages of 64 keys in shared memory (not FED). Head size 128 has three when two blocks
+// are to share an SM and five when there are no more blocks than SMs: five tiles are what a
+// block of a small batch walks at 2048-token contexts, and with all of them in shared memory
+// before the kernel in front is done nothing is copied inside the loop (16 copies of 16 bytes
+// per thread and tile there: some 2000 cycles a tile).
+template <int D, bool FED, bool TWO, int STG>
 __global__ void __launch_bounds__(FED ? 160 : 128)
 attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
@@ -678,7 +683,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // then needs no block per head, and every tile of the pages can be copied before the wait.
     constexpr int CH = D / 8;
     // (FED: one stage per warp, see the tile loop)
-    constexpr int STAGES = FED ? 4 : (D == 64 ? 5 : 3);
+    constexpr int STAGES = FED ? 4 : STG;
     __nv_bfloat16* k_pages_out = const_cast<__nv_bfloat16*>(k_pages);
     __nv_bfloat16* v_pages_out = const_cast<__nv_bfloat16*>(v_pages);
     __shared__ __align__(16) __nv_bfloat16 new_k[16][D]; // this step's keys, rotated
@@ -787,7 +792,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     const int box = FED ? (page_size < HALF ? page_size : HALF) : (page_size < MMA_BN ? page_size : MMA_BN);
     const int box_shift = 31 - __clz(box);
     auto load_tile = [&](int stage, int kt) {
-        if (FED) return;     // (the producer warp's copies: fetch_half below)
+        if (FED) return;     // (the producer warp's copies: fetch_round below)
         const int key = kt * MMA_BN + lj;
         int page = -1;
         if (key < kv_len && !(raw && key >= first_pos))
@@ -979,9 +984,10 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     const float scale2 = scale * 1.4426950408889634f;
 
-    // raw, and no more tiles than stages: every tile was asked for before the wait and none
-    // is refilled, so one wait and the barrier below stand for the per-tile ones
-    const bool resident = !FED && raw && n_tiles <= STAGES;
+    // no more tiles than stages: every tile was asked for before the wait (or, a tile with
+    // this step's keys that the kernel in front writes, right after it) and none is refilled,
+    // so one wait and the barrier below stand for the per-tile ones
+    const bool resident = !FED && n_tiles <= STAGES;
     if (resident) asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
     if (FED && warp == 4) {
@@ -1084,7 +1090,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         // every warp taking a quarter of every tile: a warp takes n_tiles consecutive units
         // of 16 keys, computes all its scores, goes through the softmax once and then through
         // P V, so that its MMAs are independent chains and nothing is rescaled.
-        if (t_new < t_hi) {
+        if (raw && t_new < t_hi) {
             // this step's keys and values take their rows of their tiles (the copies left zeros)
             for (int idx = tid; idx < q_len * CH; idx += 128) {
                 const int tok = idx / CH, c = idx - tok * CH;
@@ -1502,14 +1508,25 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int D, bool FED, bool TWO>
+static int device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+template <int D, bool FED, bool TWO, int STG>
 int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
                                     const void* v_pages, const int* table, int max_pages,
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
                                     int page_size, float scale, int window, int num_seqs, int cluster,
                                     const float* cos_t, const float* sin_t, int raw, int store,
                                     int num_pages, int* error, cudaStream_t s) {
-    constexpr int STAGES = FED ? 4 : (D == 64 ? 5 : 3);
+    constexpr int STAGES = FED ? 4 : STG;
     CUtensorMap map_k, map_v;
     memset(&map_k, 0, sizeof(map_k));
     memset(&map_v, 0, sizeof(map_v));
@@ -1529,7 +1546,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                         (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED, TWO>,
+        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED, TWO, STG>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = true;
@@ -1548,7 +1565,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     config.attrs = attrs;
     config.numAttrs = num_attrs;
-    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO>, map_k, map_v, (const bf*)qkv,
+    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO, STG>, map_k, map_v, (const bf*)qkv,
                        q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start,
                        kv_len, (bf*)out, n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store,
                        error);
@@ -1656,14 +1673,17 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                      page_size <= MMA_BN && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
     // (the longest portion bounds every sequence's rows: one column tile of 8 rows, or two)
     const bool two = max_q_len * (n_q / n_kv) > 8;
-#define MB_DC_LAUNCH(D_, FED_, TWO_)                                                                  \
-    launch_attention_decode_cluster<D_, FED_, TWO_>(qkv, q_row_stride, k_pages, v_pages, table, max_pages, \
+#define MB_DC_LAUNCH(D_, FED_, TWO_, STG_)                                                            \
+    launch_attention_decode_cluster<D_, FED_, TWO_, STG_>(qkv, q_row_stride, k_pages, v_pages, table, max_pages, \
                                                     q_start, kv_len, out, n_q, n_kv, page_size, scale, \
                                                     window, num_seqs, cluster, cos_t, sin_t, raw, store, \
                                                     FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
-    if (fed) return two ? MB_DC_LAUNCH(64, true, true) : MB_DC_LAUNCH(64, true, false);
-    if (d == 64) return two ? MB_DC_LAUNCH(64, false, true) : MB_DC_LAUNCH(64, false, false);
-    return two ? MB_DC_LAUNCH(128, false, true) : MB_DC_LAUNCH(128, false, false);
+    if (fed) return two ? MB_DC_LAUNCH(64, true, true, 4) : MB_DC_LAUNCH(64, true, false, 4);
+    if (d == 64) return two ? MB_DC_LAUNCH(64, false, true, 5) : MB_DC_LAUNCH(64, false, false, 5);
+    // head size 128: five stages (164 KB, one block per SM) while the blocks are no more than the SMs
+    if ((long long)num_seqs * n_kv * cluster <= device_sms())
+        return two ? MB_DC_LAUNCH(128, false, true, 5) : MB_DC_LAUNCH(128, false, false, 5);
+    return two ? MB_DC_LAUNCH(128, false, true, 3) : MB_DC_LAUNCH(128, false, false, 3);
 #undef MB_DC_LAUNCH
 }
 

@@ -70,24 +70,45 @@ argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part
     __shared__ int best_i[8];
     const int r = blockIdx.y, part = blockIdx.x;
     const float* row = logits + (int64_t)r * vocab;
-    const int per = (vocab + parts - 1) / parts;
-    const int begin = part * per, end = begin + per < vocab ? begin + per : vocab;
+    const int per = (((vocab + parts - 1) / parts) + 3) & ~3;      // a multiple of four floats
+    const int begin = part * per < vocab ? part * per : vocab;
+    const int end = begin + per < vocab ? begin + per : vocab;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const float v = row[i];
+    auto take = [&](float v, int i) {
         if (v > bv || (v == bv && i < bi)) {
             bv = v;
             bi = i;
         }
+    };
+    if ((vocab & 3) == 0 && (per & 3) == 0) {
+        // 16 bytes per load and four loads in flight per thread (the slice of a row is a few
+        // thousand floats: with one float per load the kernel waited for memory trip by trip)
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int b4 = begin >> 2, e4 = end >> 2;
+        for (int i0 = b4 + threadIdx.x; i0 < e4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < e4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = (i0 + u * (int)blockDim.x) << 2;
+                take(v[u].x, i);
+                take(v[u].y, i + 1);
+                take(v[u].z, i + 2);
+                take(v[u].w, i + 3);
+            }
+        }
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) take(row[i], i);
     }
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
-            bv = ov;
-            bi = oi;
-        }
+        take(ov, oi);
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) {

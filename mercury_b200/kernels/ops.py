@@ -81,6 +81,12 @@ class CudaOps:
         # 2048 tokens: K 896, 34 us one CTA against 35 us pairs; K 1536, 91 against 86; at 4096
         # tokens, K 3584 and 2 x 18944 rows, 1515 against 1028)
         self.pair_min_k = 1024
+        # ... and beyond this many weight elements the library's product followed by the gate
+        # kernel is ahead of both (measured on B200 at 2048 tokens, replayed from a graph:
+        # 2 x 4864 x 896, 35 us fused against 43; 2 x 8960 x 1536, 87 against 101;
+        # 2 x 18944 x 3584, 503 against 424: there the library's 1.5 PFLOP/s outweigh the
+        # gate kernel's extra pass)
+        self.gated_max_elements = 64 * 1024 * 1024
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head sizes 64 and
         # 128, the mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
@@ -441,6 +447,7 @@ class CudaOps:
             x = x.materialize()
         if (self.gemm in ("tcgen05", "auto") and x.dtype == torch.bfloat16
                 and weight.dtype == torch.bfloat16 and m >= 256 and width % 8 == 0
+                and (2 * width * k <= self.gated_max_elements or self.gemm == "tcgen05")
                 and self.lib.mb_gemm_tcgen05_supports(m, width, k)):
             if k >= self.pair_min_k and self.lib.mb_gemm_pair_supports(m, width, k):
                 # pairs of SMs sharing one 256-row MMA: a CTA loads a third less per output
