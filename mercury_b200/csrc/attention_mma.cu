@@ -1633,11 +1633,12 @@ MB_EXPORT int mb_attention_mma_supports(int d) { return d == 64 || d == 128; }
 
 // Whether a decode-like step should hand the cluster kernel the bare projections (`raw`: it
 // then rotates the queries and rotates and stores the new keys itself) instead of running the
-// fused q/k/v kernel in front of it. Measured inside the captured decode step on B200: at head
-// size 64 the bare form is ahead (batch 8: 0.671 -> 0.660 ms per step), at head size 128 it is
-// behind (1.515 -> 1.569 ms: the kernel's landing area for a new key doubles and one block
-// fewer fits an SM), so the answer is a property of this kernel, asked for here.
-MB_EXPORT int mb_attention_decode_raw_pays(int d) { return d == 64; }
+// fused q/k/v kernel in front of it. Measured inside the captured decode step on B200: head
+// size 64, batch 8, 0.671 -> 0.660 ms per step; head size 128 (since its tiles are all in shared
+// memory before the wait and the new keys are put in there): 1.5B sizes batch 8 1.552 -> 1.544,
+// batch 16 2.18 -> 2.07, 7B sizes batch 8 3.93 -> 3.73. The answer is a property of this
+// kernel, asked for here.
+MB_EXPORT int mb_attention_decode_raw_pays(int d) { return d == 64 || d == 128; }
 
 // Decode-like batches (at most 16 rows per sequence and KV head) with the key ranges of a
 // (sequence, KV head) as one cluster of `cluster` blocks (1, 2, 4 or 8): no scratch, no
