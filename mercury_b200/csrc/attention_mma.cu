@@ -660,10 +660,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // TWO: the step's query rows (tokens x heads of the group) are more than 8 and take a second
 // column tile of the transposed products.
 // STG: stages of 64 keys in shared memory (not FED). Head size 128 has three when two blocks
-// are to share an SM and five when there are no more blocks than SMs: five tiles are what a
-// block of a small batch walks at 2048-token contexts, and with all of them in shared memory
-// before the kernel in front is done nothing is copied inside the loop (16 copies of 16 bytes
-// per thread and tile there: some 2000 cycles a tile).
+// are to share an SM and five when the blocks are few: five tiles are what a block of a small
+// batch walks at 2048-token contexts, and with all of them in shared memory before the kernel
+// in front is done nothing is copied inside the loop (16 copies of 16 bytes per thread and
+// tile there: some 2000 cycles a tile).
 template <int D, bool FED, bool TWO, int STG>
 __global__ void __launch_bounds__(FED ? 160 : 128)
 attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
@@ -1681,8 +1681,12 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                     FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
     if (fed) return two ? MB_DC_LAUNCH(64, true, true, 4) : MB_DC_LAUNCH(64, true, false, 4);
     if (d == 64) return two ? MB_DC_LAUNCH(64, false, true, 5) : MB_DC_LAUNCH(64, false, false, 5);
-    // head size 128: five stages (164 KB, one block per SM) while the blocks are no more than the SMs
-    if ((long long)num_seqs * n_kv * cluster <= device_sms())
+    // head size 128: five stages (164 KB, one block per SM) while the blocks are at most half
+    // the SMs. Measured on B200 inside the captured decode step at 1.5B sizes: batch 1 (16
+    // blocks) 1.29 ms with three stages, 1.17 with five; batch 8 (128 blocks) 1.49 with three,
+    // 1.54 with five (a block that needs an SM to itself is placed later while blocks of the
+    // kernel in front are still there)
+    if (2ll * num_seqs * n_kv * cluster <= device_sms())
         return two ? MB_DC_LAUNCH(128, false, true, 5) : MB_DC_LAUNCH(128, false, false, 5);
     return two ? MB_DC_LAUNCH(128, false, true, 3) : MB_DC_LAUNCH(128, false, false, 3);
 #undef MB_DC_LAUNCH
