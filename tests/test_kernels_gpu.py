@@ -649,6 +649,9 @@ ATTENTION_CASES = [
     (16, 8, 128, 16, (2, 1), (500, 129), 0),
     (4, 2, 64, 16, (1, 2), (700, 300), 128),
     (7, 1, 64, 64, (2,), (333,), 0),
+    # one block walks more keys than the 256 block-table entries it keeps in shared memory
+    (14, 2, 64, 16, (1, 1), (5000, 4101), 0),
+    (4, 2, 128, 8, (1, 2), (2500, 40), 0),
 ]
 
 
