@@ -307,6 +307,17 @@ skinny_gemm_kernel(SkinnyInput in_all,
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
     if (n0 < limit) skinny_mainloop<NT, NORM>(in, rstd_s, w, n0, T, K, c_begin, c_end, acc);
+    if (EPI == 2 && next_norm_w != nullptr && blockIdx.z == 0) {
+        // The gated form has no next norm: its two spare arguments name the matrix of the
+        // product behind it (`h_stable` lines of 128 bytes from `next_norm_w` on). This
+        // kernel's own weights are in by now, so L2 is asked for those lines here: they travel
+        // while this kernel reduces, stores and leaves, and the product behind (whose blocks
+        // of 1024 threads cannot be resident beside these) finds them there.
+        const char* ahead = reinterpret_cast<const char*>(next_norm_w);
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < h_stable;
+             i += (long long)gridDim.x * blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(ahead + i * 128));
+    }
     store_partial<NT>(red, acc);
     __syncthreads();
 
@@ -930,7 +941,10 @@ MB_EXPORT int mb_gemm_skinny(const void* x, const float* h, const void* norm_w, 
 MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* norm_w,
                                     const int* rows, float eps, const float* ss_part, int ss_tiles,
                                     float ss_eps, int ss_k, const void* w, void* out, int T,
-                                    int width, int K, int* error, void* stream) {
+                                    int width, int K, const void* ahead, long long ahead_bytes,
+                                    int* error, void* stream) {
+    // ahead, ahead_bytes: the matrix that the product behind this one will stream (or null):
+    // L2 is asked for it once this product's own weights are in
     if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
@@ -951,8 +965,9 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
     const int threads = rowt * ksplit * 32;
     const int N = 2 * width, half_n = width;
     const void* bias = nullptr;
-    const int h_stable = 0;
-    const void* next_w = nullptr;
+    const bool look_ahead = ahead != nullptr && ahead_bytes >= 128 && ahead_bytes / 128 < (1ll << 30);
+    const int h_stable = look_ahead ? (int)(ahead_bytes / 128) : 0;   // (EPI 2: lines to ask L2 for)
+    const void* next_w = look_ahead ? ahead : nullptr;                // (EPI 2: where they start)
     void* next_x = nullptr;
     float* next_ss = nullptr;
     const int slices = 1;

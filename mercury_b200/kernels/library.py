@@ -49,7 +49,7 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "mb_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                               c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                              c_void_p],
+                              c_longlong, c_void_p, c_void_p],
     "mb_gemm_skinny_set_fed_min": [c_longlong],
     "mb_gemm_skinny_qkv_rope": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float,
                                 c_int, c_void_p, c_void_p,

@@ -81,6 +81,13 @@ class CudaOps:
         # 2048 tokens: K 896, 34 us one CTA against 35 us pairs; K 1536, 91 against 86; at 4096
         # tokens, K 3584 and 2 x 18944 rows, 1515 against 1028)
         self.pair_min_k = 1024
+        # The gated few-token product asks L2 for the down-proj's matrix while it finishes, up
+        # to this many bytes (a matrix that L2 cannot hold beside everything else gains nothing)
+        self.look_ahead_max_bytes = 32 * 1024 * 1024
+        # ... and from this many tokens on (measured on B200 inside the captured decode step,
+        # 0.5B sizes: 16 sequences 0.950 -> 0.907 ms; 8 sequences 0.598 -> 0.605, one sequence
+        # 0.566 -> 0.578: with few tokens the kernel is too short for the lines to arrive)
+        self.look_ahead_min_tokens = 9
         # ... and beyond this many weight elements the library's product followed by the gate
         # kernel is ahead of both (measured on B200 at 2048 tokens, replayed from a graph:
         # 2 x 4864 x 896, 35 us fused against 43; 2 x 8960 x 1536, 87 against 101;
@@ -428,16 +435,24 @@ class CudaOps:
         self.library_calls += 1
 
     @_timed("gated product")
-    def linear_swiglu(self, x, weight, out, ctx):
+    def linear_swiglu(self, x, weight, out, ctx, ahead=None):
         """out = silu(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]: one kernel
-        for few tokens, product then gate otherwise."""
+        for few tokens, product then gate otherwise. `ahead`: the matrix that the product
+        behind this one will stream; the few-token kernel asks L2 for it once its own weights
+        are in (`look_ahead_max_bytes` bounds what is asked for)."""
         m, k = x.shape
         width = out.shape[1]
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_supports(m, width, k)
                 and 2 * width * k <= self.skinny_max_elements):
+            bytes_ahead = 0
+            if (ahead is not None and m >= self.look_ahead_min_tokens and ahead.is_cuda
+                    and ahead.is_contiguous()
+                    and ahead.numel() * ahead.element_size() <= self.look_ahead_max_bytes):
+                bytes_ahead = ahead.numel() * ahead.element_size()
             check(self.lib.mb_gemm_skinny_swiglu(*self._skinny_input(x), _ptr(weight), _ptr(out),
-                                                 m, width, k, _ptr(self._error_word()),
+                                                 m, width, k, _ptr(ahead) if bytes_ahead else None,
+                                                 bytes_ahead, _ptr(self._error_word()),
                                                  self._stream()),
                   "linear_swiglu (skinny)")
             self.launches += 1

@@ -42,7 +42,7 @@ class GatedFeedForward(FeedForward):
     def forward(self, x, ctx, residual=None, then_norm=None):
         tokens = x.shape[0]
         act = ctx.buffer("ff_act", tokens, self.intermediate_size)
-        ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx)
+        ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx, ahead=self.down_weight)
         if residual is not None:
             return ctx.ops.linear_residual(act, self.down_weight, None, residual, ctx, "ff_out",
                                            then_norm=then_norm)

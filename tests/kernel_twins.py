@@ -64,7 +64,7 @@ class TorchOps:
             y = y + bias.to(self.acc)
         out.copy_(y.to(out.dtype))
 
-    def linear_swiglu(self, x, weight, out, ctx=None):
+    def linear_swiglu(self, x, weight, out, ctx=None, ahead=None):
         x = self._x(x)
         gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         self.linear(x, weight, None, gate_up)
