@@ -694,8 +694,19 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                          (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
                                    : smem_raw;
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_base);     // [16][D]
+    // FED: half stages of 32 keys, two per consumer warp at head size 64, one at 128 (two
+    // blocks are to fit an SM); a head of 128 features lies as two sub-tiles of 64, each
+    // 128-byte swizzled, the form in which TMA leaves a box of 64 features
+    constexpr int HALF = MMA_BN / 2, HDEPTH = D == 64 ? 2 : 1, HSTAGES = 4 * HDEPTH;
+    constexpr bool SUBTILED = FED && D > 64;
+    constexpr int KV_ELEMS = FED ? HSTAGES * HALF * D : STAGES * MMA_BN * D;
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
-    __nv_bfloat16* v_s = k_s + STAGES * MMA_BN * D;                       // [STAGES][64][D]
+    __nv_bfloat16* v_s = k_s + KV_ELEMS;                                  // [STAGES][64][D]
+    // where row j, 16-byte piece c of a key (or value) tile lies
+    auto piece_at = [&](const __nv_bfloat16* tile, int j, int c) -> const __nv_bfloat16* {
+        if (SUBTILED) return tile + (c >> 3) * (HALF * 64) + j * 64 + (((c & 7) ^ (j & 7)) * 8);
+        return tile + j * D + ((c ^ (j & 7)) * 8);
+    };
     // (rows of D + 4 floats: the warps write their pieces of O^T column by column, and with
     // this stride the 32 lanes of a store fall into 32 banks)
     constexpr int OR = D + 4;
@@ -705,7 +716,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // [range][row of this block][D], then [range][row of this block][maximum, sum]; no
     // other use, since a block that is done early writes here while this one still runs
     constexpr bool PUSH = D == 64;
-    float* land_o = reinterpret_cast<float*>(v_s + STAGES * MMA_BN * D);
+    float* land_o = reinterpret_cast<float*>(v_s + KV_ELEMS);
     float* land_ml = land_o + 16 * D;
     __shared__ float ml_red[4][16][2];
     __shared__ float ml_part[16][2];                                      // row maximum (log2 units), sum
@@ -714,8 +725,6 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // copies (with 16 tiles per block that trip, not the copies, set the kernel's time).
     constexpr int PAGE_WINDOW = 256;
     __shared__ int page_s[PAGE_WINDOW];
-    // FED: the four stages are eight half stages of 32 keys, two per consumer warp
-    constexpr int HALF = MMA_BN / 2, HSTAGES = 2 * STAGES;
     __shared__ uint64_t tile_full[HSTAGES];      // FED: a half stage's copies have landed
     __shared__ uint64_t tile_free[HSTAGES];      // FED: its warp has read it
     __shared__ uint32_t tile_pages[HSTAGES];     // FED: which of its pages were there
@@ -822,10 +831,10 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         const int w = lane >> copies_shift, piece = lane & ((1 << copies_shift) - 1);
         const int h = 4 * r + w;
         const bool active = w < 4 && h < n_half;
-        const int hs = (w & 3) + 4 * (r & 1);
+        const int hs = (w & 3) + 4 * (r % HDEPTH);
         bool ok = true;
         if (active && reuse)
-            ok = mbar_wait(&tile_free[hs], (uint32_t)(((r >> 1) - 1) & 1), error ? error : &fed_error, 8);
+            ok = mbar_wait(&tile_free[hs], (uint32_t)((r / HDEPTH - 1) & 1), error ? error : &fed_error, 8);
         if (!__all_sync(0xffffffffu, ok)) return false;
         int page = -1, row = 0;
         if (active) {
@@ -843,12 +852,17 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         if (active && piece == 0) {
             const unsigned mine = (valid >> (w << copies_shift)) & ((1u << (1 << copies_shift)) - 1u);
             tile_pages[hs] = mine;
-            mbar_expect_tx(&tile_full[hs], (uint32_t)(__popc(mine) << (box_shift + 8)));
+            // (a copy brings `box` keys of 2 D bytes, of K and of V)
+            mbar_expect_tx(&tile_full[hs], (uint32_t)(__popc(mine) << box_shift) * (4u * D));
         }
         __syncwarp();
         if (page >= 0) {
-            tma_load_2d(k_s + (hs * HALF + (piece << box_shift)) * D, &map_k, 0, row, &tile_full[hs]);
-            tma_load_2d(v_s + (hs * HALF + (piece << box_shift)) * D, &map_v, 0, row, &tile_full[hs]);
+#pragma unroll
+            for (int sb = 0; sb < D / 64; ++sb) {
+                const int to = hs * HALF * D + sb * (HALF * 64) + (piece << box_shift) * 64;
+                tma_load_2d(k_s + to, &map_k, sb * 64, row, &tile_full[hs]);
+                tma_load_2d(v_s + to, &map_v, sb * 64, row, &tile_full[hs]);
+            }
         }
         return true;
     };
@@ -991,9 +1005,8 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     if (resident) asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
     if (FED && warp == 4) {
-        // the first two rounds (the block table and the barriers are there now)
-        fetch_round(0, false);
-        if (n_half > 4) fetch_round(1, false);
+        // the first rounds (the block table and the barriers are there now)
+        for (int r = 0; r < HDEPTH && 4 * r < n_half; ++r) fetch_round(r, false);
     }
     uint32_t qf[D / 16][4];                  // Q as the B operand: [0], [1] rows 0..7, [2], [3] rows 8..15
 #pragma unroll
@@ -1012,7 +1025,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             uint32_t a[4];
             const int j = j0 + (lane & 15);
             const int c = ks * 2 + (lane >> 4);
-            ldmatrix_x4(a, kt_s + j * D + ((c ^ (j & 7)) * 8));
+            ldmatrix_x4(a, piece_at(kt_s, j, c));
             mma_bf16(sc[0], a, qf[ks][0], qf[ks][1]);
             if (two) mma_bf16(sc[1], a, qf[ks][2], qf[ks][3]);
         }
@@ -1079,7 +1092,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             uint32_t a[4];
             const int j = j0 + (lane & 7) + (lane >> 4) * 8;
             const int c = d2 * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4_trans(a, vt_s + j * D + ((c ^ (j & 7)) * 8));
+            ldmatrix_x4_trans(a, piece_at(vt_s, j, c));
             mma_bf16(o[d2][0], a, pt[0][0], pt[0][1]);
             if (two) mma_bf16(o[d2][1], a, pt[1][0], pt[1][1]);
         }
@@ -1123,7 +1136,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                     const int unit = u_lo + u;
                     const int j = (unit & 3) * 16 + (lane & 15);
                     const int c = ks * 2 + (lane >> 4);
-                    ldmatrix_x4(a[u], k_s + (unit >> 2) * MMA_BN * D + j * D + ((c ^ (j & 7)) * 8));
+                    ldmatrix_x4(a[u], piece_at(k_s + (unit >> 2) * MMA_BN * D, j, c));
                 }
             }
 #pragma unroll
@@ -1152,7 +1165,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     if (FED && warp == 4) {
         // ---- the producer warp: a round's half tiles go into their half stages as soon as the
         // warps that own the stages have read what was there (two rounds earlier)
-        for (int r = 2; 4 * r < n_half; ++r)
+        for (int r = HDEPTH; 4 * r < n_half; ++r)
             if (!fetch_round(r, true)) break;
     } else if (FED) {
         // ---- Many tiles per block: every consumer warp walks half tiles of its own (warp w
@@ -1161,11 +1174,11 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         // the half stage back to the producer warp, so that no barrier of the block stands in
         // the loop, the copies are nobody's detour, and while a warp waits the others work.
         for (int h = warp; h < n_half; h += 4) {
-            const int hs = warp + 4 * ((h >> 2) & 1);
+            const int hs = warp + 4 * ((h >> 2) % HDEPTH);
             const int key_base = t_lo * MMA_BN + h * HALF;
             // (bounded like every mbarrier wait of this library; a wait that gives up sets
             // the error word and the warp goes on with whatever the stage holds)
-            mbar_wait(&tile_full[hs], (uint32_t)((h >> 3) & 1), error ? error : &fed_error, 8);
+            mbar_wait(&tile_full[hs], (uint32_t)(((h >> 2) / HDEPTH) & 1), error ? error : &fed_error, 8);
             __nv_bfloat16* kt_s = k_s + hs * HALF * D;
             __nv_bfloat16* vt_s = v_s + hs * HALF * D;
             if (raw && key_base + HALF > first_pos) {
@@ -1174,10 +1187,9 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                     const int tok = idx / CH, c = idx - tok * CH;
                     const int row = first_pos + tok - key_base;
                     if (row < 0 || row >= HALF) continue;
-                    const int sw = (c ^ (row & 7)) * 8;
-                    *reinterpret_cast<uint4*>(kt_s + row * D + sw) =
+                    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(piece_at(kt_s, row, c))) =
                         *reinterpret_cast<const uint4*>(&new_k[tok][c * 8]);
-                    *reinterpret_cast<uint4*>(vt_s + row * D + sw) =
+                    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(piece_at(vt_s, row, c))) =
                         *reinterpret_cast<const uint4*>(&new_v[tok][c * 8]);
                 }
             }
@@ -1190,7 +1202,8 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 if (!there) {
                     const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-                    for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(vt_s + lane * D + c * 8) = zero;
+                    for (int c = 0; c < CH; ++c)
+                        *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(piece_at(vt_s, lane, c))) = zero;
                 }
             }
             __syncwarp();
@@ -1208,7 +1221,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 for (int u = 0; u < 2; ++u) {
                     const int j = u * 16 + (lane & 15);
                     const int c = ks * 2 + (lane >> 4);
-                    ldmatrix_x4(a[u], kt_s + j * D + ((c ^ (j & 7)) * 8));
+                    ldmatrix_x4(a[u], piece_at(kt_s, j, c));
                 }
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
@@ -1471,7 +1484,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         const int r_first = (int)split * per_block;
         const uint32_t local_o = (uint32_t)__cvta_generic_to_shared(o_part);
         const uint32_t local_ml = (uint32_t)__cvta_generic_to_shared(&ml_part[0][0]);
-        for (int e = tid; e < per_block * D; e += 128) {
+        for (int e = tid; e < per_block * D && tid < 128; e += 128) {
             const int r = r_first + e / D, c = e % D;
             if (r >= rows) continue;
             float mz[8], vz[8], lz[8];
@@ -1542,7 +1555,9 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     // queries and key/value stages; with head size 64 also the landing area of the merge
     // (FED: and room to start the tiles on a 1024-byte boundary)
-    const size_t smem = (size_t)(16 * D + 2 * STAGES * MMA_BN * D) * sizeof(__nv_bfloat16) +
+    // (FED: half stages of 32 keys, eight at head size 64, four at 128, as in the kernel)
+    const size_t kv_elems = FED ? (size_t)(D == 64 ? 8 : 4) * (MMA_BN / 2) * D : (size_t)STAGES * MMA_BN * D;
+    const size_t smem = (size_t)(16 * D + 2 * kv_elems) * sizeof(__nv_bfloat16) +
                         (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
@@ -1655,9 +1670,9 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                 int raw, int store, int num_pages, int* error,
                                                 void* stream) {
     // num_pages > 0 (with the pages' count) and `error` (a zeroed word on the device) select
-    // the TMA-fed form for head size 64 and pages of 8 to 64 tokens: for blocks that walk many
-    // key tiles each (large batches). 0: the copies are 16 bytes per thread, as the small
-    // batches want them, whose tiles are all in flight before the kernel in front is done.
+    // the TMA-fed form (pages of 8 to 64 tokens): for blocks that walk many key tiles each
+    // (large batches). 0: the copies are 16 bytes per thread, as the small batches want them,
+    // whose tiles are all in flight before the kernel in front is done.
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     // (pages of one token would leave the kernel's window of the block table shorter than
@@ -1670,7 +1685,7 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
     // reads another layer's cache must find this step's keys in the pages
     if (raw && !store) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool fed = d == 64 && num_pages > 0 && error != nullptr && page_size >= 8 &&
+    const bool fed = num_pages > 0 && error != nullptr && page_size >= 8 &&
                      page_size <= MMA_BN && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
     // (the longest portion bounds every sequence's rows: one column tile of 8 rows, or two)
     const bool two = max_q_len * (n_q / n_kv) > 8;
@@ -1679,7 +1694,8 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                     q_start, kv_len, out, n_q, n_kv, page_size, scale, \
                                                     window, num_seqs, cluster, cos_t, sin_t, raw, store, \
                                                     FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
-    if (fed) return two ? MB_DC_LAUNCH(64, true, true, 4) : MB_DC_LAUNCH(64, true, false, 4);
+    if (fed && d == 64) return two ? MB_DC_LAUNCH(64, true, true, 4) : MB_DC_LAUNCH(64, true, false, 4);
+    if (fed) return two ? MB_DC_LAUNCH(128, true, true, 4) : MB_DC_LAUNCH(128, true, false, 4);
     if (d == 64) return two ? MB_DC_LAUNCH(64, false, true, 5) : MB_DC_LAUNCH(64, false, false, 5);
     // head size 128: five stages (164 KB, one block per SM) while the blocks are at most half
     // the SMs. Measured on B200 inside the captured decode step at 1.5B sizes: batch 1 (16

@@ -685,8 +685,8 @@ def test_rope_store_and_attention(twin, dtype, kernel, splits, case):
                                                        and max(q_lens) * (n_q // n_kv) <= 16):
         pytest.skip("the cluster kernel is for decode-like batches of head size 64 or 128")
     if kernel == "clusters-tma":
-        if d != 64 or not 8 <= page <= 64:
-            pytest.skip("the TMA-fed form is for head size 64 and pages of 8 to 64 tokens")
+        if not 8 <= page <= 64:
+            pytest.skip("the TMA-fed form is for pages of 8 to 64 tokens")
         ops.decode_long_ranges = True      # the form that large batches take
     # for the tensor-memory kernel the split is the number of CTAs that share a row tile, for
     # the decode clusters the number of blocks of a (sequence, KV head)
