@@ -655,7 +655,7 @@ class CudaOps:
         cos, sin = tables if tables is not None else (None, None)
         self._check_limits(cache, tables)
         # blocks that walk many key tiles each (a large batch) get their tiles by TMA
-        fed = self._long_ranges(batch, num_kv_heads)
+        fed = self._long_ranges(batch, num_kv_heads, head_dim)
         if fed:
             self._tc_pending = True
         check(self.lib.mb_paged_attention_decode_cluster(
@@ -667,13 +667,21 @@ class CudaOps:
             self._stream()), "paged_attention (decode clusters)")
         self.launches += 1
 
-    def _long_ranges(self, batch, num_kv_heads) -> bool:
-        """Whether the blocks of the cluster decode kernel will walk many key tiles each:
-        the batch alone brings more (sequence, KV head) pairs than `graph_small_rows`, so
-        that few key ranges per pair fill the device."""
+    def _long_ranges(self, batch, num_kv_heads, head_dim=64) -> bool:
+        """Whether the cluster decode kernel takes its TMA-fed form. Head size 64: when its
+        blocks will walk many key tiles each, that is when the batch alone brings more
+        (sequence, KV head) pairs than `graph_small_rows`, so that few key ranges per pair fill
+        the device (for small batches every tile is in shared memory before the kernel in
+        front is done, and 16 bytes per thread and copy are the faster way there). Head size
+        128, whose tiles cost a thread twice the copies: from 16 pairs on (measured on B200
+        inside the captured decode step, 1.5B sizes: 8 sequences 1.56 -> 1.34 ms, 16: 2.10 ->
+        1.76; 4 sequences 1.23 -> 1.25, one 1.18 -> 1.22)."""
         if self.decode_long_ranges is not None:
             return bool(self.decode_long_ranges)
-        return batch.num_seqs * num_kv_heads > 2 * self.graph_small_rows
+        pairs = batch.num_seqs * num_kv_heads
+        if head_dim > 64:
+            return pairs >= self.graph_small_rows
+        return pairs > 2 * self.graph_small_rows
 
     @staticmethod
     def _cluster_of(splits: int) -> int:
