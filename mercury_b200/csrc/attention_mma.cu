@@ -682,7 +682,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
     // the new values into the pages (if `store`) and into its own tiles. The product in front
     // then needs no block per head, and every tile of the pages can be copied before the wait.
     constexpr int CH = D / 8;
-    // (FED: one stage per warp, see the tile loop)
+    // (FED: STG counts half stages, see below)
     constexpr int STAGES = FED ? 4 : STG;
     __nv_bfloat16* k_pages_out = const_cast<__nv_bfloat16*>(k_pages);
     __nv_bfloat16* v_pages_out = const_cast<__nv_bfloat16*>(v_pages);
@@ -694,10 +694,10 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                          (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
                                    : smem_raw;
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_base);     // [16][D]
-    // FED: half stages of 32 keys, two per consumer warp at head size 64, one at 128 (two
-    // blocks are to fit an SM); a head of 128 features lies as two sub-tiles of 64, each
+    // FED: STG half stages of 32 keys, two per consumer warp, or one where two blocks of head
+    // size 128 are to fit an SM; a head of 128 features lies as two sub-tiles of 64, each
     // 128-byte swizzled, the form in which TMA leaves a box of 64 features
-    constexpr int HALF = MMA_BN / 2, HDEPTH = D == 64 ? 2 : 1, HSTAGES = 4 * HDEPTH;
+    constexpr int HALF = MMA_BN / 2, HDEPTH = FED ? STG / 4 : 1, HSTAGES = 4 * HDEPTH;
     constexpr bool SUBTILED = FED && D > 64;
     constexpr int KV_ELEMS = FED ? HSTAGES * HALF * D : STAGES * MMA_BN * D;
     __nv_bfloat16* k_s = q_s + 16 * D;                                    // [STAGES][64][D]
@@ -1555,8 +1555,8 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     // queries and key/value stages; with head size 64 also the landing area of the merge
     // (FED: and room to start the tiles on a 1024-byte boundary)
-    // (FED: half stages of 32 keys, eight at head size 64, four at 128, as in the kernel)
-    const size_t kv_elems = FED ? (size_t)(D == 64 ? 8 : 4) * (MMA_BN / 2) * D : (size_t)STAGES * MMA_BN * D;
+    // (FED: STG half stages of 32 keys, as in the kernel)
+    const size_t kv_elems = FED ? (size_t)STG * (MMA_BN / 2) * D : (size_t)STAGES * MMA_BN * D;
     const size_t smem = (size_t)(16 * D + 2 * kv_elems) * sizeof(__nv_bfloat16) +
                         (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
@@ -1694,7 +1694,10 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
                                                     q_start, kv_len, out, n_q, n_kv, page_size, scale, \
                                                     window, num_seqs, cluster, cos_t, sin_t, raw, store, \
                                                     FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
-    if (fed && d == 64) return two ? MB_DC_LAUNCH(64, true, true, 4) : MB_DC_LAUNCH(64, true, false, 4);
+    // (TMA-fed: eight half stages at head size 64, four at 128, where eight would leave an SM
+    // to one block: measured at 1.5B sizes with no more blocks than SMs, 8 sequences, 1.32 ms per
+    // step with four and 1.44 with eight)
+    if (fed && d == 64) return two ? MB_DC_LAUNCH(64, true, true, 8) : MB_DC_LAUNCH(64, true, false, 8);
     if (fed) return two ? MB_DC_LAUNCH(128, true, true, 4) : MB_DC_LAUNCH(128, true, false, 4);
     if (d == 64) return two ? MB_DC_LAUNCH(64, false, true, 5) : MB_DC_LAUNCH(64, false, false, 5);
     // head size 128: five stages (164 KB, one block per SM) while the blocks are at most half
