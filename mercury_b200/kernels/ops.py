@@ -94,6 +94,10 @@ class CudaOps:
         # 2 x 18944 x 3584, 503 against 424: there the library's 1.5 PFLOP/s outweigh the
         # gate kernel's extra pass)
         self.gated_max_elements = 64 * 1024 * 1024
+        # ... and so it is for small portions, below this many multiply-adds (replayed from a
+        # graph: 512 tokens at 0.5B widths 17.5 us fused against 14.9; 1024 tokens 23.5 against
+        # 25.2; 256 tokens at 1.5B widths 16.2 against 16.5; 512 tokens 25.4 against 28.5)
+        self.gated_min_products = 8 * 10 ** 9
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head sizes 64 and
         # 128, the mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
@@ -462,7 +466,8 @@ class CudaOps:
             x = x.materialize()
         if (self.gemm in ("tcgen05", "auto") and x.dtype == torch.bfloat16
                 and weight.dtype == torch.bfloat16 and m >= 256 and width % 8 == 0
-                and (2 * width * k <= self.gated_max_elements or self.gemm == "tcgen05")
+                and ((2 * width * k <= self.gated_max_elements
+                      and 2 * m * width * k >= self.gated_min_products) or self.gemm == "tcgen05")
                 and self.lib.mb_gemm_tcgen05_supports(m, width, k)):
             if k >= self.pair_min_k and self.lib.mb_gemm_pair_supports(m, width, k):
                 # pairs of SMs sharing one 256-row MMA: a CTA loads a third less per output
