@@ -404,6 +404,44 @@ def e2e_rate(torch, config, tensors, batch, context, vocab, steps, warmup):
     return tokens / seconds, lay["size"] * 4, batch * 4
 
 
+def other_sizes(torch, args) -> dict:
+    """The side workloads of the benchmark description, one flat block: decode at batch 8 and
+    the 2048-token prompt at Qwen2.5-1.5B and 7B sizes (all their layers, random weights), and
+    the mixed serving workload at 1.5B sizes. A size that fails says so and does not take the
+    line with it."""
+    from types import SimpleNamespace
+
+    from mercury_b200.config import config_from_dict
+    from mercury_b200.weights import random_tensors
+
+    out = {}
+    for name in ("1.5b", "7b"):
+        try:
+            raw = SIZES[name]
+            _entry, config = config_from_dict(raw)
+            tensors = random_tensors(config, SEED, torch.bfloat16)
+            runner = make_runner(torch, config, tensors, BATCH, BATCH * (CONTEXT + 256))
+            steps = min(args.steps, 32)
+            rate, ms, _l, _s = decode_rate(torch, runner, BATCH, CONTEXT, raw["vocab_size"], steps,
+                                           max(3, min(args.warmup, 8)))
+            out[f"{name}_decode_b8"] = round(rate, 1)
+            out[f"{name}_decode_ms"] = round(ms, 4)
+            out[f"{name}_prefill_ms"] = round(prefill_rate(torch, runner, raw["vocab_size"], reps=3), 3)
+            out[f"{name}_layers"] = raw["num_hidden_layers"]
+            del runner
+            torch.cuda.empty_cache()
+            if name == "1.5b":
+                mixed = run_mixed(SimpleNamespace(size=name, policy="lpm"), prepared=(config, tensors))
+                out["1.5b_mixed_output_tokens_per_s"] = mixed["output_tokens_per_s"]
+                out["1.5b_mixed_prefix_hit_tokens"] = mixed["prefix_hit_tokens"]
+                out["1.5b_mixed_requests"] = 32
+            del tensors
+            torch.cuda.empty_cache()
+        except Exception as exc:      # a side workload must not cost the headline its line
+            out[f"{name}_error"] = f"{type(exc).__name__}: {exc}"[:200]
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -431,6 +469,9 @@ def run_ours(args) -> dict:
     del runner
     torch.cuda.empty_cache()
     e2e, h2d, d2h = e2e_rate(torch, config, tensors, BATCH, CONTEXT, vocab, args.steps, args.warmup)
+    del tensors
+    torch.cuda.empty_cache()
+    sizes = {} if args.no_sizes else other_sizes(torch, args)
 
     def step_bytes(batch, steps_before):
         return numbers["weight_bytes"] + batch * (CONTEXT + steps_before) * numbers["kv_bytes_per_token"]
@@ -465,6 +506,7 @@ def run_ours(args) -> dict:
         "point_rooflines": {"decode_b1": {"ms": round(ms1, 4), "frac": fraction(1, ms1, args.warmup + 3 * args.steps // 2)},
                             "decode_b64": {"ms": round(ms64, 4), "frac": fraction(64, ms64, args.warmup + 3 * args.steps // 2)}},
         "kernels": kernels,
+        "sizes": sizes,
         "clocks": clocks,
     }
 
@@ -559,7 +601,7 @@ def run_part(args) -> dict:
             "launches_per_step": launches, "graphs": not args.no_graphs}
 
 
-def run_mixed(args) -> dict:
+def run_mixed(args, prepared=None) -> dict:
     """`--only mixed`: 32 requests through Engine.generate, prompt lengths uniform in
     [64, 2048], half of them sharing one 512-token prefix, 128 greedy tokens each (the
     benchmark description's serving workload, by default at Qwen2.5-1.5B sizes)."""
@@ -571,8 +613,11 @@ def run_mixed(args) -> dict:
     from mercury_b200.weights import random_tensors
 
     raw = SIZES[args.size]
-    _entry, config = config_from_dict(raw)
-    tensors = random_tensors(config, SEED, torch.bfloat16)
+    if prepared is None:
+        _entry, config = config_from_dict(raw)
+        tensors = random_tensors(config, SEED, torch.bfloat16)
+    else:
+        config, tensors = prepared
     gen = torch.Generator().manual_seed(SEED + 5)
     shared = torch.randint(0, raw["vocab_size"], (512,), generator=gen).tolist()
     prompts = []
@@ -694,6 +739,8 @@ def main() -> int:
     p.add_argument("--policy", default="lpm", choices=("fcfs", "lpm", "lpm_aging"))
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")
     p.add_argument("--no-graphs", action="store_true", help="launch kernels one by one")
+    p.add_argument("--no-sizes", action="store_true",
+                   help="leave the 1.5B and 7B side workloads out of the full run (about a minute)")
     p.add_argument("--gemm", default=None, choices=("library", "tcgen05", "auto"),
                    help="many-token product of --only prefill/decode (default: the engine's)")
     args = p.parse_args()
