@@ -306,6 +306,18 @@ def test_linear_swiglu(ops, twin, m, width, k):
     # gate and up are rounded to bfloat16 before the gate, then the result once more
     err = float((got.double() - want.double()).abs().max() / want.double().abs().max())
     assert err <= 3 * 2.0 ** -8, err
+    # with the matrix of the product behind named (the few-token kernel asks L2 for it while it
+    # finishes; sizes that are no multiple of a line, and one too large to be asked for): the
+    # same result, and the matrix untouched
+    for rows in (7, 896, 5000):
+        ahead = rand((rows, width + 3), torch.bfloat16, 23)
+        kept = ahead.clone()
+        again = torch.zeros_like(got)
+        ops.look_ahead_min_tokens = 1
+        ops.look_ahead_max_bytes = 4 * 1024 * 1024
+        ops.linear_swiglu(x, w, again, ctx, ahead=ahead)
+        torch.cuda.synchronize()
+        assert torch.equal(again, got) and torch.equal(ahead, kept)
 
 
 def fake_ctx(ops):
