@@ -571,13 +571,22 @@ class CudaOps:
 
     def _prompt_cluster(self, batch, num_kv_heads, group) -> int:
         """CTAs per row tile of the tensor-memory attention: the CTAs of a cluster share a
-        row tile and split its keys (merged through distributed shared memory). Measured on
-        B200 the split never paid with one CTA per SM and the heaviest row tiles scheduled
-        first (14 heads over 2 KV heads of 64, 2048 tokens: 36 us alone, 61 us in pairs; 12
-        over 2 of 128: 36 against 60 us), so it is used only when asked for."""
+        row tile and split its keys (merged through distributed shared memory). It pays only
+        while the row tiles alone leave SMs idle, that is for portions of a prompt: measured
+        on B200 (14 heads over 2 KV heads of 64, context 2048, replayed from a graph) a prompt
+        in portions of 256 tokens (30 row tiles a step) took 11.3 ms whole, 10.7 ms in pairs and
+        10.5 in fours; in portions of 512 (58 row tiles) 6.13 and 6.13 ms; in one step of 2048
+        tokens (228 row tiles) 2.8 ms whole, 3.5 in pairs, 4.5 in fours."""
         if self.prompt_cluster is not None:
             return self.prompt_cluster
-        return 1
+        tokens_per_tile = max(1, 128 // group)
+        row_tiles = batch.num_seqs * -(-batch.max_q_len // tokens_per_tile) * num_kv_heads
+        if batch.max_kv_len < 4 * 128:
+            return 1
+        cluster = 1
+        while cluster < 4 and row_tiles * cluster * 2 <= self.sm_count:
+            cluster *= 2
+        return cluster
 
     def _prompt_splits(self, batch, num_kv_heads, group) -> int:
         """Key ranges per row tile of a prompt portion. Cutting the keys (and merging the
